@@ -1,0 +1,37 @@
+"""hipkittens_b200: B200-native bf16 GQA flash-attention forward and paged-KV decode.
+
+Everything here runs on hand-written sm_100a CUDA kernels behind a C ABI (``include/hk_attn.h``,
+``lib/libhk_attn.so``). There is no CPU or PyTorch fallback: if the native library is missing or no
+sm_100 device is present, calls raise.
+
+Public surface
+--------------
+* ``attn_fwd(q, k, v, causal=False, ...) -> (O, L)`` and ``paged_decode(...) -> (O, L)``: torch-tensor
+  front ends over the C ABI (ctypes).
+* ``load_tk_kernel(causal)`` / ``load_tk_kernel_fwd(causal)``: the reference's extension modules
+  (``tk_kernel.dispatch_micro``, ``tk_kernel_fwd.dispatch_fwd``) built for B200.
+* ``HipAttnFunction`` in :mod:`hipkittens_b200.attention`: the reference's autograd-function forward.
+"""
+from ._native import (  # noqa: F401
+    HkError,
+    attn_fwd,
+    capi,
+    kernel_launch_count,
+    lib_path,
+    load_tk_kernel,
+    load_tk_kernel_fwd,
+    paged_decode,
+    paged_decode_workspace_bytes,
+)
+
+__all__ = [
+    "HkError",
+    "attn_fwd",
+    "capi",
+    "kernel_launch_count",
+    "lib_path",
+    "load_tk_kernel",
+    "load_tk_kernel_fwd",
+    "paged_decode",
+    "paged_decode_workspace_bytes",
+]

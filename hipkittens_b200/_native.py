@@ -1,0 +1,220 @@
+"""ctypes binding of ``libhk_attn.so`` plus torch-tensor front ends.
+
+torch is used for device memory and streams only; all arithmetic happens in the CUDA library.
+"""
+from __future__ import annotations
+
+import ctypes
+import importlib.util
+import math
+import os
+import sysconfig
+from typing import Optional, Tuple
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+_LIB = os.path.join(_PKG, "lib", "libhk_attn.so")
+
+HK_OK, HK_EINVAL, HK_EUNSUPPORTED, HK_ECUDA, HK_ETIMEOUT, HK_EWORKSPACE = 0, -1, -2, -3, -4, -5
+
+# Every symbol declared in include/hk_attn.h.
+EXPORTED_SYMBOLS = (
+    "hk_attn_fwd",
+    "hk_attn_paged_decode_workspace_bytes",
+    "hk_attn_paged_decode",
+    "hk_last_device_status",
+    "hk_kernel_launch_count",
+    "hk_strerror",
+    "hk_last_cuda_error",
+)
+
+
+class HkError(RuntimeError):
+    """A libhk_attn call returned a negative HK_E* code."""
+
+    def __init__(self, code: int, what: str, detail: str = ""):
+        self.code = code
+        msg = f"{what}: error {code}"
+        if detail:
+            msg += f" ({detail})"
+        super().__init__(msg)
+
+
+def lib_path() -> str:
+    return _LIB
+
+
+_capi = None
+
+
+def capi() -> ctypes.CDLL:
+    """The loaded C-ABI library with argument types declared. Raises if it has not been built."""
+    global _capi
+    if _capi is not None:
+        return _capi
+    if not os.path.exists(_LIB):
+        raise ImportError(
+            f"{_LIB} is missing: build it with `python -m hipkittens_b200._build` (needs nvcc); "
+            "there is no fallback implementation"
+        )
+    lib = ctypes.CDLL(_LIB)
+    vp, ci, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+    lib.hk_attn_fwd.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, cf, ci, vp]
+    lib.hk_attn_fwd.restype = ci
+    lib.hk_attn_paged_decode_workspace_bytes.argtypes = [ci, ci, ci, ci, ci]
+    lib.hk_attn_paged_decode_workspace_bytes.restype = ctypes.c_size_t
+    lib.hk_attn_paged_decode.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cf, vp,
+                                         ctypes.c_size_t, ci, vp]
+    lib.hk_attn_paged_decode.restype = ci
+    lib.hk_last_device_status.argtypes = [ci]
+    lib.hk_last_device_status.restype = ci
+    lib.hk_kernel_launch_count.argtypes = []
+    lib.hk_kernel_launch_count.restype = ctypes.c_ulonglong
+    lib.hk_strerror.argtypes = [ci]
+    lib.hk_strerror.restype = ctypes.c_char_p
+    lib.hk_last_cuda_error.argtypes = []
+    lib.hk_last_cuda_error.restype = ctypes.c_char_p
+    _capi = lib
+    return lib
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != HK_OK:
+        lib = capi()
+        detail = lib.hk_strerror(rc).decode()
+        extra = lib.hk_last_cuda_error().decode()
+        if extra and rc in (HK_ECUDA, HK_EUNSUPPORTED):
+            detail += "; " + extra
+        raise HkError(rc, what, detail)
+
+
+def kernel_launch_count() -> int:
+    return int(capi().hk_kernel_launch_count())
+
+
+def _require_cuda_bf16(name: str, t: torch.Tensor, ndim: int) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise RuntimeError("Expected a torch.Tensor")
+    if not t.is_contiguous():
+        raise RuntimeError("Tensor must be contiguous")
+    if t.device.type != "cuda":
+        raise RuntimeError("Tensor must be on CUDA device")
+    if t.dim() != ndim:
+        raise RuntimeError(f"{name} must have {ndim} dimensions, got {t.dim()}")
+
+
+def attn_fwd(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    causal: bool = False,
+    softmax_scale: Optional[float] = None,
+    out: Optional[torch.Tensor] = None,
+    lse: Optional[torch.Tensor] = None,
+    stream: Optional[torch.cuda.Stream] = None,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """O = softmax(scale q k^T) v and L = logsumexp(scale q k^T) on the GPU.
+
+    q [B,N,H,D] bf16, k/v [B,N,H_KV,D] bf16, contiguous CUDA tensors; returns O [B,N,H,D] bf16 and
+    L [B,H,1,N] fp32 (the layouts of kernels/attn/gqa/test_python.py:97-98). Asynchronous on `stream`
+    (default: torch's current stream).
+    """
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _require_cuda_bf16(name, t, 4)
+        if t.dtype != torch.bfloat16:
+            raise RuntimeError(f"{name} must be torch.bfloat16")
+    b, n, h, d = q.shape
+    hkv = k.shape[2]
+    if k.shape != v.shape or k.shape[0] != b or k.shape[1] != n or k.shape[3] != d:
+        raise RuntimeError("k/v must be [B, N, H_KV, D] matching q")
+    if out is None:
+        out = torch.empty_like(q)
+    if lse is None:
+        lse = torch.empty((b, h, 1, n), dtype=torch.float32, device=q.device)
+    if out.shape != q.shape or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise RuntimeError("out must be a contiguous bf16 tensor of q's shape")
+    if lse.shape != (b, h, 1, n) or lse.dtype != torch.float32 or not lse.is_contiguous():
+        raise RuntimeError("lse must be a contiguous fp32 tensor [B, H, 1, N]")
+    s = stream if stream is not None else torch.cuda.current_stream(q.device)
+    rc = capi().hk_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                            b, n, h, hkv, d, int(bool(causal)), float(softmax_scale or 0.0),
+                            q.device.index, s.cuda_stream)
+    _check(rc, "hk_attn_fwd")
+    return out, lse
+
+
+def paged_decode_workspace_bytes(s: int, h: int, d: int, max_pages: int, page_size: int = 16) -> int:
+    return int(capi().hk_attn_paged_decode_workspace_bytes(s, h, d, max_pages, page_size))
+
+
+def paged_decode(
+    q: torch.Tensor,
+    k_pages: torch.Tensor,
+    v_pages: torch.Tensor,
+    block_table: torch.Tensor,
+    ctx_lens: torch.Tensor,
+    softmax_scale: Optional[float] = None,
+    out: Optional[torch.Tensor] = None,
+    lse: Optional[torch.Tensor] = None,
+    workspace: Optional[torch.Tensor] = None,
+    stream: Optional[torch.cuda.Stream] = None,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Paged-KV decode: q [S,1,H,D] bf16, pages [P,16,H_KV,D] bf16, block_table [S,max_pages] int32,
+    ctx_lens [S] int32 -> O [S,1,H,D] bf16, L [S,H,1,1] fp32. `workspace` is a uint8 CUDA tensor of at
+    least ``paged_decode_workspace_bytes(...)`` bytes (allocated here when omitted)."""
+    for name, t in (("q", q), ("k_pages", k_pages), ("v_pages", v_pages)):
+        _require_cuda_bf16(name, t, 4)
+        if t.dtype != torch.bfloat16:
+            raise RuntimeError(f"{name} must be torch.bfloat16")
+    if block_table.dtype != torch.int32 or ctx_lens.dtype != torch.int32:
+        raise RuntimeError("block_table and ctx_lens must be torch.int32")
+    if not (block_table.is_contiguous() and ctx_lens.is_contiguous()):
+        raise RuntimeError("Tensor must be contiguous")
+    s_n, one, h, d = q.shape
+    p_n, page, hkv, d2 = k_pages.shape
+    if one != 1 or d2 != d or v_pages.shape != k_pages.shape:
+        raise RuntimeError("q must be [S,1,H,D] and k_pages/v_pages [P,page,H_KV,D]")
+    if block_table.dim() != 2 or block_table.shape[0] != s_n or ctx_lens.shape != (s_n,):
+        raise RuntimeError("block_table must be [S, max_pages] and ctx_lens [S]")
+    max_pages = block_table.shape[1]
+    if out is None:
+        out = torch.empty_like(q)
+    if lse is None:
+        lse = torch.empty((s_n, h, 1, 1), dtype=torch.float32, device=q.device)
+    need = paged_decode_workspace_bytes(s_n, h, d, max_pages, page)
+    if workspace is None:
+        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=q.device)
+    st = stream if stream is not None else torch.cuda.current_stream(q.device)
+    rc = capi().hk_attn_paged_decode(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
+                                     block_table.data_ptr(), ctx_lens.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                     s_n, h, hkv, d, page, max_pages, p_n, float(softmax_scale or 0.0),
+                                     workspace.data_ptr(), workspace.numel(), q.device.index, st.cuda_stream)
+    _check(rc, "hk_attn_paged_decode")
+    return out, lse
+
+
+def device_status(device: int = 0) -> int:
+    """Synchronise `device` and return the kernels' status word as an HK_* code (0 = OK)."""
+    return int(capi().hk_last_device_status(device))
+
+
+def _load_ext(subdir: str, module: str):
+    path = os.path.join(_PKG, subdir, module + sysconfig.get_config_var("EXT_SUFFIX"))
+    if not os.path.exists(path):
+        raise ImportError(f"{path} is missing: build it with `python -m hipkittens_b200._build`")
+    spec = importlib.util.spec_from_file_location(module, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def load_tk_kernel(causal: bool = False):
+    """The ``tk_kernel`` module of kernels/attn/gqa (or gqa_causal): ``dispatch_micro(q,k,v,out,lse)``."""
+    return _load_ext("kernels/attn/gqa_causal" if causal else "kernels/attn/gqa", "tk_kernel")
+
+
+def load_tk_kernel_fwd(causal: bool = True):
+    """The ``tk_kernel_fwd`` module of the training call site: blocking ``dispatch_fwd(q,k,v,O,L)``."""
+    return _load_ext("kernels/attn/gqa_causal_backwards" if causal else "kernels/attn/gqa_backwards",
+                     "tk_kernel_fwd")

@@ -1,0 +1,255 @@
+// Host side of libhk_attn: argument validation, TMA descriptors, launches. C ABI in include/hk_attn.h.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/hk_attn.h"
+#include "attn_fwd_sm100.cuh"
+#include "paged_decode_sm100.cuh"
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+
+thread_local char g_cuda_err[256] = "";
+std::atomic<unsigned long long> g_launches{0};
+
+int cuda_fail(cudaError_t e, const char* what) {
+  snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", what, cudaGetErrorString(e));
+  return HK_ECUDA;
+}
+#define HK_CUDA(call)                                   \
+  do {                                                  \
+    cudaError_t e__ = (call);                           \
+    if (e__ != cudaSuccess) return cuda_fail(e__, #call); \
+  } while (0)
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// Per-device state: SM count, the device status word, one-time kernel attribute set-up.
+struct DeviceState {
+  std::once_flag once;
+  int init_rc = HK_OK;
+  int sm_count = 0;
+  int cc_major = 0;
+  int* status = nullptr;  // device word
+};
+DeviceState g_dev[kMaxDevices];
+
+template <int D, bool CAUSAL>
+int prepare_fwd_kernel() {
+  auto* fn = hk::attn_fwd_kernel<D, CAUSAL>;
+  HK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, hk::FwdSmem<D>::kDynBytes));
+  cudaFuncAttributes attr;
+  HK_CUDA(cudaFuncGetAttributes(&attr, fn));
+  // The kernel re-balances registers between warpgroups (232/232/40 per thread); that only adds up if
+  // it was compiled to exactly 168 registers per thread at launch. Refuse to launch otherwise: a
+  // register pool that is too small would block the re-allocation forever.
+  if (attr.numRegs != 168) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "attn_fwd_kernel<%d,%d> compiled to %d registers, expected 168", D,
+             int(CAUSAL), attr.numRegs);
+    return HK_EUNSUPPORTED;
+  }
+  return HK_OK;
+}
+
+int init_device(int device) {
+  DeviceState& st = g_dev[device];
+  cudaDeviceProp prop;
+  HK_CUDA(cudaGetDeviceProperties(&prop, device));
+  st.sm_count = prop.multiProcessorCount;
+  st.cc_major = prop.major;
+  if (prop.major != 10) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "device %d is sm_%d%d; this library needs sm_100", device, prop.major,
+             prop.minor);
+    return HK_EUNSUPPORTED;
+  }
+  HK_CUDA(cudaMalloc(&st.status, sizeof(int)));
+  HK_CUDA(cudaMemset(st.status, 0, sizeof(int)));
+  int rc;
+  if ((rc = prepare_fwd_kernel<128, false>()) != HK_OK) return rc;
+  if ((rc = prepare_fwd_kernel<128, true>()) != HK_OK) return rc;
+  if ((rc = prepare_fwd_kernel<64, false>()) != HK_OK) return rc;
+  if ((rc = prepare_fwd_kernel<64, true>()) != HK_OK) return rc;
+  if ((rc = hk::prepare_decode_kernels(g_cuda_err, sizeof(g_cuda_err))) != HK_OK) return rc;
+  return HK_OK;
+}
+
+// Makes `device` current (when >= 0) and returns its state, initialising it on first use.
+int use_device(int device, DeviceState** out) {
+  if (device < 0) HK_CUDA(cudaGetDevice(&device));
+  if (device >= kMaxDevices) return HK_EINVAL;
+  HK_CUDA(cudaSetDevice(device));
+  DeviceState& st = g_dev[device];
+  std::call_once(st.once, [&] { st.init_rc = init_device(device); });
+  if (st.init_rc != HK_OK) return st.init_rc;
+  *out = &st;
+  return HK_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// 4-D map over a contiguous bf16 [B, N, heads, D] tensor, box = 64 columns x 1 head x 128 rows,
+// 128-byte swizzle (rows of the box are 128 B, the layout tcgen05 descriptors expect).
+int make_bnhd_map(CUtensorMap* map, const void* base, int B, int N, int heads, int D) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled not available from the driver");
+    return HK_ECUDA;
+  }
+  cuuint64_t dims[4] = {cuuint64_t(D), cuuint64_t(heads), cuuint64_t(N), cuuint64_t(B)};
+  cuuint64_t strides[3] = {cuuint64_t(D) * 2, cuuint64_t(heads) * D * 2, cuuint64_t(N) * heads * D * 2};
+  cuuint32_t box[4] = {64, 1, cuuint32_t(hk::kBlockM), 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
+    return HK_ECUDA;
+  }
+  return HK_OK;
+}
+
+template <int D, bool CAUSAL>
+int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const hk::FwdParams& p,
+               int grid, cudaStream_t stream) {
+  hk::attn_fwd_kernel<D, CAUSAL><<<grid, hk::kFwdThreads, hk::FwdSmem<D>::kDynBytes, stream>>>(tq, tk, tv, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  HK_CUDA(cudaGetLastError());
+  return HK_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int hk_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int N, int H, int H_KV,
+                int D, int causal, float softmax_scale, int device, void* cuda_stream) {
+  if (!q || !k || !v || !o || !lse) return HK_EINVAL;
+  if (B <= 0 || N <= 0 || H <= 0 || H_KV <= 0) return HK_EINVAL;
+  if (D != 64 && D != 128) return HK_EUNSUPPORTED;
+  if (H % H_KV != 0 || N % hk::kBlockM != 0) return HK_EINVAL;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || (reinterpret_cast<uintptr_t>(lse) & 3))
+    return HK_EINVAL;
+  DeviceState* st = nullptr;
+  int rc = use_device(device, &st);
+  if (rc != HK_OK) return rc;
+
+  CUtensorMap tq, tk, tv;
+  if ((rc = make_bnhd_map(&tq, q, B, N, H, D)) != HK_OK) return rc;
+  if ((rc = make_bnhd_map(&tk, k, B, N, H_KV, D)) != HK_OK) return rc;
+  if ((rc = make_bnhd_map(&tv, v, B, N, H_KV, D)) != HK_OK) return rc;
+
+  const int G = H / H_KV;
+  const int nqb = N / hk::kBlockM;
+  hk::FwdParams p;
+  p.o = static_cast<__nv_bfloat16*>(o);
+  p.lse = lse;
+  p.B = B;
+  p.N = N;
+  p.H = H;
+  p.H_KV = H_KV;
+  p.pair_heads = (G % 2 == 0) ? 1 : 0;
+  p.n_items = p.pair_heads ? B * H_KV * (G / 2) * nqb : B * H_KV * G * ((nqb + 1) / 2);
+  p.scale = softmax_scale > 0.f ? softmax_scale : 1.0f / std::sqrt(float(D));
+  p.scale_log2 = p.scale * 1.4426950408889634f;
+  p.status = st->status;
+  const int grid = p.n_items < st->sm_count ? p.n_items : st->sm_count;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (D == 128) return causal ? launch_fwd<128, true>(tq, tk, tv, p, grid, stream)
+                              : launch_fwd<128, false>(tq, tk, tv, p, grid, stream);
+  return causal ? launch_fwd<64, true>(tq, tk, tv, p, grid, stream)
+                : launch_fwd<64, false>(tq, tk, tv, p, grid, stream);
+}
+
+size_t hk_attn_paged_decode_workspace_bytes(int S, int H, int D, int max_pages_per_seq, int page_size) {
+  return hk::decode_workspace_bytes(S, H, D, max_pages_per_seq, page_size);
+}
+
+int hk_attn_paged_decode(const void* q, const void* k_pages, const void* v_pages, const int32_t* block_table,
+                         const int32_t* ctx_lens, void* o, float* lse, int S, int H, int H_KV, int D,
+                         int page_size, int max_pages_per_seq, int num_pages, float softmax_scale,
+                         void* workspace, size_t workspace_bytes, int device, void* cuda_stream) {
+  if (!q || !k_pages || !v_pages || !block_table || !ctx_lens || !o || !lse) return HK_EINVAL;
+  if (S <= 0 || H <= 0 || H_KV <= 0 || max_pages_per_seq <= 0 || num_pages <= 0) return HK_EINVAL;
+  if (D != 128 || page_size != 16) return HK_EUNSUPPORTED;
+  if (H % H_KV != 0) return HK_EINVAL;
+  const int G = H / H_KV;
+  if (G != 1 && G != 2 && G != 4 && G != 8) return HK_EUNSUPPORTED;
+  if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(o)) return HK_EINVAL;
+  const size_t need = hk::decode_workspace_bytes(S, H, D, max_pages_per_seq, page_size);
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)) return HK_EWORKSPACE;
+  DeviceState* st = nullptr;
+  int rc = use_device(device, &st);
+  if (rc != HK_OK) return rc;
+  hk::DecodeParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
+  p.v_pages = static_cast<const __nv_bfloat16*>(v_pages);
+  p.block_table = block_table;
+  p.ctx_lens = ctx_lens;
+  p.o = static_cast<__nv_bfloat16*>(o);
+  p.lse = lse;
+  p.S = S;
+  p.H = H;
+  p.H_KV = H_KV;
+  p.max_pages = max_pages_per_seq;
+  p.num_pages = num_pages;
+  p.scale = softmax_scale > 0.f ? softmax_scale : 1.0f / std::sqrt(float(D));
+  p.scale_log2 = p.scale * 1.4426950408889634f;
+  p.workspace = workspace;
+  p.status = st->status;
+  int launched = 0;
+  cudaError_t e = hk::launch_paged_decode(p, st->sm_count, static_cast<cudaStream_t>(cuda_stream), &launched);
+  g_launches.fetch_add(launched, std::memory_order_relaxed);
+  if (e != cudaSuccess) return cuda_fail(e, "paged decode launch");
+  return HK_OK;
+}
+
+int hk_last_device_status(int device) {
+  DeviceState* st = nullptr;
+  int rc = use_device(device, &st);
+  if (rc != HK_OK) return rc;
+  HK_CUDA(cudaDeviceSynchronize());
+  int word = 0;
+  HK_CUDA(cudaMemcpy(&word, st->status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (word != 0) HK_CUDA(cudaMemset(st->status, 0, sizeof(int)));
+  return word == hk::kStatusOk ? HK_OK : HK_ETIMEOUT;
+}
+
+unsigned long long hk_kernel_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char* hk_strerror(int code) {
+  switch (code) {
+    case HK_OK: return "ok";
+    case HK_EINVAL: return "invalid argument (shape, null or misaligned pointer)";
+    case HK_EUNSUPPORTED: return "unsupported configuration or device";
+    case HK_ECUDA: return "CUDA call failed";
+    case HK_ETIMEOUT: return "bounded device-side wait expired";
+    case HK_EWORKSPACE: return "workspace missing, misaligned or too small";
+    default: return "unknown error code";
+  }
+}
+
+const char* hk_last_cuda_error(void) { return g_cuda_err; }
+
+}  // extern "C"

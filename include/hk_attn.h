@@ -1,0 +1,69 @@
+/* C ABI of libhk_attn: bf16 grouped-query flash-attention forward and paged-KV decode for NVIDIA B200.
+ *
+ * Plain pointers and sizes only. All pointers are DEVICE pointers on `device` unless a comment says
+ * otherwise. Every function returns 0 on success or a negative HK_E* code; none aborts or throws.
+ * Kernels are launched asynchronously on `cuda_stream` (NULL = the legacy default stream), exactly as
+ * the reference launcher does (kernels/attn/gqa/kernel.cpp:576-581).
+ */
+#ifndef HK_ATTN_H_
+#define HK_ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HK_OK 0
+#define HK_EINVAL (-1)       /* bad shape, null or misaligned pointer */
+#define HK_EUNSUPPORTED (-2) /* head dim / page size / device not supported */
+#define HK_ECUDA (-3)        /* a CUDA runtime or driver call failed; see hk_last_cuda_error() */
+#define HK_ETIMEOUT (-4)     /* a bounded device-side wait expired; results are invalid */
+#define HK_EWORKSPACE (-5)   /* workspace missing or too small */
+
+/* Attention forward.
+ * Replaces dispatch_micro<D>(attn_globals<D>) (kernels/attn/gqa/kernel.cpp:93-100,576-581, causal twin
+ * kernels/attn/gqa_causal/kernel.cpp) and dispatch_fwd<D> (training/llama/csrc/attn_fwd_causal.cpp:624-630).
+ *   q, o   : bf16 [B, N, H, D] contiguous          k, v : bf16 [B, N, H_KV, D] contiguous
+ *   lse    : fp32 [B, H, 1, N] contiguous, natural-log logsumexp of the scaled logits
+ *   D in {64, 128}; N a multiple of 128; H a multiple of H_KV; pointers 16-byte aligned.
+ *   causal != 0 applies the lower-triangular mask; softmax_scale <= 0 selects 1/sqrt(D).
+ * Shapes, causality and scale are compile-time constants in the reference; here they are arguments. */
+int hk_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                int B, int N, int H, int H_KV, int D, int causal, float softmax_scale,
+                int device, void* cuda_stream);
+
+/* Paged-KV decode: one query token per sequence attends to its whole context. No counterpart exists in
+ * the reference (its nearest relative is the contiguous cache update training/llama/llama/models/mha.py:16-42).
+ *   q, o        : bf16 [S, 1, H, D]                 lse : fp32 [S, H, 1, 1]
+ *   k_pages, v_pages : bf16 [num_pages, page_size, H_KV, D]
+ *   block_table : int32 [S, max_pages_per_seq]; token j of sequence s is row j % page_size of page
+ *                 block_table[s, j / page_size]; entries must lie in [0, num_pages)
+ *   ctx_lens    : int32 [S], 1 <= ctx_lens[s] <= max_pages_per_seq * page_size
+ *   D = 128, page_size = 16, H / H_KV in {1, 2, 4, 8}.
+ *   workspace   : device scratch of at least hk_attn_paged_decode_workspace_bytes(...) bytes, 256-byte
+ *                 aligned; holds the per-split partial results between the two kernels. */
+size_t hk_attn_paged_decode_workspace_bytes(int S, int H, int D, int max_pages_per_seq, int page_size);
+int hk_attn_paged_decode(const void* q, const void* k_pages, const void* v_pages,
+                         const int32_t* block_table, const int32_t* ctx_lens, void* o, float* lse,
+                         int S, int H, int H_KV, int D, int page_size, int max_pages_per_seq, int num_pages,
+                         float softmax_scale, void* workspace, size_t workspace_bytes,
+                         int device, void* cuda_stream);
+
+/* Synchronises `device` and reports the device-side status word of the kernels above:
+ * HK_OK, or HK_ETIMEOUT when a bounded wait inside a kernel expired. The word is cleared on read.
+ * The reference launchers check nothing after launch (include/pyutils/util.cuh:6-16). */
+int hk_last_device_status(int device);
+
+/* Number of kernels this library has launched in the calling process (all devices). */
+unsigned long long hk_kernel_launch_count(void);
+
+/* Text for an HK_* code, and the text of the last CUDA error seen by the calling thread. */
+const char* hk_strerror(int code);
+const char* hk_last_cuda_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HK_ATTN_H_ */

@@ -1,0 +1,198 @@
+"""CPU oracle for the bf16 GQA attention forward and the paged-KV decode variant.
+
+TEST INFRASTRUCTURE ONLY. Nothing in the product package imports this module; it is used by the
+tests, by the smoke check and by the CPU-baseline leg of the benchmark as the checker / baseline.
+
+What it restates
+----------------
+The reference's PyTorch math path, ``training/llama/llama/models/attentions/base.py:78-120``
+(``CrossAttention.forward``): GQA by repeating each KV head over its group (``:92-93``),
+``scores = einsum("bthd,bshd->bhts", q, k * scale)`` (``:96``), causal mask ``col > row + Sk - Sq``
+(``:104-116``), softmax over keys (``:117``), ``einsum("bhts,bshd->bthd", attention, v)`` (``:119``).
+
+Deliberate deltas (they define the parity target of this build):
+  1. the softmax and both contractions run in fp32 on the bf16 inputs (the reference softmaxes in
+     ``v.dtype``, i.e. bf16 for bf16 inputs);
+  2. masked logits are ``-inf`` instead of ``-10000`` (identical after exp in fp32);
+  3. it also returns ``L = logsumexp(scale * q k^T)`` (natural log) per (batch, head, row), laid out
+     ``[B, H, 1, N]`` as the kernels do: ``kernels/attn/gqa/kernel.cpp:569-573`` computes
+     ``max * ln2 + ln(sum)`` in the log2 domain and stores it at ``L[b, h, 0, row]``;
+  4. O is rounded to bf16 once at the end, as the kernels do (``kernels/attn/gqa/kernel.cpp:565-567``).
+
+Parity pin
+----------
+O is pinned against outputs of the reference module itself, run in this build's container on fp32
+copies of bf16-valued inputs (then delta 1 vanishes and the reference computes exactly this math);
+see ``tests/golden/make_golden.py`` and ``tests/test_oracle.py``. The reference has no CPU path that
+emits L and no recorded kernel outputs, so L is pinned only to its definition above, and parity
+against the reference's HIP kernels themselves is unpinned (they cannot run here).
+
+The paged decode variant has no counterpart in the reference; its oracle gathers each sequence's
+pages through the block table and applies the same math to one query row.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+__all__ = [
+    "attn_fwd_oracle",
+    "paged_decode_oracle",
+    "make_prefill_inputs",
+    "make_paged_inputs",
+    "robustness_check",
+]
+
+
+def _unit(q_g: torch.Tensor, k_g: torch.Tensor, v_g: torch.Tensor, scale: float, causal: bool):
+    """One (batch, kv-head) unit. q_g [N, G, D] fp32, k_g/v_g [S, D] fp32 -> O [N, G, D] fp32, L [G, N]."""
+    n, _, _ = q_g.shape
+    s = k_g.shape[0]
+    # base.py:96  scores = einsum(q, k * scale)
+    scores = torch.einsum("tgd,sd->gts", q_g, k_g * scale)
+    if causal:
+        # base.py:104-116  col > row + Sk - Sq is masked
+        row = torch.arange(n).view(n, 1)
+        col = torch.arange(s).view(1, s)
+        scores = scores.masked_fill((col > row + (s - n)).unsqueeze(0), float("-inf"))
+    lse = torch.logsumexp(scores, dim=-1)  # [G, N]
+    # base.py:117,119  softmax then contraction with v
+    attn = torch.exp(scores - lse.unsqueeze(-1))
+    out = torch.einsum("gts,sd->tgd", attn, v_g)
+    return out, lse
+
+
+def attn_fwd_oracle(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    causal: bool = False,
+    softmax_scale: Optional[float] = None,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """q [B,N,H,D], k/v [B,S,H_KV,D] (any float dtype; values are used as given, math in fp32).
+
+    Returns O [B,N,H,D] bf16 and L [B,H,1,N] fp32. Work is chunked per (batch, kv-head) so that the
+    largest benchmark shapes fit in host memory.
+    """
+    b, n, h, d = q.shape
+    hkv = k.shape[2]
+    assert h % hkv == 0 and k.shape == v.shape and k.shape[0] == b and k.shape[3] == d
+    g = h // hkv
+    scale = softmax_scale if softmax_scale else 1.0 / math.sqrt(d)
+    out = torch.empty((b, n, h, d), dtype=torch.bfloat16)
+    lse = torch.empty((b, h, 1, n), dtype=torch.float32)
+    for bi in range(b):
+        for kh in range(hkv):
+            qg = q[bi, :, kh * g:(kh + 1) * g, :].float()
+            o_u, l_u = _unit(qg, k[bi, :, kh, :].float(), v[bi, :, kh, :].float(), scale, causal)
+            out[bi, :, kh * g:(kh + 1) * g, :] = o_u.to(torch.bfloat16)
+            lse[bi, kh * g:(kh + 1) * g, 0, :] = l_u
+    return out, lse
+
+
+def paged_decode_oracle(
+    q: torch.Tensor,
+    k_pages: torch.Tensor,
+    v_pages: torch.Tensor,
+    block_table: torch.Tensor,
+    ctx_lens: torch.Tensor,
+    softmax_scale: Optional[float] = None,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """q [S,1,H,D]; k_pages/v_pages [P,page,H_KV,D]; block_table [S,max_pages] int32; ctx_lens [S] int32.
+
+    Token j of sequence s lives at ``pages[block_table[s, j // page], j % page]``. The single query row
+    sees all ``ctx_lens[s]`` keys. Returns O [S,1,H,D] bf16 and L [S,H,1,1] fp32.
+    """
+    s_n, one, h, d = q.shape
+    assert one == 1
+    page = k_pages.shape[1]
+    hkv = k_pages.shape[2]
+    g = h // hkv
+    scale = softmax_scale if softmax_scale else 1.0 / math.sqrt(d)
+    out = torch.empty((s_n, 1, h, d), dtype=torch.bfloat16)
+    lse = torch.empty((s_n, h, 1, 1), dtype=torch.float32)
+    for si in range(s_n):
+        ctx = int(ctx_lens[si])
+        npg = (ctx + page - 1) // page
+        ids = block_table[si, :npg].long()
+        ks = k_pages[ids].reshape(npg * page, hkv, d)[:ctx].float()
+        vs = v_pages[ids].reshape(npg * page, hkv, d)[:ctx].float()
+        for kh in range(hkv):
+            qg = q[si, :, kh * g:(kh + 1) * g, :].float()  # [1, G, D]
+            o_u, l_u = _unit(qg, ks[:, kh, :], vs[:, kh, :], scale, causal=False)
+            out[si, :, kh * g:(kh + 1) * g, :] = o_u.to(torch.bfloat16)
+            lse[si, kh * g:(kh + 1) * g, 0, :] = l_u
+    return out, lse
+
+
+def make_prefill_inputs(b: int, n: int, h: int, hkv: int, d: int, seed: int = 0):
+    """bf16 i.i.d. N(0,1) q, k, v drawn on the CPU in that order from one seed.
+
+    This is the reference harness's distribution (``kernels/attn/gqa/test_python.py:30-32``); drawing on
+    the CPU lets the oracle and the GPU see identical bits.
+    """
+    gen = torch.Generator().manual_seed(seed)
+    q = torch.randn((b, n, h, d), generator=gen, dtype=torch.float32).to(torch.bfloat16)
+    k = torch.randn((b, n, hkv, d), generator=gen, dtype=torch.float32).to(torch.bfloat16)
+    v = torch.randn((b, n, hkv, d), generator=gen, dtype=torch.float32).to(torch.bfloat16)
+    return q, k, v
+
+
+def make_paged_inputs(
+    n_seq: int,
+    h: int,
+    hkv: int,
+    d: int,
+    page: int,
+    num_pages: int,
+    ctx_lo: int,
+    ctx_hi: int,
+    seed: int = 0,
+    pool_on: Optional[str] = None,
+):
+    """Synthetic paged-KV decode problem.
+
+    Context lengths are uniform integers in [ctx_lo, ctx_hi]; every sequence's block table is a slice
+    of one seeded permutation of page ids, so ids are distinct across the whole batch. The K/V pools
+    are bf16 N(0,1). ``pool_on`` may name a device on which to draw the (large) pools directly.
+    """
+    gen = torch.Generator().manual_seed(seed)
+    ctx = torch.randint(ctx_lo, ctx_hi + 1, (n_seq,), generator=gen, dtype=torch.int32)
+    npg = (ctx + page - 1) // page
+    total = int(npg.sum())
+    assert total <= num_pages, "page pool too small for the drawn context lengths"
+    perm = torch.randperm(num_pages, generator=gen, dtype=torch.int64)[:total].to(torch.int32)
+    max_pages = int(npg.max())
+    table = torch.zeros((n_seq, max_pages), dtype=torch.int32)
+    off = 0
+    for s in range(n_seq):
+        c = int(npg[s])
+        table[s, :c] = perm[off:off + c]
+        off += c
+    q = torch.randn((n_seq, 1, h, d), generator=gen, dtype=torch.float32).to(torch.bfloat16)
+    if pool_on is None:
+        kp = torch.randn((num_pages, page, hkv, d), generator=gen, dtype=torch.float32).to(torch.bfloat16)
+        vp = torch.randn((num_pages, page, hkv, d), generator=gen, dtype=torch.float32).to(torch.bfloat16)
+    else:
+        dgen = torch.Generator(device=pool_on).manual_seed(seed + 1)
+        kp = torch.randn((num_pages, page, hkv, d), generator=dgen, dtype=torch.bfloat16, device=pool_on)
+        vp = torch.randn((num_pages, page, hkv, d), generator=dgen, dtype=torch.bfloat16, device=pool_on)
+    return q, kp, vp, table, ctx
+
+
+def robustness_check(ref: torch.Tensor, pred: torch.Tensor):
+    """The reference harness's error statistics (``kernels/attn/gqa/test_python.py:46-57``).
+
+    Returns (max_abs, error_count, numel, rel_l2, cosine) where an element counts as an error when
+    ``|diff| > 0.001 + 0.05 * |ref|``.
+    """
+    ref = ref.float()
+    pred = pred.float()
+    diff = (ref - pred).abs()
+    denom = ref.abs().clamp_min(1e-6)
+    err = int((diff > (0.001 + 0.05 * denom)).sum())
+    l2 = float(diff.pow(2).sum().sqrt() / ref.pow(2).sum().sqrt())
+    cos = float(torch.nn.functional.cosine_similarity(ref.flatten(), pred.flatten(), dim=0))
+    return float(diff.max()), err, ref.numel(), l2, cos

@@ -1,0 +1,76 @@
+"""Generate the golden fixtures in this folder by running the reference's own PyTorch attention.
+
+Run once in a container that has the reference checkout (default location below, or pass its path):
+
+    python tests/golden/make_golden.py [/path/to/HipKittens]
+
+It imports ``llama.models.attentions.base.CrossAttention`` / ``SelfAttention`` from the reference's
+``training/llama`` tree and evaluates them on seeded bf16-valued inputs, once on fp32 copies (then the
+reference computes its softmax in fp32 and its result is the parity target to ~1e-6) and, for the
+first case, once natively in bf16 (its stock behaviour; looser agreement, recorded for context).
+
+Each ``case_*.npz`` holds the inputs as raw bf16 bit patterns (uint16), the reference outputs, and the
+logsumexp of the reference's own score expression ``einsum(q, k * scale)`` evaluated in fp64 -- the
+reference has no CPU path that returns L, so that array pins L's definition, not a reference output.
+The GPU box has no reference checkout; tests read only the committed ``.npz`` files.
+"""
+import math
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+# (name, B, N, H, H_KV, D, causal, seed)
+CASES = [
+    ("c1_b1_n256_h8_kv2_d64_nc", 1, 256, 8, 2, 64, False, 0),
+    ("b1_n128_h4_kv2_d64_causal", 1, 128, 4, 2, 64, True, 1),
+    ("b2_n128_h2_kv1_d128_causal", 2, 128, 2, 1, 128, True, 2),
+    ("b1_n256_h2_kv2_d128_nc", 1, 256, 2, 2, 128, False, 3),
+]
+
+
+def bf16_bits(t: torch.Tensor) -> np.ndarray:
+    return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def main() -> None:
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    sys.path.insert(0, os.path.join(ref_root, "training", "llama"))
+    from llama.models.attentions.base import CrossAttention, SelfAttention  # noqa: E402
+
+    for name, b, n, h, hkv, d, causal, seed in CASES:
+        gen = torch.Generator().manual_seed(seed)
+        q = torch.randn((b, n, h, d), generator=gen).to(torch.bfloat16)
+        k = torch.randn((b, n, hkv, d), generator=gen).to(torch.bfloat16)
+        v = torch.randn((b, n, hkv, d), generator=gen).to(torch.bfloat16)
+        attn = CrossAttention(causal=causal)
+        with torch.no_grad():
+            o32 = attn(q.float(), torch.stack([k.float(), v.float()], dim=2))
+            out = {"q": bf16_bits(q), "k": bf16_bits(k), "v": bf16_bits(v),
+                   "o_ref_fp32": o32.numpy().astype(np.float32),
+                   "shape": np.array([b, n, h, hkv, d, int(causal), seed], dtype=np.int64)}
+            if h == hkv:
+                # MHA: the SelfAttention module must agree with CrossAttention on the same inputs.
+                o_self = SelfAttention(causal=causal)(torch.stack([q.float(), k.float(), v.float()], dim=2))
+                assert torch.allclose(o_self, o32, atol=1e-6), "reference modules disagree"
+            if name.startswith("c1_"):
+                o16 = attn(q, torch.stack([k, v], dim=2))
+                out["o_ref_native_bf16"] = bf16_bits(o16)
+            # L: logsumexp of the reference's score expression (base.py:96), in fp64.
+            g = h // hkv
+            kk = k.double().repeat_interleave(g, dim=2)
+            scores = torch.einsum("bthd,bshd->bhts", q.double(), kk * (1.0 / math.sqrt(d)))
+            if causal:
+                mask = torch.triu(torch.ones(n, n, dtype=torch.bool), 1)
+                scores = scores.masked_fill(mask, float("-inf"))
+            out["lse_def_fp64"] = torch.logsumexp(scores, dim=-1).numpy()  # [B,H,N]
+        path = os.path.join(HERE, f"case_{name}.npz")
+        np.savez_compressed(path, **out)
+        print("wrote", path, os.path.getsize(path), "bytes")
+
+
+if __name__ == "__main__":
+    main()
