@@ -1,0 +1,474 @@
+#!/usr/bin/env python
+"""Benchmark of the bf16 GQA attention forward (and paged decode) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+A step is one pass of the hot path over one batch of synthetic input (one kernel launch for the
+forward; split + combine launches for decode). The default workload is the reference README's default
+shape: B=16, N=2048, H=64, H_KV=8, D=128, non-causal (kernels/attn/gqa/test_python.py:22-27).
+TFLOPS = 4*B*N^2*H*D / (2 if causal) / time, the reference's convention (test_python.py:35-38).
+
+With N > 1 (torchrun, one rank per GPU) every rank runs the same workload on its own seeded inputs
+(weak scaling: (batch, kv-head) units are independent, there is no collective on the data path);
+`value` is the sum over ranks divided by the slowest rank's time. `--scaling strong` instead splits the
+one workload's units over the ranks with hipkittens_b200.shard.
+
+One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (kind, B, N, H, H_KV, D, causal)
+    "gqa_fwd_b16_n2048_h64_kv8_d128": ("fwd", 16, 2048, 64, 8, 128, False),
+    "gqa_causal_fwd_b4_n8192_h64_kv8_d128": ("fwd", 4, 8192, 64, 8, 128, True),
+    "mha_fwd_b16_n4096_h16_d64": ("fwd", 16, 4096, 16, 16, 64, False),
+    "paged_decode_s64_ctx512_8192_h64_kv8_d128": ("decode", 64, 0, 64, 8, 128, False),
+}
+DEFAULT_WORKLOAD = "gqa_fwd_b16_n2048_h64_kv8_d128"
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
+# summarised under profiles/ (None = not captured for that workload).
+NCU_TRAFFIC_BYTES = {
+    "gqa_fwd_b16_n2048_h64_kv8_d128": None,
+    "gqa_causal_fwd_b4_n8192_h64_kv8_d128": None,
+    "mha_fwd_b16_n4096_h16_d64": None,
+    "paged_decode_s64_ctx512_8192_h64_kv8_d128": None,
+}
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+    except Exception:
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+def fwd_flops(b, n, h, d, causal):
+    return 4 * b * n * n * h * d // (2 if causal else 1)
+
+
+# ------------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the GPU is under load."""
+
+    REASONS = {
+        0x4: "sw_power_cap",
+        0x8: "hw_slowdown",
+        0x20: "sw_thermal_slowdown",
+        0x40: "hw_thermal_slowdown",
+        0x80: "hw_power_brake_slowdown",
+    }
+
+    def __init__(self, device_index: int, period_s: float = 0.01):
+        self.period = period_s
+        self.samples = []
+        self.timed = False
+        self._stop = threading.Event()
+        self._thread = None
+        self.sm_max = None
+        self.handle = None
+        try:
+            import pynvml
+
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            try:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self.sm_max = int(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.handle = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                mhz = int(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                except Exception:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                self.samples.append((self.timed, mhz, mask))
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def start(self):
+        if self.handle is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+
+    def summary(self):
+        if self.handle is None or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [], "samples": 0}
+        timed = [s for s in self.samples if s[0]]
+        use = timed if len(timed) >= 3 else self.samples
+        mask = 0
+        for s in use:
+            mask |= s[2]
+        reasons = [name for bit, name in self.REASONS.items() if mask & bit]
+        return {
+            "sm_mhz": statistics.median(s[1] for s in use),
+            "sm_max_mhz": self.sm_max,
+            "reasons": reasons,
+            "samples": len(use),
+            "window": "timed" if use is timed else "warmup+timed",
+        }
+
+
+# ------------------------------------------------------------------------------------------ CPU arm
+def cpu_prefill_sample(b, n, h, hkv, d, causal, budget_s: float, max_units: int):
+    """Times the oracle on (batch, kv-head) units of the workload's shape until `budget_s` is spent.
+    Returns (flops_done, seconds, units_done)."""
+    from hipkittens_b200.synthetic import make_prefill_inputs
+    from oracle.attn_oracle import attn_fwd_oracle
+
+    g = h // hkv
+    q, k, v = make_prefill_inputs(1, n, g, 1, d, seed=123)
+    attn_fwd_oracle(q[:, :128], k[:, :128], v[:, :128], causal)  # warm the thread pool
+    done, t0 = 0, time.perf_counter()
+    while done < max_units:
+        attn_fwd_oracle(q, k, v, causal)
+        done += 1
+        if time.perf_counter() - t0 >= budget_s:
+            break
+    dt = time.perf_counter() - t0
+    return done * fwd_flops(1, n, g, d, causal), dt, done
+
+
+def cpu_decode_sample(budget_s: float):
+    from hipkittens_b200.synthetic import make_paged_inputs
+    from oracle.attn_oracle import paged_decode_oracle
+
+    q, kp, vp, bt, cl = make_paged_inputs(8, 64, 8, 128, 16, 4200, 512, 8192, seed=0)
+    done, t0 = 0, time.perf_counter()
+    toks = 0
+    while True:
+        paged_decode_oracle(q, kp, vp, bt, cl)
+        done += 1
+        toks += 8
+        if time.perf_counter() - t0 >= budget_s:
+            break
+    return toks, int(cl.sum()) * done, time.perf_counter() - t0, done
+
+
+# ------------------------------------------------------------------------------------------ main
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--cpu-budget-s", type=float, default=12.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    kind, b, n, h, hkv, d, causal = WORKLOADS[args.workload]
+    peaks, peaks_src = load_peaks()
+
+    if args.impl == "reference":
+        return run_reference_arm(args, rank, world, kind, b, n, h, hkv, d, causal)
+
+    import hipkittens_b200 as hk
+    from hipkittens_b200 import _native
+    from hipkittens_b200.shard import partition_units, shard_tensors
+    from hipkittens_b200.synthetic import make_paged_inputs, make_prefill_inputs
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stream = torch.cuda.current_stream(dev)
+    sampler = ClockSampler(local_rank)
+
+    # ---------------- inputs resident in HBM
+    if kind == "fwd":
+        if args.scaling == "strong" and world > 1:
+            qf, kf, vf = make_prefill_inputs(b, n, h, hkv, d, seed=0)
+            parts = shard_tensors(qf, kf, vf, hkv, partition_units(b, hkv, world, rank))
+            shards = [(qs.to(dev), ks.to(dev), vs.to(dev)) for qs, ks, vs, _m in parts]
+            del qf, kf, vf
+        else:
+            qf, kf, vf = make_prefill_inputs(b, n, h, hkv, d, seed=rank)
+            shards = [(qf.to(dev), kf.to(dev), vf.to(dev))]
+        outs = [(torch.empty_like(qs), torch.empty((qs.shape[0], qs.shape[2], 1, n), dtype=torch.float32, device=dev))
+                for qs, _k, _v in shards]
+        my_flops = sum(fwd_flops(qs.shape[0], n, qs.shape[2], d, causal) for qs, _k, _v in shards)
+        my_units = float(my_flops)
+
+        def step():
+            for (qs, ks, vs), (o, l) in zip(shards, outs):
+                hk.attn_fwd(qs, ks, vs, causal=causal, out=o, lse=l, stream=stream)
+
+        in_bytes = sum(t.numel() * 2 for sh in shards for t in sh)
+    else:
+        q, kp, vp, bt, cl = make_paged_inputs(b, h, hkv, d, 16, 40000, 512, 8192, seed=rank, pool_on=str(dev))
+        q, bt, cl = q.to(dev), bt.to(dev), cl.to(dev)
+        ws = torch.empty(hk.paged_decode_workspace_bytes(b, h, d, bt.shape[1]), dtype=torch.uint8, device=dev)
+        o = torch.empty_like(q)
+        l = torch.empty((b, h, 1, 1), dtype=torch.float32, device=dev)
+        sum_ctx = int(cl.sum())
+        my_units = float(b)  # tokens generated per step
+        kv_bytes = 2 * sum_ctx * hkv * d * 2
+
+        def step():
+            hk.paged_decode(q, kp, vp, bt, cl, out=o, lse=l, workspace=ws, stream=stream)
+
+        in_bytes = kp.numel() * 4
+
+    # ---------------- device-resident timing
+    sampler.start()
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    launches0 = hk.kernel_launch_count()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    sampler.timed = True
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    sampler.timed = False
+    launches = hk.kernel_launch_count() - launches0
+    ms_total = e0.elapsed_time(e1)
+    status = _native.device_status(local_rank)
+    if status != 0:
+        raise SystemExit(f"device status {status} after the timed region")
+
+    # ---------------- end-to-end through the reference-facing module, host buffers
+    e2e = None
+    if not args.no_e2e:
+        e2e = measure_e2e(hk, kind, args, dev, stream, causal, b, n, h, hkv, d,
+                          shards if kind == "fwd" else None,
+                          (q, kp, vp, bt, cl, ws) if kind == "decode" else None, barrier)
+    sampler.stop()
+
+    # ---------------- reduce over ranks: slowest rank's time, summed work
+    ms = torch.tensor([ms_total, e2e["ms_total"] if e2e else 0.0], dtype=torch.float64, device=dev)
+    units = torch.tensor([my_units], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(units, op=dist.ReduceOp.SUM)
+    ms_total_max, e2e_ms_max = float(ms[0]), float(ms[1])
+    total_units = float(units[0])
+    ms_per_step = ms_total_max / args.steps
+
+    if rank == 0:
+        clocks = sampler.summary()
+        line = {
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "data": "synthetic",
+            "gpu_launches": int(launches), "clocks": clocks, "peaks_source": peaks_src,
+        }
+        if kind == "fwd":
+            tflops = total_units / (ms_per_step * 1e-3) / 1e12
+            per_launch_flops = my_flops / max(len(shards), 1)
+            ach = my_flops / (ms_total / args.steps * 1e-3) / 1e12
+            line.update({
+                "metric": "bf16 GQA attn-fwd TFLOPS (4*B*N^2*H*D, /2 causal)", "value": tflops, "unit": "TFLOP/s",
+                "dtype": "bf16",
+                "config": {"workload": args.workload, "B": b, "N": n, "H": h, "H_KV": hkv, "D": d,
+                           "causal": causal, "per_gpu_batch": b if args.scaling == "weak" else b / world,
+                           "cache": "inputs_exceed_l2" if in_bytes > 126e6 else "inputs_fit_l2",
+                           "sharding": "independent (batch, kv-head) units, no collective"},
+                "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                             "frac": ach / peaks["bf16_tflops"],
+                             "peak_sustained": peaks["bf16_tflops_sustained"],
+                             "frac_of_sustained": ach / peaks["bf16_tflops_sustained"],
+                             "peak_kind": f"of {peaks_src} (burst cuBLAS bf16)",
+                             "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                             "flops_per_launch": per_launch_flops},
+            })
+            if e2e:
+                line["e2e"] = {"value": total_units / (e2e_ms_max / e2e["steps"] * 1e-3) / 1e12, "unit": "TFLOP/s",
+                               "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                               "steps": e2e["steps"], "path": e2e["path"]}
+        else:
+            tok_s = total_units / (ms_per_step * 1e-3)
+            ach = kv_bytes / (ms_total / args.steps * 1e-3) / 1e9
+            line.update({
+                "metric": "paged-KV GQA decode tokens/s", "value": tok_s, "unit": "tokens/s", "dtype": "bf16",
+                "config": {"workload": args.workload, "S": b, "H": h, "H_KV": hkv, "D": d, "page": 16,
+                           "pool_pages": 40000, "ctx": "U{512..8192}", "sum_ctx": sum_ctx,
+                           "cache": "inputs_exceed_l2"},
+                "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": ach / peaks["hbm_gbs"], "peak_kind": f"of {peaks_src} (copy)",
+                             "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "bytes_per_launch": kv_bytes},
+            })
+            if e2e:
+                line["e2e"] = {"value": total_units / (e2e_ms_max / e2e["steps"] * 1e-3), "unit": "tokens/s",
+                               "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                               "steps": e2e["steps"], "path": e2e["path"]}
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(kind, b, n, h, hkv, d, causal, args.cpu_budget_s)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def measure_e2e(hk, kind, args, dev, stream, causal, b, n, h, hkv, d, shards, dec, barrier):
+    """Same step, but inputs start in pinned host memory and results end in pinned host memory, through
+    the reference's Python entry (tk_kernel.dispatch_micro / dispatch_paged_decode)."""
+    steps = max(1, min(args.steps, 10))
+    tk = hk.load_tk_kernel(causal)
+    if kind == "fwd":
+        host_in = [[t.cpu().pin_memory() for t in sh] for sh in shards]
+        dev_in = shards
+        dev_out = [(torch.empty_like(sh[0]), torch.empty((sh[0].shape[0], sh[0].shape[2], 1, n), dtype=torch.float32,
+                                                          device=dev)) for sh in shards]
+        host_out = [(torch.empty(o.shape, dtype=o.dtype).pin_memory(), torch.empty(l.shape, dtype=l.dtype).pin_memory())
+                    for o, l in dev_out]
+        h2d = sum(t.numel() * t.element_size() for hs in host_in for t in hs)
+        d2h = sum(t.numel() * t.element_size() for ho in host_out for t in ho)
+
+        def step():
+            for hs, ds, do, ho in zip(host_in, dev_in, dev_out, host_out):
+                for src, dst in zip(hs, ds):
+                    dst.copy_(src, non_blocking=True)
+                tk.dispatch_micro(ds[0], ds[1], ds[2], do[0], do[1], causal=causal, stream=stream.cuda_stream)
+                ho[0].copy_(do[0], non_blocking=True)
+                ho[1].copy_(do[1], non_blocking=True)
+
+        path = "pinned host -> H2D -> tk_kernel.dispatch_micro -> D2H (O and L)"
+    else:
+        q, kp, vp, bt, cl, ws = dec
+        # decode step inputs: the new query token, block table and lengths; the KV pool is state that
+        # lives on the device between steps, as in a serving loop
+        host_in = [t.cpu().pin_memory() for t in (q, bt, cl)]
+        dev_in = [q, bt, cl]
+        o = torch.empty_like(q)
+        l = torch.empty((b, h, 1, 1), dtype=torch.float32, device=dev)
+        host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory(), torch.empty(l.shape, dtype=l.dtype).pin_memory()]
+        h2d = sum(t.numel() * t.element_size() for t in host_in)
+        d2h = sum(t.numel() * t.element_size() for t in host_out)
+
+        def step():
+            for src, dst in zip(host_in, dev_in):
+                dst.copy_(src, non_blocking=True)
+            tk.dispatch_paged_decode(q, kp, vp, bt, cl, o, l, ws, stream=stream.cuda_stream)
+            host_out[0].copy_(o, non_blocking=True)
+            host_out[1].copy_(l, non_blocking=True)
+
+        path = "pinned host (q, block table, lengths) -> H2D -> tk_kernel.dispatch_paged_decode -> D2H (O and L)"
+    for _ in range(2):
+        step()
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    barrier()
+    return {"ms_total": e0.elapsed_time(e1), "steps": steps, "h2d": h2d, "d2h": d2h, "path": path}
+
+
+def cpu_baseline(kind, b, n, h, hkv, d, causal, budget_s):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    if kind == "fwd":
+        flops, dt, units = cpu_prefill_sample(b, n, h, hkv, d, causal, budget_s, max_units=b * hkv)
+        return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                "sample": f"{units} of {b * hkv} (batch, kv-head) units of the workload shape, {dt:.1f} s, "
+                          "oracle (fp32 PyTorch restatement of the reference math path)"}
+    toks, _ctx, dt, reps = cpu_decode_sample(budget_s)
+    return {"value": toks / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": f"{reps} passes over 8 sequences with ctx ~ U{{512..8192}}, {dt:.1f} s, paged oracle"}
+
+
+def run_reference_arm(args, rank, world, kind, b, n, h, hkv, d, causal) -> int:
+    """The reference's CPU implementation of the path (the oracle port: the reference's HIP kernels cannot be
+    built or run here) on the host cores. Rank 0 only."""
+    if rank != 0:
+        return 0
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    total_steps = args.warmup + args.steps
+    per_step_budget = max(0.2, min(3.0, 150.0 / total_steps))
+    times, work = [], []
+    for i in range(total_steps):
+        if kind == "fwd":
+            flops, dt, units = cpu_prefill_sample(b, n, h, hkv, d, causal, per_step_budget, max_units=b * hkv)
+            if i >= args.warmup:
+                times.append(dt)
+                work.append(flops)
+        else:
+            toks, _ctx, dt, _reps = cpu_decode_sample(per_step_budget)
+            if i >= args.warmup:
+                times.append(dt)
+                work.append(toks)
+    total_t, total_w = sum(times), sum(work)
+    if kind == "fwd":
+        value, unit = total_w / total_t / 1e12, "TFLOP/s"
+        metric = "bf16 GQA attn-fwd TFLOPS (4*B*N^2*H*D, /2 causal)"
+        sample = (f"each step: as many (batch, kv-head) units of the workload shape as fit in {per_step_budget:.1f} s "
+                  f"(of {b * hkv} per full pass)")
+        config = {"workload": args.workload, "B": b, "N": n, "H": h, "H_KV": hkv, "D": d, "causal": causal}
+    else:
+        value, unit = total_w / total_t, "tokens/s"
+        metric = "paged-KV GQA decode tokens/s"
+        sample = f"each step: passes over 8 sequences with ctx ~ U{{512..8192}} for {per_step_budget:.1f} s"
+        config = {"workload": args.workload, "S": b, "H": h, "H_KV": hkv, "D": d, "page": 16}
+    line = {
+        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": total_t / max(len(times), 1) * 1e3, "higher_is_better": True,
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+        "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

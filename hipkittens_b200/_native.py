@@ -8,6 +8,7 @@ import ctypes
 import importlib.util
 import math
 import os
+import sys
 import sysconfig
 from typing import Optional, Tuple
 
@@ -16,7 +17,7 @@ import torch
 _PKG = os.path.dirname(os.path.abspath(__file__))
 _LIB = os.path.join(_PKG, "lib", "libhk_attn.so")
 
-HK_OK, HK_EINVAL, HK_EUNSUPPORTED, HK_ECUDA, HK_ETIMEOUT, HK_EWORKSPACE = 0, -1, -2, -3, -4, -5
+HK_OK, HK_EINVAL, HK_EUNSUPPORTED, HK_ECUDA, HK_ETIMEOUT, HK_EWORKSPACE, HK_EBADPAGE = 0, -1, -2, -3, -4, -5, -6
 
 # Every symbol declared in include/hk_attn.h.
 EXPORTED_SYMBOLS = (
@@ -24,6 +25,7 @@ EXPORTED_SYMBOLS = (
     "hk_attn_paged_decode_workspace_bytes",
     "hk_attn_paged_decode",
     "hk_last_device_status",
+    "hk_selftest_bounded_wait",
     "hk_kernel_launch_count",
     "hk_strerror",
     "hk_last_cuda_error",
@@ -69,6 +71,8 @@ def capi() -> ctypes.CDLL:
     lib.hk_attn_paged_decode.restype = ci
     lib.hk_last_device_status.argtypes = [ci]
     lib.hk_last_device_status.restype = ci
+    lib.hk_selftest_bounded_wait.argtypes = [ci, ctypes.c_uint]
+    lib.hk_selftest_bounded_wait.restype = ci
     lib.hk_kernel_launch_count.argtypes = []
     lib.hk_kernel_launch_count.restype = ctypes.c_ulonglong
     lib.hk_strerror.argtypes = [ci]
@@ -203,9 +207,15 @@ def _load_ext(subdir: str, module: str):
     path = os.path.join(_PKG, subdir, module + sysconfig.get_config_var("EXT_SUFFIX"))
     if not os.path.exists(path):
         raise ImportError(f"{path} is missing: build it with `python -m hipkittens_b200._build`")
-    spec = importlib.util.spec_from_file_location(module, path)
+    # The dotted name keeps the two same-named builds (causal / non-causal) apart inside one process;
+    # from its own directory each is still importable as plain `tk_kernel`, as in the reference.
+    full = "hipkittens_b200." + subdir.replace("/", ".") + "." + module
+    if full in sys.modules:
+        return sys.modules[full]
+    spec = importlib.util.spec_from_file_location(full, path)
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
+    sys.modules[full] = mod
     return mod
 
 

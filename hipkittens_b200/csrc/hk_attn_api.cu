@@ -60,7 +60,7 @@ int prepare_fwd_kernel() {
   HK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, hk::FwdSmem<D>::kDynBytes));
   cudaFuncAttributes attr;
   HK_CUDA(cudaFuncGetAttributes(&attr, fn));
-  // The kernel re-balances registers between warpgroups (232/232/40 per thread); that only adds up if
+  // The kernel re-balances registers between warpgroups (208/208/88 per thread); that only adds up if
   // it was compiled to exactly 168 registers per thread at launch. Refuse to launch otherwise: a
   // register pool that is too small would block the re-allocation forever.
   if (attr.numRegs != 168) {
@@ -127,6 +127,19 @@ int make_bnhd_map(CUtensorMap* map, const void* base, int B, int N, int heads, i
     return HK_ECUDA;
   }
   return HK_OK;
+}
+
+__global__ void bounded_wait_selftest_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    hk::ptx::mbar_init(&bar, 1);
+    hk::ptx::fence_mbar_init();
+  }
+  __syncthreads();
+  const bool ok = hk::ptx::mbar_wait(&bar, 0, &abort_flag, limit_ns);  // nobody ever arrives
+  if (!ok && threadIdx.x == 0) atomicCAS(status, hk::kStatusOk, hk::kStatusTimeout);
 }
 
 template <int D, bool CAUSAL>
@@ -233,7 +246,19 @@ int hk_last_device_status(int device) {
   int word = 0;
   HK_CUDA(cudaMemcpy(&word, st->status, sizeof(int), cudaMemcpyDeviceToHost));
   if (word != 0) HK_CUDA(cudaMemset(st->status, 0, sizeof(int)));
-  return word == hk::kStatusOk ? HK_OK : HK_ETIMEOUT;
+  if (word == hk::kStatusOk) return HK_OK;
+  return word == hk::kStatusBadPage ? HK_EBADPAGE : HK_ETIMEOUT;
+}
+
+int hk_selftest_bounded_wait(int device, unsigned limit_us) {
+  DeviceState* st = nullptr;
+  int rc = use_device(device, &st);
+  if (rc != HK_OK) return rc;
+  if (limit_us == 0 || limit_us > 1000000u) return HK_EINVAL;
+  bounded_wait_selftest_kernel<<<1, 32>>>(st->status, static_cast<unsigned long long>(limit_us) * 1000ull);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  HK_CUDA(cudaGetLastError());
+  return hk_last_device_status(device);
 }
 
 unsigned long long hk_kernel_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
@@ -246,6 +271,7 @@ const char* hk_strerror(int code) {
     case HK_ECUDA: return "CUDA call failed";
     case HK_ETIMEOUT: return "bounded device-side wait expired";
     case HK_EWORKSPACE: return "workspace missing, misaligned or too small";
+    case HK_EBADPAGE: return "block-table entry outside the page pool";
     default: return "unknown error code";
   }
 }

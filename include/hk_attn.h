@@ -21,6 +21,7 @@ extern "C" {
 #define HK_ECUDA (-3)        /* a CUDA runtime or driver call failed; see hk_last_cuda_error() */
 #define HK_ETIMEOUT (-4)     /* a bounded device-side wait expired; results are invalid */
 #define HK_EWORKSPACE (-5)   /* workspace missing or too small */
+#define HK_EBADPAGE (-6)     /* a block-table entry outside [0, num_pages) was met; it was not dereferenced */
 
 /* Attention forward.
  * Replaces dispatch_micro<D>(attn_globals<D>) (kernels/attn/gqa/kernel.cpp:93-100,576-581, causal twin
@@ -51,10 +52,16 @@ int hk_attn_paged_decode(const void* q, const void* k_pages, const void* v_pages
                          float softmax_scale, void* workspace, size_t workspace_bytes,
                          int device, void* cuda_stream);
 
-/* Synchronises `device` and reports the device-side status word of the kernels above:
- * HK_OK, or HK_ETIMEOUT when a bounded wait inside a kernel expired. The word is cleared on read.
+/* Synchronises `device` and reports the device-side status word of the kernels above: HK_OK,
+ * HK_ETIMEOUT when a bounded wait inside a kernel expired, or HK_EBADPAGE. The word is cleared on read.
  * The reference launchers check nothing after launch (include/pyutils/util.cuh:6-16). */
 int hk_last_device_status(int device);
+
+/* Self-test of the bounded-wait path: launches a one-warp kernel that waits on a barrier nobody ever
+ * signals, with a time limit of `limit_us` microseconds, then synchronises. Returns HK_ETIMEOUT when the
+ * wait gave up as designed (the expected result) and leaves the context usable. Has no counterpart in the
+ * reference, whose kernels have no bounded waits. */
+int hk_selftest_bounded_wait(int device, unsigned limit_us);
 
 /* Number of kernels this library has launched in the calling process (all devices). */
 unsigned long long hk_kernel_launch_count(void);

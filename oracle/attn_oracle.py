@@ -37,6 +37,8 @@ from typing import Optional, Tuple
 
 import torch
 
+from hipkittens_b200.synthetic import make_paged_inputs, make_prefill_inputs  # noqa: F401  (re-exported for tests)
+
 __all__ = [
     "attn_fwd_oracle",
     "paged_decode_oracle",
@@ -125,61 +127,6 @@ def paged_decode_oracle(
             out[si, :, kh * g:(kh + 1) * g, :] = o_u.to(torch.bfloat16)
             lse[si, kh * g:(kh + 1) * g, 0, :] = l_u
     return out, lse
-
-
-def make_prefill_inputs(b: int, n: int, h: int, hkv: int, d: int, seed: int = 0):
-    """bf16 i.i.d. N(0,1) q, k, v drawn on the CPU in that order from one seed.
-
-    This is the reference harness's distribution (``kernels/attn/gqa/test_python.py:30-32``); drawing on
-    the CPU lets the oracle and the GPU see identical bits.
-    """
-    gen = torch.Generator().manual_seed(seed)
-    q = torch.randn((b, n, h, d), generator=gen, dtype=torch.float32).to(torch.bfloat16)
-    k = torch.randn((b, n, hkv, d), generator=gen, dtype=torch.float32).to(torch.bfloat16)
-    v = torch.randn((b, n, hkv, d), generator=gen, dtype=torch.float32).to(torch.bfloat16)
-    return q, k, v
-
-
-def make_paged_inputs(
-    n_seq: int,
-    h: int,
-    hkv: int,
-    d: int,
-    page: int,
-    num_pages: int,
-    ctx_lo: int,
-    ctx_hi: int,
-    seed: int = 0,
-    pool_on: Optional[str] = None,
-):
-    """Synthetic paged-KV decode problem.
-
-    Context lengths are uniform integers in [ctx_lo, ctx_hi]; every sequence's block table is a slice
-    of one seeded permutation of page ids, so ids are distinct across the whole batch. The K/V pools
-    are bf16 N(0,1). ``pool_on`` may name a device on which to draw the (large) pools directly.
-    """
-    gen = torch.Generator().manual_seed(seed)
-    ctx = torch.randint(ctx_lo, ctx_hi + 1, (n_seq,), generator=gen, dtype=torch.int32)
-    npg = (ctx + page - 1) // page
-    total = int(npg.sum())
-    assert total <= num_pages, "page pool too small for the drawn context lengths"
-    perm = torch.randperm(num_pages, generator=gen, dtype=torch.int64)[:total].to(torch.int32)
-    max_pages = int(npg.max())
-    table = torch.zeros((n_seq, max_pages), dtype=torch.int32)
-    off = 0
-    for s in range(n_seq):
-        c = int(npg[s])
-        table[s, :c] = perm[off:off + c]
-        off += c
-    q = torch.randn((n_seq, 1, h, d), generator=gen, dtype=torch.float32).to(torch.bfloat16)
-    if pool_on is None:
-        kp = torch.randn((num_pages, page, hkv, d), generator=gen, dtype=torch.float32).to(torch.bfloat16)
-        vp = torch.randn((num_pages, page, hkv, d), generator=gen, dtype=torch.float32).to(torch.bfloat16)
-    else:
-        dgen = torch.Generator(device=pool_on).manual_seed(seed + 1)
-        kp = torch.randn((num_pages, page, hkv, d), generator=dgen, dtype=torch.bfloat16, device=pool_on)
-        vp = torch.randn((num_pages, page, hkv, d), generator=dgen, dtype=torch.bfloat16, device=pool_on)
-    return q, kp, vp, table, ctx
 
 
 def robustness_check(ref: torch.Tensor, pred: torch.Tensor):

@@ -1,0 +1,245 @@
+"""GPU parity of the attention forward against the CPU oracle, through the C ABI and the reference's Python
+entry points. Tolerances are the build's: max-abs 2e-2 on O, 1e-3 on L."""
+import glob
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import hipkittens_b200 as hk
+from hipkittens_b200 import _native
+from hipkittens_b200.synthetic import make_prefill_inputs
+from oracle.attn_oracle import attn_fwd_oracle, robustness_check
+
+pytestmark = pytest.mark.gpu
+TOL_O, TOL_L = 2e-2, 1e-3
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "case_*.npz")))
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "these tests need a B200"
+    return torch.device("cuda:0")
+
+
+def run_fwd(q, k, v, causal, dev, scale=None):
+    """Poison the outputs with NaN first so rows the kernel failed to write are caught."""
+    b, n, h, d = q.shape
+    o = torch.full((b, n, h, d), float("nan"), dtype=torch.bfloat16, device=dev)
+    l = torch.full((b, h, 1, n), float("nan"), dtype=torch.float32, device=dev)
+    hk.attn_fwd(q.to(dev), k.to(dev), v.to(dev), causal=causal, softmax_scale=scale, out=o, lse=l)
+    assert _native.device_status(0) == 0
+    return o.cpu(), l.cpu()
+
+
+def assert_parity(o, l, o_ref, l_ref):
+    assert not torch.isnan(o.float()).any() and not torch.isnan(l).any()
+    eo = float((o.float() - o_ref.float()).abs().max())
+    el = float((l - l_ref).abs().max())
+    assert eo <= TOL_O, f"max|dO| = {eo}"
+    assert el <= TOL_L, f"max|dL| = {el}"
+
+
+SMALL = [
+    # B, N, H, H_KV, D, causal
+    (1, 256, 8, 2, 64, False),     # BASELINE config 1
+    (1, 128, 2, 1, 128, False),    # one tile per slot
+    (1, 128, 1, 1, 128, True),     # a single tile: second slot unused
+    (2, 384, 4, 2, 128, True),     # head-paired slots, odd q-block count
+    (1, 512, 2, 2, 128, True),     # MHA causal: q-block pairs of unequal length
+    (1, 384, 3, 3, 64, False),     # odd group size and odd q-block count
+    (2, 256, 8, 8, 64, True),      # MHA, D=64, causal
+    (1, 1024, 16, 2, 128, False),  # group of 8
+    (3, 256, 12, 4, 64, False),    # group of 3 (q-block pairing under GQA)
+]
+
+
+@pytest.mark.parametrize("b,n,h,hkv,d,causal", SMALL)
+def test_parity_small(dev, b, n, h, hkv, d, causal):
+    q, k, v = make_prefill_inputs(b, n, h, hkv, d, seed=b * 1000 + n + h)
+    o, l = run_fwd(q, k, v, causal, dev)
+    o_ref, l_ref = attn_fwd_oracle(q, k, v, causal)
+    assert_parity(o, l, o_ref, l_ref)
+    # the reference harness's own statistic: no element beyond 0.001 + 0.05|ref| ... for L; O within a few
+    _max_abs, err, numel, _l2, cos = robustness_check(l_ref, l)
+    assert err == 0 and cos > 0.99999
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
+def test_parity_against_reference_module_outputs(dev, path):
+    """Directly against the committed outputs of the reference's PyTorch module (fp32 run)."""
+    z = np.load(path)
+    b, n, h, hkv, d, causal, _ = [int(x) for x in z["shape"]]
+    bits = lambda a: torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16)  # noqa: E731
+    q, k, v = bits(z["q"]), bits(z["k"]), bits(z["v"])
+    o, l = run_fwd(q, k, v, bool(causal), dev)
+    assert float((o.float() - torch.from_numpy(z["o_ref_fp32"])).abs().max()) <= TOL_O
+    assert float((l[:, :, 0, :] - torch.from_numpy(z["lse_def_fp64"]).float()).abs().max()) <= TOL_L
+
+
+def test_through_reference_entry_points(dev):
+    """tk_kernel.dispatch_micro and tk_kernel_fwd.dispatch_fwd, called as the reference's harness and
+    training code call them (kernels/attn/gqa/test_python.py:97-102, hipkittens.py:43-51)."""
+    q, k, v = make_prefill_inputs(2, 256, 8, 2, 128, seed=11)
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+    for causal in (False, True):
+        o_ref, l_ref = attn_fwd_oracle(q, k, v, causal)
+        tk = hk.load_tk_kernel(causal)
+        out = torch.zeros(2, 256, 8, 128, dtype=torch.bfloat16, device=dev, requires_grad=True)
+        lse = torch.zeros(2, 8, 1, 256, dtype=torch.float32, device=dev, requires_grad=True)
+        tk.dispatch_micro(qd, kd, vd, out, lse)
+        torch.cuda.synchronize()
+        assert_parity(out.detach().cpu(), lse.detach().cpu(), o_ref, l_ref)
+        fwd = hk.load_tk_kernel_fwd(causal)
+        O = torch.empty(2, 256, 8, 128, dtype=torch.bfloat16, device=dev)
+        L = torch.empty(2, 8, 1, 256, dtype=torch.float32, device=dev)
+        fwd.dispatch_fwd(qd, kd, vd, O, L)  # blocking, like the reference's
+        assert_parity(O.cpu(), L.cpu(), o_ref, l_ref)
+
+
+def test_autograd_function_forward(dev):
+    from hipkittens_b200.attention import HipCrossAttention, HipSelfAttention
+
+    q, k, v = make_prefill_inputs(1, 256, 4, 4, 64, seed=12)
+    qkv = torch.stack([q, k, v], dim=2).to(dev)
+    out = HipSelfAttention(causal=True)(qkv)
+    o_ref, _ = attn_fwd_oracle(q, k, v, True)
+    assert out.dtype == torch.bfloat16 and float((out.float().cpu() - o_ref.float()).abs().max()) <= TOL_O
+    q, k, v = make_prefill_inputs(1, 256, 8, 2, 64, seed=13)
+    out = HipCrossAttention(causal=False)(q.to(dev), torch.stack([k, v], dim=2).to(dev))
+    o_ref, _ = attn_fwd_oracle(q, k, v, False)
+    assert float((out.float().cpu() - o_ref.float()).abs().max()) <= TOL_O
+
+
+def test_custom_softmax_scale(dev):
+    q, k, v = make_prefill_inputs(1, 256, 2, 1, 128, seed=14)
+    o, l = run_fwd(q, k, v, False, dev, scale=0.05)
+    o_ref, l_ref = attn_fwd_oracle(q, k, v, False, softmax_scale=0.05)
+    assert_parity(o, l, o_ref, l_ref)
+
+
+def test_adversarial_numerics(dev):
+    q, k, v = make_prefill_inputs(1, 512, 2, 1, 128, seed=15)
+    # (a) one huge logit per row late in the sequence: the running max jumps, forcing the rescale path
+    k2 = k.clone()
+    k2[0, 400] = (q[0, 100, 0].float() * 4).to(torch.bfloat16)
+    o, l = run_fwd(q, k2, v, False, dev)
+    assert_parity(o, l, *attn_fwd_oracle(q, k2, v, False))
+    # (b) logits that keep growing tile after tile (max rises by more than the lazy threshold each tile)
+    kg = (k.float() * torch.linspace(0.2, 6.0, 512).view(1, 512, 1, 1)).to(torch.bfloat16)
+    o, l = run_fwd(q, kg, v, False, dev)
+    assert_parity(o, l, *attn_fwd_oracle(q, kg, v, False))
+    # (c) all-equal logits: uniform softmax, L = ln N
+    qz = torch.zeros_like(q)
+    o, l = run_fwd(qz, k, v, False, dev)
+    assert float((l - math.log(512)).abs().max()) <= 1e-5
+    assert_parity(o, l, *attn_fwd_oracle(qz, k, v, False))
+    # (d) causal first row sees exactly one key: O = V[0], L = its logit
+    o, l = run_fwd(q, k, v, True, dev)
+    assert torch.equal(o[0, 0, 0], v[0, 0, 0])
+    assert_parity(o, l, *attn_fwd_oracle(q, k, v, True))
+    # (e) large-magnitude logits (|s| of several hundred) stay finite
+    qb = (q.float() * 30).to(torch.bfloat16)
+    o, l = run_fwd(qb, k, v, False, dev)
+    assert torch.isfinite(o.float()).all() and torch.isfinite(l).all()
+    o_ref, l_ref = attn_fwd_oracle(qb, k, v, False)
+    assert float((o.float() - o_ref.float()).abs().max()) <= TOL_O
+    assert float(((l - l_ref).abs() / l_ref.abs().clamp_min(1)).max()) <= 1e-5
+
+
+def test_bitwise_deterministic_and_gqa_equals_mha(dev):
+    q, k, v = make_prefill_inputs(2, 512, 8, 2, 128, seed=16)
+    o1, l1 = run_fwd(q, k, v, True, dev)
+    o2, l2 = run_fwd(q, k, v, True, dev)
+    assert torch.equal(o1, o2) and torch.equal(l1, l2)
+    o3, l3 = run_fwd(q, k.repeat_interleave(4, dim=2), v.repeat_interleave(4, dim=2), True, dev)
+    assert torch.equal(o1, o3) and torch.equal(l1, l3)
+
+
+def _gpu_fp32_unit(q, k, v, causal):
+    """fp32 restatement on the GPU for one (batch, kv-head) unit of a full-size shape (the CPU oracle on
+    the whole tensor would take minutes); used only next to CPU-oracle spot checks."""
+    n = q.shape[0]
+    s = torch.einsum("tgd,sd->gts", q.float(), k.float()) / math.sqrt(q.shape[-1])
+    if causal:
+        s = s.masked_fill(torch.triu(torch.ones(n, n, dtype=torch.bool, device=q.device), 1), float("-inf"))
+    lse = torch.logsumexp(s, -1)
+    return torch.einsum("gts,sd->tgd", torch.exp(s - lse[..., None]), v.float()).to(torch.bfloat16), lse
+
+
+FULL = [
+    (16, 2048, 64, 8, 128, False),  # BASELINE config 2
+    (4, 8192, 64, 8, 128, True),    # config 3
+    (16, 4096, 16, 16, 64, False),  # config 4
+]
+
+
+@pytest.mark.parametrize("b,n,h,hkv,d,causal", FULL)
+def test_full_size_configs(dev, b, n, h, hkv, d, causal):
+    g = h // hkv
+    q, k, v = make_prefill_inputs(b, n, h, hkv, d, seed=0)
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    o = torch.full_like(qd, float("nan"))
+    l = torch.full((b, h, 1, n), float("nan"), dtype=torch.float32, device=dev)
+    hk.attn_fwd(qd, kd, vd, causal=causal, out=o, lse=l)
+    assert _native.device_status(0) == 0
+    assert not torch.isnan(o.float()).any() and not torch.isnan(l).any()
+    # (1) CPU oracle on the first and last (batch, kv-head) unit, a row band of the queries for long N
+    for bi, kh in ((0, 0), (b - 1, hkv - 1)):
+        rows = slice(0, n) if n <= 2048 else slice(n - 512, n)
+        qs = q[bi:bi + 1, :, kh * g:(kh + 1) * g]
+        o_ref, l_ref = _band_oracle(qs, k[bi:bi + 1, :, kh:kh + 1], v[bi:bi + 1, :, kh:kh + 1], causal, rows)
+        eo = float((o[bi, rows, kh * g:(kh + 1) * g].float().cpu() - o_ref[0].float()).abs().max())
+        el = float((l[bi, kh * g:(kh + 1) * g, 0, rows].cpu() - l_ref[0, :, 0]).abs().max())
+        assert eo <= TOL_O and el <= TOL_L, (bi, kh, eo, el)
+    # (2) every unit against the fp32 restatement evaluated on the GPU
+    worst_o = worst_l = 0.0
+    for bi in range(b):
+        for kh in range(hkv):
+            o_ref, l_ref = _gpu_fp32_unit(qd[bi, :, kh * g:(kh + 1) * g], kd[bi, :, kh], vd[bi, :, kh], causal)
+            worst_o = max(worst_o, float((o[bi, :, kh * g:(kh + 1) * g].float() - o_ref.float()).abs().max()))
+            worst_l = max(worst_l, float((l[bi, kh * g:(kh + 1) * g, 0] - l_ref).abs().max()))
+            del o_ref, l_ref
+    assert worst_o <= TOL_O and worst_l <= TOL_L, (worst_o, worst_l)
+    # (3) size-independent properties: scaling V by 2 doubles O exactly and leaves L unchanged
+    o2 = torch.empty_like(o)
+    l2 = torch.empty_like(l)
+    hk.attn_fwd(qd, kd, (vd.float() * 2).to(torch.bfloat16), causal=causal, out=o2, lse=l2)
+    assert torch.equal(o2.float(), o.float() * 2) and torch.equal(l2, l)
+
+
+def _band_oracle(q, k, v, causal, rows):
+    """CPU oracle for a band of query rows of one unit (keeps the score matrix small for N = 8192)."""
+    n = q.shape[1]
+    qb = q[:, rows]
+    nb = qb.shape[1]
+    g = q.shape[2]
+    scale = 1.0 / math.sqrt(q.shape[-1])
+    s = torch.einsum("tgd,sd->gts", qb[0].float(), k[0, :, 0].float() * scale)
+    if causal:
+        row = torch.arange(rows.start, rows.stop).view(nb, 1)
+        col = torch.arange(n).view(1, n)
+        s = s.masked_fill((col > row).unsqueeze(0), float("-inf"))
+    lse = torch.logsumexp(s, -1)
+    o = torch.einsum("gts,sd->tgd", torch.exp(s - lse[..., None]), v[0, :, 0].float())
+    return o.to(torch.bfloat16)[None], lse[None, :, None, :].reshape(1, g, 1, nb)
+
+
+def test_causal_prefix_property(dev):
+    """Causal attention on the first half of a sequence equals the first half of causal attention on the
+    whole sequence, bit for bit (same tiles, same order of accumulation)."""
+    q, k, v = make_prefill_inputs(1, 2048, 8, 2, 128, seed=17)
+    o_full, l_full = run_fwd(q, k, v, True, dev)
+    o_half, l_half = run_fwd(q[:, :1024].contiguous(), k[:, :1024].contiguous(), v[:, :1024].contiguous(), True, dev)
+    assert torch.equal(o_full[:, :1024], o_half) and torch.equal(l_full[..., :1024], l_half)
+
+
+def test_bounded_wait_reports_timeout_and_context_survives(dev):
+    lib = hk.capi()
+    assert lib.hk_selftest_bounded_wait(0, 2000) == _native.HK_ETIMEOUT
+    assert lib.hk_last_device_status(0) == 0  # cleared on read
+    q, k, v = make_prefill_inputs(1, 128, 2, 1, 64, seed=18)
+    o, l = run_fwd(q, k, v, False, dev)
+    assert_parity(o, l, *attn_fwd_oracle(q, k, v, False))
