@@ -37,16 +37,23 @@ WORKLOADS = {
     "gqa_causal_fwd_b4_n8192_h64_kv8_d128": ("fwd", 4, 8192, 64, 8, 128, True),
     "mha_fwd_b16_n4096_h16_d64": ("fwd", 16, 4096, 16, 16, 64, False),
     "paged_decode_s64_ctx512_8192_h64_kv8_d128": ("decode", 64, 0, 64, 8, 128, False),
+    # reduced copies of the above for ncu captures (same kernels and tile shapes, inputs still beyond L2)
+    "profile_gqa_fwd_b4_n2048_h64_kv8_d128": ("fwd", 4, 2048, 64, 8, 128, False),
+    "profile_paged_decode_s14_ctx512_8192_h64_kv8_d128": ("decode", 14, 0, 64, 8, 128, False),
 }
+DECODE_POOL_PAGES = {"paged_decode_s64_ctx512_8192_h64_kv8_d128": 40000,
+                     "profile_paged_decode_s14_ctx512_8192_h64_kv8_d128": 8000}
 DEFAULT_WORKLOAD = "gqa_fwd_b16_n2048_h64_kv8_d128"
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None = not captured for that workload).
 NCU_TRAFFIC_BYTES = {
-    "gqa_fwd_b16_n2048_h64_kv8_d128": None,
+    # 4 x the B=4 capture (260.2 MB per launch; traffic grows with the (batch, kv-head) units)
+    "gqa_fwd_b16_n2048_h64_kv8_d128": 4 * 260.2e6,
     "gqa_causal_fwd_b4_n8192_h64_kv8_d128": None,
     "mha_fwd_b16_n4096_h16_d64": None,
-    "paged_decode_s64_ctx512_8192_h64_kv8_d128": None,
+    # 14-sequence capture (280.26 MB for sum ctx 66 608) scaled by sum ctx to 275 479; split + combine
+    "paged_decode_s64_ctx512_8192_h64_kv8_d128": (280.26e6 + 4.64e6) * 275479 / 66608,
 }
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -247,7 +254,8 @@ def main() -> int:
 
         in_bytes = sum(t.numel() * 2 for sh in shards for t in sh)
     else:
-        q, kp, vp, bt, cl = make_paged_inputs(b, h, hkv, d, 16, 40000, 512, 8192, seed=rank, pool_on=str(dev))
+        q, kp, vp, bt, cl = make_paged_inputs(b, h, hkv, d, 16, DECODE_POOL_PAGES[args.workload], 512, 8192, seed=rank,
+                                               pool_on=str(dev))
         q, bt, cl = q.to(dev), bt.to(dev), cl.to(dev)
         ws = torch.empty(hk.paged_decode_workspace_bytes(b, h, d, bt.shape[1]), dtype=torch.uint8, device=dev)
         o = torch.empty_like(q)
@@ -336,7 +344,7 @@ def main() -> int:
             line.update({
                 "metric": "paged-KV GQA decode tokens/s", "value": tok_s, "unit": "tokens/s", "dtype": "bf16",
                 "config": {"workload": args.workload, "S": b, "H": h, "H_KV": hkv, "D": d, "page": 16,
-                           "pool_pages": 40000, "ctx": "U{512..8192}", "sum_ctx": sum_ctx,
+                           "pool_pages": DECODE_POOL_PAGES[args.workload], "ctx": "U{512..8192}", "sum_ctx": sum_ctx,
                            "cache": "inputs_exceed_l2"},
                 "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                              "frac": ach / peaks["hbm_gbs"], "peak_kind": f"of {peaks_src} (copy)",
