@@ -24,6 +24,7 @@ EXPORTED_SYMBOLS = (
     "hk_attn_fwd",
     "hk_attn_paged_decode_workspace_bytes",
     "hk_attn_paged_decode",
+    "hk_attn_paged_decode_static",
     "hk_last_device_status",
     "hk_selftest_bounded_wait",
     "hk_kernel_launch_count",
@@ -69,6 +70,9 @@ def capi() -> ctypes.CDLL:
     lib.hk_attn_paged_decode.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cf, vp,
                                          ctypes.c_size_t, ci, vp]
     lib.hk_attn_paged_decode.restype = ci
+    lib.hk_attn_paged_decode_static.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cf, ci, vp,
+                                                ctypes.POINTER(ci)]
+    lib.hk_attn_paged_decode_static.restype = ci
     lib.hk_last_device_status.argtypes = [ci]
     lib.hk_last_device_status.restype = ci
     lib.hk_selftest_bounded_wait.argtypes = [ci, ctypes.c_uint]

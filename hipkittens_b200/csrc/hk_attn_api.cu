@@ -279,3 +279,104 @@ const char* hk_strerror(int code) {
 const char* hk_last_cuda_error(void) { return g_cuda_err; }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free paged decode: scratch and status live in the library image instead of in memory the
+// caller or this library would have to allocate (see hk_attn_paged_decode_static in hk_attn.h).
+// In host code `g_decode_static_scratch` is only a handle for the runtime, not a device address; the
+// address each device gave the array is looked up once per device with cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_decode_static_scratch[HK_DECODE_STATIC_SCRATCH_BYTES];
+static __device__ int g_decode_static_status;
+
+namespace {
+
+struct StaticDecodeState {
+  std::once_flag once;
+  int init_rc = HK_OK;
+  int sm_count = 0;
+  void* scratch = nullptr;  // device address of g_decode_static_scratch on this device
+  int* status = nullptr;    // device address of g_decode_static_status on this device
+};
+StaticDecodeState g_static_dev[kMaxDevices];
+
+// Runs once per device, with that device current. Nothing in here allocates.
+int init_static_decode(int device) {
+  StaticDecodeState& st = g_static_dev[device];
+  cudaDeviceProp prop;
+  HK_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "device %d is sm_%d%d; this library needs sm_100", device, prop.major,
+             prop.minor);
+    return HK_EUNSUPPORTED;
+  }
+  st.sm_count = prop.multiProcessorCount;
+  HK_CUDA(cudaGetSymbolAddress(&st.scratch, g_decode_static_scratch));
+  HK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&st.status), g_decode_static_status));
+  if (!st.scratch || !st.status || (reinterpret_cast<uintptr_t>(st.scratch) & 255)) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "static decode scratch has no usable device address");
+    return HK_ECUDA;
+  }
+  return hk::prepare_decode_kernels(g_cuda_err, sizeof(g_cuda_err));
+}
+
+}  // namespace
+
+extern "C" int hk_attn_paged_decode_static(const void* q, const void* k_pages, const void* v_pages,
+                                           const int32_t* block_table, const int32_t* ctx_lens, void* o, float* lse,
+                                           int S, int H, int H_KV, int D, int page_size, int max_pages_per_seq,
+                                           int num_pages, float softmax_scale, int device, void* cuda_stream,
+                                           int* status_out) {
+  if (!q || !k_pages || !v_pages || !block_table || !ctx_lens || !o || !lse) return HK_EINVAL;
+  if (S <= 0 || H <= 0 || H_KV <= 0 || max_pages_per_seq <= 0 || num_pages <= 0) return HK_EINVAL;
+  if (D != 128 || page_size != 16) return HK_EUNSUPPORTED;
+  if (H % H_KV != 0) return HK_EINVAL;
+  const int G = H / H_KV;
+  if (G != 1 && G != 2 && G != 4 && G != 8) return HK_EUNSUPPORTED;
+  if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(o)) return HK_EINVAL;
+  const size_t need = hk::decode_workspace_bytes(S, H, D, max_pages_per_seq, page_size);
+  if (need == 0 || need > HK_DECODE_STATIC_SCRATCH_BYTES) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err),
+             "problem needs %zu bytes of scratch, the built-in array holds %u: use hk_attn_paged_decode", need,
+             unsigned(HK_DECODE_STATIC_SCRATCH_BYTES));
+    return HK_EWORKSPACE;
+  }
+  if (device < 0) HK_CUDA(cudaGetDevice(&device));
+  if (device >= kMaxDevices) return HK_EINVAL;
+  HK_CUDA(cudaSetDevice(device));
+  StaticDecodeState& st = g_static_dev[device];
+  std::call_once(st.once, [&] { st.init_rc = init_static_decode(device); });
+  if (st.init_rc != HK_OK) return st.init_rc;
+
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  // the status word is shared by all calls and keeps the last call's value: start this call from zero
+  HK_CUDA(cudaMemsetAsync(st.status, 0, sizeof(int), stream));
+  hk::DecodeParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
+  p.v_pages = static_cast<const __nv_bfloat16*>(v_pages);
+  p.block_table = block_table;
+  p.ctx_lens = ctx_lens;
+  p.o = static_cast<__nv_bfloat16*>(o);
+  p.lse = lse;
+  p.S = S;
+  p.H = H;
+  p.H_KV = H_KV;
+  p.max_pages = max_pages_per_seq;
+  p.num_pages = num_pages;
+  p.scale = softmax_scale > 0.f ? softmax_scale : 1.0f / std::sqrt(float(D));
+  p.scale_log2 = p.scale * 1.4426950408889634f;
+  p.workspace = st.scratch;  // the looked-up device address, never the host-side symbol
+  p.status = st.status;
+  int launched = 0;
+  cudaError_t e = hk::launch_paged_decode(p, st.sm_count, stream, &launched);
+  g_launches.fetch_add(launched, std::memory_order_relaxed);
+  if (e != cudaSuccess) return cuda_fail(e, "paged decode launch");
+  if (status_out) {
+    int word = 0;
+    HK_CUDA(cudaMemcpyAsync(&word, st.status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    HK_CUDA(cudaStreamSynchronize(stream));
+    *status_out = (word == hk::kStatusOk) ? HK_OK : (word == hk::kStatusBadPage ? HK_EBADPAGE : HK_ETIMEOUT);
+  }
+  return HK_OK;
+}
+

@@ -52,6 +52,33 @@ int hk_attn_paged_decode(const void* q, const void* k_pages, const void* v_pages
                          float softmax_scale, void* workspace, size_t workspace_bytes,
                          int device, void* cuda_stream);
 
+/* Paged-KV decode for callers that cannot allocate device memory. No counterpart in the reference.
+ *
+ * Who needs it: a serving engine that hands all of HBM to its own block allocator at start-up leaves nothing
+ * for a plug-in to cudaMalloc, and a latency-critical decode loop cannot afford cudaMalloc's device-wide
+ * synchronisation. hk_attn_paged_decode() makes such callers bring a workspace (and its first call on a device
+ * allocates a status word); this variant brings its own: the per-chunk partial results live in a fixed
+ * HK_DECODE_STATIC_SCRATCH_BYTES array that is part of the library image, so every GPU that loads the library
+ * holds that much memory until the process exits, whether or not this function is ever called. It calls no
+ * cudaMalloc / cudaFree and no allocating library routine.
+ *
+ * Same arguments and results as hk_attn_paged_decode() minus the workspace, plus `status_out`:
+ *   status_out  HOST pointer or NULL. When given, the call waits for its own kernels on `cuda_stream` and stores
+ *               HK_OK or HK_EBADPAGE there; with NULL the call is asynchronous and the status is dropped.
+ * Limit: hk_attn_paged_decode_workspace_bytes(S, H, D, max_pages_per_seq, page_size) must not exceed
+ * HK_DECODE_STATIC_SCRATCH_BYTES (e.g. S=16, H=64 at up to 7680 tokens per sequence); larger problems are
+ * refused with HK_EWORKSPACE before anything is launched - use hk_attn_paged_decode() for them.
+ * The first call on each device looks up the device address of the array (one-time set-up, under a lock); make
+ * that first call before any stream capture begins.
+ * All calls on a device share the one array: it still holds the previous call's partials (every value a call
+ * reads it has written first, and the status word is cleared on the stream at the start of each call), and two
+ * calls whose kernels overlap on the GPU - different streams, or different host threads - race on it. Serialise them. */
+#define HK_DECODE_STATIC_SCRATCH_BYTES (8u << 20)
+int hk_attn_paged_decode_static(const void* q, const void* k_pages, const void* v_pages,
+                                const int32_t* block_table, const int32_t* ctx_lens, void* o, float* lse,
+                                int S, int H, int H_KV, int D, int page_size, int max_pages_per_seq, int num_pages,
+                                float softmax_scale, int device, void* cuda_stream, int* status_out);
+
 /* Synchronises `device` and reports the device-side status word of the kernels above: HK_OK,
  * HK_ETIMEOUT when a bounded wait inside a kernel expired, or HK_EBADPAGE. The word is cleared on read.
  * The reference launchers check nothing after launch (include/pyutils/util.cuh:6-16). */
