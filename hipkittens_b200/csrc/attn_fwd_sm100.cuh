@@ -37,6 +37,14 @@ constexpr int kBlockN = 128;        // keys per KV tile
 constexpr int kFwdThreads = 384;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThresholdLog2 = 8.0f;
+#ifndef HK_EMU_MOD
+#define HK_EMU_MOD 4
+#endif
+#ifndef HK_EMU_CNT
+#define HK_EMU_CNT 0
+#endif
+constexpr int kEmuMod = HK_EMU_MOD;   // of every kEmuMod column pairs ...
+constexpr int kEmuCnt = HK_EMU_CNT;   // ... this many compute exp2 with the polynomial instead of the MUFU
 constexpr uint64_t kWaitLimitNs = 4000ull * 1000 * 1000;  // 4 s: far beyond any legitimate wait
 
 // Device status codes written to FwdParams::status (0 = OK).
@@ -51,6 +59,9 @@ struct FwdParams {
   float scale;          // softmax scale
   float scale_log2;     // scale * log2(e)
   int* status;          // device word: first non-zero status wins
+#ifdef HK_TRACE
+  long long* trace;     // [3 roles][4096] clock stamps of CTA 0 (debug builds only)
+#endif
 };
 
 template <int D>
@@ -134,6 +145,25 @@ __device__ __forceinline__ int item_for_round(int round, int cta, int n_cta) {
   return round * n_cta + ((round & 1) ? (n_cta - 1 - cta) : cta);
 }
 
+#ifdef HK_TRACE
+// Phase stamps for tuning: CTA 0, one thread per role appends (event id, SM clock) pairs.
+#define HK_STAMP(role, ev)                                                            \
+  do {                                                                                \
+    if (blockIdx.x == 0 && trace_on && trace_n < 2040) {                              \
+      p.trace[(role) * 4096 + 2 * trace_n] = (ev);                                    \
+      p.trace[(role) * 4096 + 2 * trace_n + 1] = clock64();                           \
+      ++trace_n;                                                                      \
+    }                                                                                 \
+  } while (0)
+#else
+#define HK_STAMP(role, ev) do {} while (0)
+#endif
+#if defined(HK_TRACE) && HK_TRACE >= 2
+#define HK_STAMP2(role, ev) HK_STAMP(role, ev)
+#else
+#define HK_STAMP2(role, ev) do {} while (0)
+#endif
+
 template <int D, bool CAUSAL>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -195,6 +225,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const float c = p.scale_log2;
     uint32_t s_cnt = 0, o_cnt = 0;
     bool ok = true;
+#ifdef HK_TRACE
+    const bool trace_on = ((warp & 3) == 0) && lane == 0;
+    int trace_n = 0;
+#endif
     for (int round = 0; ok; ++round) {
       const int idx = item_for_round(round, blockIdx.x, gridDim.x);
       if (idx >= p.n_items) {
@@ -207,28 +241,41 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if (nkv == 0) continue;
       float m = 0.f, l = 0.f;
       for (int j = 0; j < nkv && ok; ++j) {
+        HK_STAMP2(slot, 0);
         ok = mbar_wait(&s_full[slot], s_cnt & 1, abortp, kWaitLimitNs);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         ++s_cnt;
         tc_fence_after();
+        HK_STAMP(slot, 1);
         uint32_t su[kBlockN];  // one row of S, fp32 bit patterns
 #define HK_S(i) __uint_as_float(su[(i)])
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) tmem_ld32(tS + cc * 32, su + cc * 32);
         tmem_wait_ld();
+        HK_STAMP2(slot, 2);
         if (CAUSAL && j == nkv - 1) {
           // diagonal tile: key (j*128 + col) is visible to query (qb*128 + row) iff col <= row
 #pragma unroll
           for (int i = 0; i < kBlockN; ++i) su[i] = (i > row) ? 0xff800000u : su[i];
         }
-        float bm0 = fmaxf(HK_S(0), HK_S(1)), bm1 = fmaxf(HK_S(2), HK_S(3));
+#if defined(HK_DEBUG_MINSOFTMAX)
+        // timing experiment only: the shortest possible softmax stage (load S, store something as P)
 #pragma unroll
-        for (int i = 4; i < kBlockN; i += 4) {
-          bm0 = fmaxf(bm0, fmaxf(HK_S(i), HK_S(i + 1)));
-          bm1 = fmaxf(bm1, fmaxf(HK_S(i + 2), HK_S(i + 3)));
+        for (int cc = 0; cc < 4; ++cc) tmem_st16(tS + cc * 16, su + cc * 32);
+        l += 1.0f;
+        if (false) {
+#endif
+        float bm0 = fmaxf(HK_S(0), HK_S(1)), bm1 = fmaxf(HK_S(2), HK_S(3));
+        float bm2 = fmaxf(HK_S(4), HK_S(5)), bm3 = fmaxf(HK_S(6), HK_S(7));
+#pragma unroll
+        for (int i = 8; i < kBlockN; i += 8) {
+          bm0 = max3(bm0, HK_S(i), HK_S(i + 1));
+          bm1 = max3(bm1, HK_S(i + 2), HK_S(i + 3));
+          bm2 = max3(bm2, HK_S(i + 4), HK_S(i + 5));
+          bm3 = max3(bm3, HK_S(i + 6), HK_S(i + 7));
         }
-        const float bm = fmaxf(bm0, bm1);
+        const float bm = fmaxf(fmaxf(bm0, bm2), fmaxf(bm1, bm3));
         if (j == 0) {
           m = bm;
         } else {
@@ -251,26 +298,57 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
           }
         }
-        const float mc = m * c;
-        float l0 = 0.f, l1 = 0.f;
+        // p = exp2(s*c - m*c), two columns per instruction where the hardware has packed fp32 forms.
+        // Of every kEmuMod column pairs, kEmuCnt compute exp2 on the FMA pipe (polynomial), the rest on
+        // the MUFU.
+        HK_STAMP2(slot, 3);
+        const uint64_t c2 = pack2(c, c);
+        const float nmc = -(m * c);
+        const uint64_t nmc2 = pack2(nmc, nmc);
+        uint64_t lacc0 = pack2(0.f, 0.f), lacc1 = pack2(0.f, 0.f);
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const float p0 = ex2_approx(fmaf(HK_S(cc * 32 + 2 * i), c, -mc));
-            const float p1 = ex2_approx(fmaf(HK_S(cc * 32 + 2 * i + 1), c, -mc));
-            l0 += p0;
-            l1 += p1;
+            const uint64_t x2 = fma2(pack2(HK_S(cc * 32 + 2 * i), HK_S(cc * 32 + 2 * i + 1)), c2, nmc2);
+            uint64_t p2;
+            float p0, p1;
+#if defined(HK_DEBUG_NOEXP)
+            p2 = x2;  // timing experiment only: no exponentials
+            unpack2(p2, p0, p1);
+#else
+            if ((i % kEmuMod) < kEmuCnt) {
+              p2 = ex2_poly2(x2);
+              unpack2(p2, p0, p1);
+            } else {
+              float x0, x1;
+              unpack2(x2, x0, x1);
+              p0 = ex2_approx(x0);
+              p1 = ex2_approx(x1);
+              p2 = pack2(p0, p1);
+            }
+#endif
+            if (i & 1) lacc1 = add2(lacc1, p2); else lacc0 = add2(lacc0, p2);
             pk[i] = pack_bf16x2(p0, p1);
           }
           tmem_st16(tS + cc * 16, pk);
         }
-        l += l0 + l1;
+        {
+          float a0, a1, b0, b1;
+          unpack2(lacc0, a0, a1);
+          unpack2(lacc1, b0, b1);
+          l += (a0 + a1) + (b0 + b1);
+        }
+#if defined(HK_DEBUG_MINSOFTMAX)
+        }
+#endif
+        HK_STAMP2(slot, 4);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[slot]);
+        HK_STAMP(slot, 5);
 #undef HK_S
       }
       if (!ok) break;
@@ -313,18 +391,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       prefetch_tmap(&tmap_k);
       prefetch_tmap(&tmap_v);
       uint32_t q_cnt[2] = {0, 0};
-      uint32_t kv_cnt = 0;  // tiles pushed into the ring so far
+      int ring_st = 0;        // next ring stage to fill
+      uint32_t ring_par = 0;  // its phase parity
       bool ok = true;
       auto push_kv = [&](const CUtensorMap* tm, int b, int kvh, int tile) -> bool {
-        const int st = kv_cnt % kStages;
-        const uint32_t ph = (kv_cnt / kStages) & 1;
-        if (!mbar_wait(&kv_empty[st], ph ^ 1, abortp, kWaitLimitNs)) return false;
+        const int st = ring_st;
+        if (!mbar_wait(&kv_empty[st], ring_par ^ 1, abortp, kWaitLimitNs)) return false;
         mbar_expect_tx(&kv_full[st], kTile);
         uint8_t* dst = sKV + st * kTile;
 #pragma unroll
         for (int ch = 0; ch < kChunks; ++ch)
           tma_load_4d(dst + ch * kSub, tm, &kv_full[st], ch * 64, kvh, tile * kBlockN, b);
-        ++kv_cnt;
+        if (++ring_st == kStages) {
+          ring_st = 0;
+          ring_par ^= 1;
+        }
         return true;
       };
       for (int round = 0; ok; ++round) {
@@ -354,28 +435,67 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
     } else if (warp == 9 && lane == 0) {
       // ---------------- UMMA issuer
+      // One thread issues for both slots, strictly alternating slot 0 / slot 1. The alternation is what
+      // keeps the two softmax warpgroups half a period apart, so that one slot's exponentials run under
+      // the other slot's MMAs. (Two independent issuers, one per slot, were measured: the slots drift
+      // into lock-step, both softmaxes and then both MMA chunks run at the same time, and throughput
+      // drops by 30 %.)
       constexpr uint32_t idesc_qk = make_idesc_bf16(kBlockM, kBlockN, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(kBlockM, D, true);
-      const uint32_t sQ_u = smem_u32(sQ), sKV_u = smem_u32(sKV);
-      uint32_t q_cnt[2] = {0, 0}, p_cnt[2] = {0, 0};
-      uint32_t kv_cnt = 0;  // tiles consumed from the ring so far
+      // Descriptor words: the high word is constant; the low word is (address >> 4) | (lbo >> 4) << 16 and
+      // a K step only adds a constant to it (tiles are 1024-byte aligned, so nothing carries out).
+      constexpr uint32_t desc_hi = smem_desc_hi(1024);
+      constexpr uint32_t tile16 = kTile >> 4;
+      const uint32_t q_lo0 = smem_desc_lo(smem_u32(sQ), 16);      // Q tile of slot 0 (K-major)
+      const uint32_t k_lo0 = smem_desc_lo(smem_u32(sKV), 16);     // ring stage 0 as a K tile (K-major)
+      const uint32_t v_lo0 = smem_desc_lo(smem_u32(sKV), kSub);   // ring stage 0 as a V tile (MN-major)
+      uint32_t q_par[2] = {0, 0}, p_par[2] = {0, 0};  // phase parities of q_full / p_full per slot
+      int ring_st = 0;                                // next ring stage to consume
+      uint32_t ring_par = 0;                          // its phase parity
+      int pending_v = -1, pending_k = -1;  // ring stages whose release is deferred (see the main loop)
       bool ok = true;
+#ifdef HK_TRACE
+      const bool trace_on = true;
+      int trace_n = 0;
+#endif
       // S[slot] = Q[slot] * K^T with K in ring stage `st`
       auto issue_qk = [&](int s, int st) {
+        const uint32_t a = q_lo0 + s * tile16, b = k_lo0 + st * tile16, d = tmem + s * kBlockN;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k / 4) * kSub + (k % 4) * 32;
-          umma_ss(tmem + s * kBlockN, make_smem_desc(sQ_u + s * kTile + off, 16, 1024),
-                  make_smem_desc(sKV_u + st * kTile + off, 16, 1024), idesc_qk, k > 0);
+          constexpr uint32_t sub16 = kSub >> 4;
+          const uint32_t off = (k / 4) * sub16 + (k % 4) * 2;  // 32 bytes per K step inside a 128-byte row
+          umma_ss_lohi(d, a + off, b + off, desc_hi, idesc_qk, k > 0 ? 1u : 0u);
         }
       };
       // O[slot] (+)= P[slot] * V with V in ring stage `st`; P is bf16 in TMEM (8 columns per 16 keys)
       auto issue_pv = [&](int s, int st, bool acc) {
+        const uint32_t b = v_lo0 + st * tile16, d = tmem + 2 * kBlockN + s * D, a = tmem + s * kBlockN;
 #pragma unroll
         for (int k = 0; k < kBlockN / 16; ++k)
-          umma_ts(tmem + 2 * kBlockN + s * D, tmem + s * kBlockN + k * 8,
-                  make_smem_desc(sKV_u + st * kTile + k * 2048, kSub, 1024), idesc_pv, (acc || k > 0) ? 1u : 0u);
+          umma_ts_lohi(d, a + k * 8, b + k * 128, desc_hi, idesc_pv, (acc || k > 0) ? 1u : 0u);
       };
+      auto ring_next = [&]() {
+        if (++ring_st == kStages) {
+          ring_st = 0;
+          ring_par ^= 1;
+        }
+      };
+      auto flush_releases = [&]() {
+        if (pending_v >= 0) {
+          umma_commit(&kv_empty[pending_v]);
+          pending_v = -1;
+        }
+        if (pending_k >= 0) {
+          umma_commit(&kv_empty[pending_k]);
+          pending_k = -1;
+        }
+      };
+      // The pipe runs only a couple of MMAs behind this thread, so whatever the thread does between the
+      // last MMA of one slot and the first MMA of the other is a bubble in the tensor pipe. Between slots
+      // there is therefore only the S-ready commit and the wait for the other slot's P; ring bookkeeping,
+      // the waits for the next K/V tiles and the ring releases all sit in the middle of a slot's chunk
+      // (after its PV, before its QK), where the pipe still has the PV MMAs queued.
       for (int round = 0; ok; ++round) {
         const int idx = item_for_round(round, blockIdx.x, gridDim.x);
         if (idx >= p.n_items) {
@@ -383,66 +503,95 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           continue;
         }
         const WorkItem w = decode_item<CAUSAL>(p, idx);
-        const int nmax = max(w.n[0], w.n[1]);
+        const int n0 = w.n[0], n1 = w.n[1];
+        const int nmax = max(n0, n1);
         // ---- first K tile: S = Q K0^T for both slots
-        int st_k = kv_cnt % kStages;
-        ok = mbar_wait(&kv_full[st_k], (kv_cnt / kStages) & 1, abortp, kWaitLimitNs);
-        ++kv_cnt;
-        for (int s = 0; s < 2 && ok; ++s) {
-          if (w.n[s] == 0) continue;
-          ok = mbar_wait(&q_full[s], q_cnt[s] & 1, abortp, kWaitLimitNs);
-          if (!ok) break;
-          ++q_cnt[s];
-          tc_fence_after();
-          issue_qk(s, st_k);
-          umma_commit(&s_full[s]);
-          if (w.n[s] == 1) umma_commit(&q_empty[s]);
-        }
+        ok = mbar_wait(&kv_full[ring_st], ring_par, abortp, kWaitLimitNs) &&
+             mbar_wait(&q_full[0], q_par[0], abortp, kWaitLimitNs);
         if (!ok) break;
-        umma_commit(&kv_empty[st_k]);
-        for (int j = 0; j < nmax && ok; ++j) {
-          const int st_v = kv_cnt % kStages;
-          const uint32_t ph_v = (kv_cnt / kStages) & 1;
-          ++kv_cnt;
-          bool v_ready = false, k_ready = false;
-          int st_kn = 0;
-          uint32_t ph_kn = 0;
-          const bool has_next = (j + 1 < nmax);
-          if (has_next) {
-            st_kn = kv_cnt % kStages;
-            ph_kn = (kv_cnt / kStages) & 1;
-            ++kv_cnt;
-          }
-          for (int s = 0; s < 2 && ok; ++s) {
-            if (j >= w.n[s]) continue;
-            ok = mbar_wait(&p_full[s], p_cnt[s] & 1, abortp, kWaitLimitNs);
-            if (!ok) break;
-            ++p_cnt[s];
-            if (!v_ready) {
-              ok = mbar_wait(&kv_full[st_v], ph_v, abortp, kWaitLimitNs);
-              if (!ok) break;
-              v_ready = true;
-            }
-            tc_fence_after();
-            issue_pv(s, st_v, j > 0);
-            if (j + 1 < w.n[s]) {
-              if (!k_ready) {
-                ok = mbar_wait(&kv_full[st_kn], ph_kn, abortp, kWaitLimitNs);
-                if (!ok) break;
-                k_ready = true;
-                tc_fence_after();
-              }
-              issue_qk(s, st_kn);
-              umma_commit(&s_full[s]);
-              if (j + 2 == w.n[s]) umma_commit(&q_empty[s]);  // last QK of this slot: Q may be replaced
-            } else {
-              umma_commit(&o_full[s]);
-            }
-          }
+        q_par[0] ^= 1;
+        tc_fence_after();
+        issue_qk(0, ring_st);
+        umma_commit(&s_full[0]);
+        if (n0 == 1) umma_commit(&q_empty[0]);
+        if (n1 > 0) {
+          ok = mbar_wait(&q_full[1], q_par[1], abortp, kWaitLimitNs);
           if (!ok) break;
-          umma_commit(&kv_empty[st_v]);
-          if (has_next) umma_commit(&kv_empty[st_kn]);
+          q_par[1] ^= 1;
+          tc_fence_after();
+          issue_qk(1, ring_st);
+          umma_commit(&s_full[1]);
+          if (n1 == 1) umma_commit(&q_empty[1]);
         }
+        umma_commit(&kv_empty[ring_st]);
+        ring_next();
+        // stages of V(0) and K(1)
+        int st_v = ring_st;
+        ok = mbar_wait(&kv_full[st_v], ring_par, abortp, kWaitLimitNs);
+        ring_next();
+        int st_k = ring_st;
+        if (ok && nmax > 1) {
+          ok = mbar_wait(&kv_full[st_k], ring_par, abortp, kWaitLimitNs);
+          ring_next();
+        }
+        for (int j = 0; j < nmax && ok; ++j) {
+          int nst_v = 0, nst_k = 0;
+          // ---- slot 0
+          if (j < n0) {
+            ok = mbar_wait(&p_full[0], p_par[0], abortp, kWaitLimitNs);
+            if (!ok) break;
+            p_par[0] ^= 1;
+            HK_STAMP(2, 12);
+            tc_fence_after();
+            issue_pv(0, st_v, j > 0);
+            flush_releases();  // V(j-1) and K(j): every MMA that read them is issued by now
+            if (j + 1 < n0) {
+              issue_qk(0, st_k);
+              umma_commit(&s_full[0]);
+              HK_STAMP(2, 14);
+              if (j + 2 == n0) umma_commit(&q_empty[0]);  // last QK of this slot: Q may be replaced
+            } else {
+              umma_commit(&o_full[0]);
+            }
+          }
+          // ---- slot 1
+          if (j < n1) {
+            ok = mbar_wait(&p_full[1], p_par[1], abortp, kWaitLimitNs);
+            if (!ok) break;
+            p_par[1] ^= 1;
+            HK_STAMP(2, 13);
+            tc_fence_after();
+            issue_pv(1, st_v, j > 0);
+          }
+          // next trip's tiles V(j+1), K(j+2): requested long ago, these waits normally pass at once
+          if (j + 1 < nmax) {
+            nst_v = ring_st;
+            ok = mbar_wait(&kv_full[nst_v], ring_par, abortp, kWaitLimitNs);
+            ring_next();
+            if (ok && j + 2 < nmax) {
+              nst_k = ring_st;
+              ok = mbar_wait(&kv_full[nst_k], ring_par, abortp, kWaitLimitNs);
+              ring_next();
+            }
+            if (!ok) break;
+          }
+          if (j < n1) {
+            if (j + 1 < n1) {
+              issue_qk(1, st_k);
+              umma_commit(&s_full[1]);
+              HK_STAMP(2, 15);
+              if (j + 2 == n1) umma_commit(&q_empty[1]);
+            } else {
+              umma_commit(&o_full[1]);
+            }
+          }
+          // V(j) and K(j+1) were last read by the MMAs above; their releases ride behind the next PV
+          pending_v = st_v;
+          if (j + 1 < nmax) pending_k = st_k;
+          st_v = nst_v;
+          st_k = nst_k;
+        }
+        flush_releases();
       }
     }
   }

@@ -105,6 +105,10 @@ int use_device(int device, DeviceState** out) {
   return HK_OK;
 }
 
+#ifdef HK_TRACE
+long long* g_trace_buf = nullptr;
+#endif
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // 4-D map over a contiguous bf16 [B, N, heads, D] tensor, box = 64 columns x 1 head x 128 rows,
@@ -155,6 +159,10 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
 
 extern "C" {
 
+#ifdef HK_TRACE
+void hk_debug_set_trace(long long* buf) { g_trace_buf = buf; }
+#endif
+
 int hk_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int N, int H, int H_KV,
                 int D, int causal, float softmax_scale, int device, void* cuda_stream) {
   if (!q || !k || !v || !o || !lse) return HK_EINVAL;
@@ -186,6 +194,9 @@ int hk_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse
   p.scale = softmax_scale > 0.f ? softmax_scale : 1.0f / std::sqrt(float(D));
   p.scale_log2 = p.scale * 1.4426950408889634f;
   p.status = st->status;
+#ifdef HK_TRACE
+  p.trace = g_trace_buf;
+#endif
   const int grid = p.n_items < st->sm_count ? p.n_items : st->sm_count;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (D == 128) return causal ? launch_fwd<128, true>(tq, tk, tv, p, grid, stream)

@@ -188,6 +188,43 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       : "memory");
 }
 
+// Same two instructions with the descriptors given as (low word, high word): the high word of a
+// descriptor is a per-kernel constant and the low word of a K step is base + constant, so the single
+// issuing thread spends one integer add per operand instead of rebuilding 64-bit descriptors.
+__host__ __device__ constexpr uint32_t smem_desc_hi(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3fff) | (1u << 14) | (static_cast<uint32_t>(kSwizzle128B) << 29);
+}
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return (saddr >> 4) | ((lbo_bytes >> 4) << 16);
+}
+__device__ __forceinline__ void umma_ss_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t hi,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // ---------------------------------------------------------------- TMEM <-> registers
 // 32x32b shape: thread t of the warp touches TMEM lane (lane field of taddr) + t, and N consecutive
 // 32-bit columns starting at the column field of taddr.
@@ -224,12 +261,63 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 
+// ---------------------------------------------------------------- packed fp32x2 arithmetic
+// Blackwell executes add / mul / fma on two fp32 values held in a 64-bit register pair with one
+// instruction, which halves the issue slots the softmax spends on its scale-subtract and row sums.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // ---------------------------------------------------------------- small math helpers
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 2^x for two values on the FMA and integer pipes instead of the MUFU: round x to the nearest integer n
+// with the 1.5*2^23 trick, evaluate a cubic in f = x - n on [-0.5, 0.5] (p(0) = 1 exactly, relative error
+// <= 1.02e-4), and add n to the exponent field. Inputs are clamped at -125 so the exponent stays normal.
+__device__ __forceinline__ uint64_t ex2_poly2(uint64_t x2) {
+  float x0, x1;
+  unpack2(x2, x0, x1);
+  x0 = fmaxf(x0, -125.0f);
+  x1 = fmaxf(x1, -125.0f);
+  const uint64_t xc = pack2(x0, x1);
+  const uint64_t xr = add2(xc, pack2(12582912.0f, 12582912.0f));
+  const uint64_t nf = add2(xr, pack2(-12582912.0f, -12582912.0f));
+  const uint64_t fr = fma2(nf, pack2(-1.0f, -1.0f), xc);
+  uint64_t p = fma2(fr, pack2(0.05500893294811249f, 0.05500893294811249f),
+                    pack2(0.24221095442771912f, 0.24221095442771912f));
+  p = fma2(p, fr, pack2(0.6932829022407532f, 0.6932829022407532f));
+  p = fma2(p, fr, pack2(1.0f, 1.0f));
+  float p0, p1, r0, r1;
+  unpack2(p, p0, p1);
+  unpack2(xr, r0, r1);
+  p0 = __int_as_float(__float_as_int(p0) + (__float_as_int(r0) << 23));
+  p1 = __int_as_float(__float_as_int(p1) + (__float_as_int(r1) << 23));
+  return pack2(p0, p1);
+}
+
 // Two fp32 -> packed bf16x2 (round to nearest even); `lo` lands in the low 16 bits.
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t r;
