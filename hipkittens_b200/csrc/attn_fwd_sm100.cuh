@@ -35,6 +35,7 @@ namespace hk {
 constexpr int kBlockM = 128;        // query rows per slot
 constexpr int kBlockN = 128;        // keys per KV tile
 constexpr int kFwdThreads = 384;
+constexpr int kFwdRegsAtLaunch = 168;   // 65536 / 384, rounded down to a multiple of 8; see setmaxnreg below
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThresholdLog2 = 8.0f;
 #ifndef HK_EMU_MOD
@@ -45,7 +46,7 @@ constexpr float kRescaleThresholdLog2 = 8.0f;
 #endif
 constexpr int kEmuMod = HK_EMU_MOD;   // of every kEmuMod column pairs ...
 constexpr int kEmuCnt = HK_EMU_CNT;   // ... this many compute exp2 with the polynomial instead of the MUFU
-constexpr uint64_t kWaitLimitNs = 4000ull * 1000 * 1000;  // 4 s: far beyond any legitimate wait
+constexpr uint64_t kWaitLimitNs = 8000ull * 1000 * 1000;  // SM cycles, > 4 s: far beyond any legitimate wait
 
 // Device status codes written to FwdParams::status (0 = OK).
 enum : int { kStatusOk = 0, kStatusTimeout = 1 };
@@ -319,8 +320,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             unpack2(p2, p0, p1);
 #else
             if ((i % kEmuMod) < kEmuCnt) {
-              p2 = ex2_poly2(x2);
-              unpack2(p2, p0, p1);
+              float x0, x1;
+              unpack2(x2, x0, x1);
+              p0 = ex2_poly(x0);
+              p1 = ex2_poly(x1);
+              p2 = pack2(p0, p1);
             } else {
               float x0, x1;
               unpack2(x2, x0, x1);

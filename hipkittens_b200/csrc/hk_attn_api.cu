@@ -60,12 +60,12 @@ int prepare_fwd_kernel() {
   HK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, hk::FwdSmem<D>::kDynBytes));
   cudaFuncAttributes attr;
   HK_CUDA(cudaFuncGetAttributes(&attr, fn));
-  // The kernel re-balances registers between warpgroups (208/208/88 per thread); that only adds up if
-  // it was compiled to exactly 168 registers per thread at launch. Refuse to launch otherwise: a
-  // register pool that is too small would block the re-allocation forever.
-  if (attr.numRegs != 168) {
-    snprintf(g_cuda_err, sizeof(g_cuda_err), "attn_fwd_kernel<%d,%d> compiled to %d registers, expected 168", D,
-             int(CAUSAL), attr.numRegs);
+  // The kernel re-balances registers between warpgroups (208 per softmax thread, 88 per producer thread);
+  // that only adds up if it was compiled to exactly kFwdRegsAtLaunch registers per thread at launch.
+  // Refuse to launch otherwise: a register pool that is too small would block the re-allocation forever.
+  if (attr.numRegs != hk::kFwdRegsAtLaunch) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "attn_fwd_kernel<%d,%d> compiled to %d registers, expected %d", D,
+             int(CAUSAL), attr.numRegs, hk::kFwdRegsAtLaunch);
     return HK_EUNSUPPORTED;
   }
   return HK_OK;
@@ -142,7 +142,8 @@ __global__ void bounded_wait_selftest_kernel(int* status, unsigned long long lim
     hk::ptx::fence_mbar_init();
   }
   __syncthreads();
-  const bool ok = hk::ptx::mbar_wait(&bar, 0, &abort_flag, limit_ns);  // nobody ever arrives
+  // the limit is given in nanoseconds; 2 cycles per nanosecond is the SM's maximum clock, rounded up
+  const bool ok = hk::ptx::mbar_wait(&bar, 0, &abort_flag, limit_ns * 2);  // nobody ever arrives
   if (!ok && threadIdx.x == 0) atomicCAS(status, hk::kStatusOk, hk::kStatusTimeout);
 }
 

@@ -69,20 +69,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait. `abort_flag` is a CTA-shared word that any role sets once it gave up; other
 // roles then leave their own waits quickly instead of each burning a full time limit.
-// Returns true when the phase completed, false on time-out or abort.
+// Returns true when the phase completed, false on time-out or abort. The limit is in SM clock cycles
+// (clock64 is a cheap register read; the global nanosecond timer costs hundreds of cycles per read and
+// would sit on the wake-up path of every wait).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint64_t limit_ns) {
+                                          uint64_t limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  uint32_t spins = 0;
+  const long long t0 = clock64();
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0x3f) == 0) {
-      if (*abort_flag != 0) return false;
-      if (globaltimer_ns() - t0 > limit_ns) {
-        *abort_flag = 1;
-        return false;
-      }
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag != 0) return false;
+    if (static_cast<uint64_t>(clock64() - t0) > limit_cycles) {
+      *abort_flag = 1;
+      return false;
     }
   }
 }
@@ -316,6 +317,17 @@ __device__ __forceinline__ uint64_t ex2_poly2(uint64_t x2) {
   p0 = __int_as_float(__float_as_int(p0) + (__float_as_int(r0) << 23));
   p1 = __int_as_float(__float_as_int(p1) + (__float_as_int(r1) << 23));
   return pack2(p0, p1);
+}
+
+// Scalar form of the same polynomial exp2 (8 instructions, constants as immediates).
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -125.0f);
+  const float xr = x + 12582912.0f;
+  const float f = x - (xr - 12582912.0f);
+  float p = fmaf(f, 0.05500893294811249f, 0.24221095442771912f);
+  p = fmaf(p, f, 0.6932829022407532f);
+  p = fmaf(p, f, 1.0f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(xr) << 23));
 }
 
 // Two fp32 -> packed bf16x2 (round to nearest even); `lo` lands in the low 16 bits.
