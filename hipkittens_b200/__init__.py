@@ -6,8 +6,8 @@ sm_100 device is present, calls raise.
 
 Public surface
 --------------
-* ``attn_fwd(q, k, v, causal=False, ...) -> (O, L)`` and ``paged_decode(...) -> (O, L)``: torch-tensor
-  front ends over the C ABI (ctypes).
+* ``attn_fwd(q, k, v, causal=False, ...) -> (O, L)``, ``paged_decode(...) -> (O, L)`` and
+  ``paged_kv_append(...)``: torch-tensor front ends over the C ABI (ctypes).
 * ``load_tk_kernel(causal)`` / ``load_tk_kernel_fwd(causal)``: the reference's extension modules
   (``tk_kernel.dispatch_micro``, ``tk_kernel_fwd.dispatch_fwd``) built for B200.
 * ``HipAttnFunction`` in :mod:`hipkittens_b200.attention`: the reference's autograd-function forward.
@@ -22,6 +22,7 @@ from ._native import (  # noqa: F401
     load_tk_kernel_fwd,
     paged_decode,
     paged_decode_workspace_bytes,
+    paged_kv_append,
 )
 
 __all__ = [
@@ -33,5 +34,6 @@ __all__ = [
     "load_tk_kernel",
     "load_tk_kernel_fwd",
     "paged_decode",
+    "paged_kv_append",
     "paged_decode_workspace_bytes",
 ]

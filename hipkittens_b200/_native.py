@@ -25,6 +25,7 @@ EXPORTED_SYMBOLS = (
     "hk_attn_paged_decode_workspace_bytes",
     "hk_attn_paged_decode",
     "hk_attn_paged_decode_static",
+    "hk_paged_kv_append",
     "hk_last_device_status",
     "hk_selftest_bounded_wait",
     "hk_kernel_launch_count",
@@ -73,6 +74,8 @@ def capi() -> ctypes.CDLL:
     lib.hk_attn_paged_decode_static.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cf, ci, vp,
                                                 ctypes.POINTER(ci)]
     lib.hk_attn_paged_decode_static.restype = ci
+    lib.hk_paged_kv_append.argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, ci, vp]
+    lib.hk_paged_kv_append.restype = ci
     lib.hk_last_device_status.argtypes = [ci]
     lib.hk_last_device_status.restype = ci
     lib.hk_selftest_bounded_wait.argtypes = [ci, ctypes.c_uint]
@@ -200,6 +203,38 @@ def paged_decode(
                                      workspace.data_ptr(), workspace.numel(), q.device.index, st.cuda_stream)
     _check(rc, "hk_attn_paged_decode")
     return out, lse
+
+
+def paged_kv_append(
+    k_new: torch.Tensor,
+    v_new: torch.Tensor,
+    k_pages: torch.Tensor,
+    v_pages: torch.Tensor,
+    block_table: torch.Tensor,
+    start_pos: torch.Tensor,
+    stream: Optional[torch.cuda.Stream] = None,
+) -> None:
+    """Write k_new/v_new [S,T,H_KV,D] into the page pools at positions start_pos[s] .. start_pos[s]+T-1 of each
+    sequence (the paged form of the reference's `_update_kv_cache`, training/llama/llama/models/mha.py:16-42)."""
+    for name, t in (("k_new", k_new), ("v_new", v_new), ("k_pages", k_pages), ("v_pages", v_pages)):
+        _require_cuda_bf16(name, t, 4)
+        if t.dtype != torch.bfloat16:
+            raise RuntimeError(f"{name} must be torch.bfloat16")
+    if block_table.dtype != torch.int32 or start_pos.dtype != torch.int32:
+        raise RuntimeError("block_table and start_pos must be torch.int32")
+    if not (block_table.is_contiguous() and start_pos.is_contiguous()):
+        raise RuntimeError("Tensor must be contiguous")
+    s_n, t_n, hkv, d = k_new.shape
+    p_n, page, hkv2, d2 = k_pages.shape
+    if v_new.shape != k_new.shape or v_pages.shape != k_pages.shape or (hkv2, d2) != (hkv, d):
+        raise RuntimeError("k_new/v_new must be [S,T,H_KV,D] and k_pages/v_pages [P,page,H_KV,D]")
+    if block_table.dim() != 2 or block_table.shape[0] != s_n or start_pos.shape != (s_n,):
+        raise RuntimeError("block_table must be [S, max_pages] and start_pos [S]")
+    st = stream if stream is not None else torch.cuda.current_stream(k_new.device)
+    rc = capi().hk_paged_kv_append(k_new.data_ptr(), v_new.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
+                                   block_table.data_ptr(), start_pos.data_ptr(), s_n, t_n, hkv, d, page,
+                                   block_table.shape[1], p_n, k_new.device.index, st.cuda_stream)
+    _check(rc, "hk_paged_kv_append")
 
 
 def device_status(device: int = 0) -> int:

@@ -175,6 +175,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   constexpr int kTile = SM::kTileBytes;
   constexpr int kSub = SM::kSubTileBytes;
   constexpr int kChunks = D / 64;  // 64-column TMA boxes per tile row
+  // With D = 64 the two O accumulators need only 128 TMEM columns, which leaves room for P outside S
+  // (columns [384,448) and [448,512)). S(j+1) = Q K(j+1)^T can then be issued as soon as the softmax has
+  // read S(j), instead of after O += P(j) V(j), and a slot's softmax never waits for the tensor pipe.
+  constexpr bool kSepP = (D == 64);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -182,6 +186,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint8_t* sKV = smem + 2 * kTile;    // kStages tiles, K and V alternate through the ring
 
   __shared__ uint64_t q_full[2], q_empty[2], s_full[2], p_full[2], o_full[2];
+  __shared__ uint64_t s_free[2], p_free[2];  // D = 64 only: S has been read / P has been consumed
   __shared__ uint64_t kv_full[kStages], kv_empty[kStages];
   __shared__ uint32_t tmem_base_slot;
   __shared__ uint32_t abort_flag;
@@ -198,6 +203,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       mbar_init(&s_full[s], 1);
       mbar_init(&p_full[s], 4);  // one arrival per softmax warp
       mbar_init(&o_full[s], 1);
+      mbar_init(&s_free[s], 4);
+      mbar_init(&p_free[s], 1);
     }
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&kv_full[s], 1);
@@ -223,8 +230,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + lane_addr + slot * kBlockN;
     const uint32_t tO = tmem + lane_addr + 2 * kBlockN + slot * D;
+    const uint32_t tP = kSepP ? tmem + lane_addr + 384 + slot * 64 : tS;  // bf16 P: 64 packed columns
     const float c = p.scale_log2;
-    uint32_t s_cnt = 0, o_cnt = 0;
+    uint32_t s_cnt = 0, o_cnt = 0, pv_cnt = 0;
     bool ok = true;
 #ifdef HK_TRACE
     const bool trace_on = ((warp & 3) == 0) && lane == 0;
@@ -255,6 +263,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         for (int cc = 0; cc < 4; ++cc) tmem_ld32(tS + cc * 32, su + cc * 32);
         tmem_wait_ld();
         HK_STAMP2(slot, 2);
+        if (kSepP && j + 1 < nkv) {
+          // S(j) is in registers: the issuer may overwrite it with S(j+1) right away
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s_free[slot]);
+        }
         if (CAUSAL && j == nkv - 1) {
           // diagonal tile: key (j*128 + col) is visible to query (qb*128 + row) iff col <= row
 #pragma unroll
@@ -263,7 +277,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #if defined(HK_DEBUG_MINSOFTMAX)
         // timing experiment only: the shortest possible softmax stage (load S, store something as P)
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) tmem_st16(tS + cc * 16, su + cc * 32);
+        for (int cc = 0; cc < 4; ++cc) tmem_st16(tP + cc * 16, su + cc * 32);
         l += 1.0f;
         if (false) {
 #endif
@@ -277,6 +291,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           bm3 = max3(bm3, HK_S(i + 6), HK_S(i + 7));
         }
         const float bm = fmaxf(fmaxf(bm0, bm2), fmaxf(bm1, bm3));
+        if (kSepP && pv_cnt > 0) {
+          // S(j) may be ready before O += P(j-1) V(j-1) has finished: wait for that product before
+          // rescaling O or overwriting P
+          ok = mbar_wait(&p_free[slot], (pv_cnt - 1) & 1, abortp, kWaitLimitNs);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        ++pv_cnt;
         if (j == 0) {
           m = bm;
         } else {
@@ -336,7 +359,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             if (i & 1) lacc1 = add2(lacc1, p2); else lacc0 = add2(lacc0, p2);
             pk[i] = pack_bf16x2(p0, p1);
           }
-          tmem_st16(tS + cc * 16, pk);
+          tmem_st16(tP + cc * 16, pk);
         }
         {
           float a0, a1, b0, b1;
@@ -454,6 +477,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const uint32_t k_lo0 = smem_desc_lo(smem_u32(sKV), 16);     // ring stage 0 as a K tile (K-major)
       const uint32_t v_lo0 = smem_desc_lo(smem_u32(sKV), kSub);   // ring stage 0 as a V tile (MN-major)
       uint32_t q_par[2] = {0, 0}, p_par[2] = {0, 0};  // phase parities of q_full / p_full per slot
+      uint32_t sf_par[2] = {0, 0};                    // ... and of s_free (D = 64 only)
       int ring_st = 0;                                // next ring stage to consume
       uint32_t ring_par = 0;                          // its phase parity
       int pending_v = -1, pending_k = -1;  // ring stages whose release is deferred (see the main loop)
@@ -474,7 +498,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       };
       // O[slot] (+)= P[slot] * V with V in ring stage `st`; P is bf16 in TMEM (8 columns per 16 keys)
       auto issue_pv = [&](int s, int st, bool acc) {
-        const uint32_t b = v_lo0 + st * tile16, d = tmem + 2 * kBlockN + s * D, a = tmem + s * kBlockN;
+        const uint32_t b = v_lo0 + st * tile16, d = tmem + 2 * kBlockN + s * D;
+        const uint32_t a = kSepP ? tmem + 384 + s * 64 : tmem + s * kBlockN;
 #pragma unroll
         for (int k = 0; k < kBlockN / 16; ++k)
           umma_ts_lohi(d, a + k * 8, b + k * 128, desc_hi, idesc_pv, (acc || k > 0) ? 1u : 0u);
@@ -529,71 +554,129 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
         umma_commit(&kv_empty[ring_st]);
         ring_next();
-        // stages of V(0) and K(1)
-        int st_v = ring_st;
-        ok = mbar_wait(&kv_full[st_v], ring_par, abortp, kWaitLimitNs);
-        ring_next();
-        int st_k = ring_st;
-        if (ok && nmax > 1) {
-          ok = mbar_wait(&kv_full[st_k], ring_par, abortp, kWaitLimitNs);
-          ring_next();
-        }
-        for (int j = 0; j < nmax && ok; ++j) {
-          int nst_v = 0, nst_k = 0;
-          // ---- slot 0
-          if (j < n0) {
-            ok = mbar_wait(&p_full[0], p_par[0], abortp, kWaitLimitNs);
-            if (!ok) break;
-            p_par[0] ^= 1;
-            HK_STAMP(2, 12);
-            tc_fence_after();
-            issue_pv(0, st_v, j > 0);
-            flush_releases();  // V(j-1) and K(j): every MMA that read them is issued by now
-            if (j + 1 < n0) {
-              issue_qk(0, st_k);
-              umma_commit(&s_full[0]);
-              HK_STAMP(2, 14);
-              if (j + 2 == n0) umma_commit(&q_empty[0]);  // last QK of this slot: Q may be replaced
-            } else {
-              umma_commit(&o_full[0]);
-            }
-          }
-          // ---- slot 1
-          if (j < n1) {
-            ok = mbar_wait(&p_full[1], p_par[1], abortp, kWaitLimitNs);
-            if (!ok) break;
-            p_par[1] ^= 1;
-            HK_STAMP(2, 13);
-            tc_fence_after();
-            issue_pv(1, st_v, j > 0);
-          }
-          // next trip's tiles V(j+1), K(j+2): requested long ago, these waits normally pass at once
-          if (j + 1 < nmax) {
-            nst_v = ring_st;
-            ok = mbar_wait(&kv_full[nst_v], ring_par, abortp, kWaitLimitNs);
+        if constexpr (kSepP) {
+          // D = 64: S(j+1) is issued before O += P(j) V(j); see kSepP above. (An issuer that polls the four
+          // conditions and issues whichever is ready first was measured slower than this fixed order.)
+          for (int j = 0; j < nmax && ok; ++j) {
+            const int st_v = ring_st;
+            const uint32_t par_v = ring_par;
             ring_next();
-            if (ok && j + 2 < nmax) {
-              nst_k = ring_st;
-              ok = mbar_wait(&kv_full[nst_k], ring_par, abortp, kWaitLimitNs);
+            const bool has_next = (j + 1 < nmax);
+            const int st_k = ring_st;
+            const uint32_t par_k = ring_par;
+            if (has_next) {
               ring_next();
+              ok = mbar_wait(&kv_full[st_k], par_k, abortp, kWaitLimitNs);
+              if (ok && j + 1 < n0) {
+                ok = mbar_wait(&s_free[0], sf_par[0], abortp, kWaitLimitNs);
+                sf_par[0] ^= 1;
+                if (!ok) break;
+                tc_fence_after();
+                issue_qk(0, st_k);
+                umma_commit(&s_full[0]);
+                if (j + 2 == n0) umma_commit(&q_empty[0]);
+              }
+              if (ok && j + 1 < n1) {
+                ok = mbar_wait(&s_free[1], sf_par[1], abortp, kWaitLimitNs);
+                sf_par[1] ^= 1;
+                if (!ok) break;
+                tc_fence_after();
+                issue_qk(1, st_k);
+                umma_commit(&s_full[1]);
+                if (j + 2 == n1) umma_commit(&q_empty[1]);
+              }
+              if (!ok) break;
+              umma_commit(&kv_empty[st_k]);
+            }
+            ok = mbar_wait(&kv_full[st_v], par_v, abortp, kWaitLimitNs);
+            if (ok && j < n0) {
+              ok = mbar_wait(&p_full[0], p_par[0], abortp, kWaitLimitNs);
+              if (!ok) break;
+              p_par[0] ^= 1;
+              tc_fence_after();
+              issue_pv(0, st_v, j > 0);
+              umma_commit(&p_free[0]);
+              if (j + 1 == n0) umma_commit(&o_full[0]);
+            }
+            if (ok && j < n1) {
+              ok = mbar_wait(&p_full[1], p_par[1], abortp, kWaitLimitNs);
+              if (!ok) break;
+              p_par[1] ^= 1;
+              tc_fence_after();
+              issue_pv(1, st_v, j > 0);
+              umma_commit(&p_free[1]);
+              if (j + 1 == n1) umma_commit(&o_full[1]);
             }
             if (!ok) break;
+            umma_commit(&kv_empty[st_v]);
           }
-          if (j < n1) {
-            if (j + 1 < n1) {
-              issue_qk(1, st_k);
-              umma_commit(&s_full[1]);
-              HK_STAMP(2, 15);
-              if (j + 2 == n1) umma_commit(&q_empty[1]);
-            } else {
-              umma_commit(&o_full[1]);
+        } else {
+          // stages of V(0) and K(1)
+          int st_v = ring_st;
+          ok = mbar_wait(&kv_full[st_v], ring_par, abortp, kWaitLimitNs);
+          ring_next();
+          int st_k = ring_st;
+          if (ok && nmax > 1) {
+            ok = mbar_wait(&kv_full[st_k], ring_par, abortp, kWaitLimitNs);
+            ring_next();
+          }
+          for (int j = 0; j < nmax && ok; ++j) {
+            int nst_v = 0, nst_k = 0;
+            // ---- slot 0
+            if (j < n0) {
+              ok = mbar_wait(&p_full[0], p_par[0], abortp, kWaitLimitNs);
+              if (!ok) break;
+              p_par[0] ^= 1;
+              HK_STAMP(2, 12);
+              tc_fence_after();
+              issue_pv(0, st_v, j > 0);
+              flush_releases();  // V(j-1) and K(j): every MMA that read them is issued by now
+              if (j + 1 < n0) {
+                issue_qk(0, st_k);
+                umma_commit(&s_full[0]);
+                HK_STAMP(2, 14);
+                if (j + 2 == n0) umma_commit(&q_empty[0]);  // last QK of this slot: Q may be replaced
+              } else {
+                umma_commit(&o_full[0]);
+              }
             }
+            // ---- slot 1
+            if (j < n1) {
+              ok = mbar_wait(&p_full[1], p_par[1], abortp, kWaitLimitNs);
+              if (!ok) break;
+              p_par[1] ^= 1;
+              HK_STAMP(2, 13);
+              tc_fence_after();
+              issue_pv(1, st_v, j > 0);
+            }
+            // next trip's tiles V(j+1), K(j+2): requested long ago, these waits normally pass at once
+            if (j + 1 < nmax) {
+              nst_v = ring_st;
+              ok = mbar_wait(&kv_full[nst_v], ring_par, abortp, kWaitLimitNs);
+              ring_next();
+              if (ok && j + 2 < nmax) {
+                nst_k = ring_st;
+                ok = mbar_wait(&kv_full[nst_k], ring_par, abortp, kWaitLimitNs);
+                ring_next();
+              }
+              if (!ok) break;
+            }
+            if (j < n1) {
+              if (j + 1 < n1) {
+                issue_qk(1, st_k);
+                umma_commit(&s_full[1]);
+                HK_STAMP(2, 15);
+                if (j + 2 == n1) umma_commit(&q_empty[1]);
+              } else {
+                umma_commit(&o_full[1]);
+              }
+            }
+            // V(j) and K(j+1) were last read by the MMAs above; their releases ride behind the next PV
+            pending_v = st_v;
+            if (j + 1 < nmax) pending_k = st_k;
+            st_v = nst_v;
+            st_k = nst_k;
           }
-          // V(j) and K(j+1) were last read by the MMAs above; their releases ride behind the next PV
-          pending_v = st_v;
-          if (j + 1 < nmax) pending_k = st_k;
-          st_v = nst_v;
-          st_k = nst_k;
         }
         flush_releases();
       }

@@ -11,6 +11,7 @@
 #include "../../include/hk_attn.h"
 #include "attn_fwd_sm100.cuh"
 #include "paged_decode_sm100.cuh"
+#include "paged_kv_append_sm100.cuh"
 
 namespace {
 
@@ -247,6 +248,36 @@ int hk_attn_paged_decode(const void* q, const void* k_pages, const void* v_pages
   cudaError_t e = hk::launch_paged_decode(p, st->sm_count, static_cast<cudaStream_t>(cuda_stream), &launched);
   g_launches.fetch_add(launched, std::memory_order_relaxed);
   if (e != cudaSuccess) return cuda_fail(e, "paged decode launch");
+  return HK_OK;
+}
+
+int hk_paged_kv_append(const void* k_new, const void* v_new, void* k_pages, void* v_pages,
+                       const int32_t* block_table, const int32_t* start_pos, int S, int T, int H_KV, int D,
+                       int page_size, int max_pages_per_seq, int num_pages, int device, void* cuda_stream) {
+  if (!k_new || !v_new || !k_pages || !v_pages || !block_table || !start_pos) return HK_EINVAL;
+  if (S <= 0 || T <= 0 || H_KV <= 0 || D <= 0 || max_pages_per_seq <= 0 || num_pages <= 0) return HK_EINVAL;
+  if (page_size != hk::kPageTokens) return HK_EUNSUPPORTED;
+  if ((H_KV * D) % 8 != 0 || T > 65535 || S > 65535) return HK_EINVAL;
+  if (!aligned16(k_new) || !aligned16(v_new) || !aligned16(k_pages) || !aligned16(v_pages)) return HK_EINVAL;
+  DeviceState* st = nullptr;
+  int rc = use_device(device, &st);
+  if (rc != HK_OK) return rc;
+  hk::AppendParams p;
+  p.k_new = static_cast<const __nv_bfloat16*>(k_new);
+  p.v_new = static_cast<const __nv_bfloat16*>(v_new);
+  p.k_pages = static_cast<__nv_bfloat16*>(k_pages);
+  p.v_pages = static_cast<__nv_bfloat16*>(v_pages);
+  p.block_table = block_table;
+  p.start_pos = start_pos;
+  p.S = S;
+  p.T = T;
+  p.row_vec16 = H_KV * D * 2 / 16;
+  p.max_pages = max_pages_per_seq;
+  p.num_pages = num_pages;
+  p.status = st->status;
+  hk::paged_kv_append_kernel<<<dim3(T, S), 128, 0, static_cast<cudaStream_t>(cuda_stream)>>>(p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  HK_CUDA(cudaGetLastError());
   return HK_OK;
 }
 

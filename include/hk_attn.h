@@ -52,6 +52,20 @@ int hk_attn_paged_decode(const void* q, const void* k_pages, const void* v_pages
                          float softmax_scale, void* workspace, size_t workspace_bytes,
                          int device, void* cuda_stream);
 
+/* Appends T new tokens per sequence to the paged KV cache read by hk_attn_paged_decode.
+ * Paged counterpart of the reference's contiguous cache update, kv_cache[b, offset : offset + T] = kv
+ * (training/llama/llama/models/mha.py:16-42, _update_kv_cache).
+ *   k_new, v_new : bf16 [S, T, H_KV, D]          k_pages, v_pages : bf16 [num_pages, page_size, H_KV, D]
+ *   start_pos    : int32 [S]; token t of sequence s is written at position start_pos[s] + t, i.e. row
+ *                  (pos % page_size) of page block_table[s, pos / page_size]
+ *   page_size = 16; H_KV * D a multiple of 8; pointers 16-byte aligned.
+ * A position beyond max_pages_per_seq pages or a page id outside [0, num_pages) is skipped and reported as
+ * HK_EBADPAGE by hk_last_device_status. Asynchronous on `cuda_stream`. */
+int hk_paged_kv_append(const void* k_new, const void* v_new, void* k_pages, void* v_pages,
+                       const int32_t* block_table, const int32_t* start_pos,
+                       int S, int T, int H_KV, int D, int page_size, int max_pages_per_seq, int num_pages,
+                       int device, void* cuda_stream);
+
 /* Paged-KV decode for callers that cannot allocate device memory. No counterpart in the reference.
  *
  * Who needs it: a serving engine that hands all of HBM to its own block allocator at start-up leaves nothing

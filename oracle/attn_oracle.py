@@ -42,6 +42,7 @@ from hipkittens_b200.synthetic import make_paged_inputs, make_prefill_inputs  # 
 __all__ = [
     "attn_fwd_oracle",
     "paged_decode_oracle",
+    "paged_kv_append_oracle",
     "make_prefill_inputs",
     "make_paged_inputs",
     "robustness_check",
@@ -143,3 +144,24 @@ def robustness_check(ref: torch.Tensor, pred: torch.Tensor):
     l2 = float(diff.pow(2).sum().sqrt() / ref.pow(2).sum().sqrt())
     cos = float(torch.nn.functional.cosine_similarity(ref.flatten(), pred.flatten(), dim=0))
     return float(diff.max()), err, ref.numel(), l2, cos
+
+
+def paged_kv_append_oracle(k_new, v_new, k_pages, v_pages, block_table, start_pos):
+    """Paged form of the reference's cache update ``kv_cache[b, offset:offset+T] = kv``
+    (``training/llama/llama/models/mha.py:16-42``): token t of sequence s goes to position
+    ``start_pos[s] + t``, i.e. row ``pos % page`` of page ``block_table[s, pos // page]``.
+    Returns updated copies of the pools; positions outside the table or ids outside the pool are skipped."""
+    kp, vp = k_pages.clone(), v_pages.clone()
+    page = kp.shape[1]
+    s_n, t_n = k_new.shape[:2]
+    for s in range(s_n):
+        for t in range(t_n):
+            pos = int(start_pos[s]) + t
+            if pos < 0 or pos // page >= block_table.shape[1]:
+                continue
+            pid = int(block_table[s, pos // page])
+            if pid < 0 or pid >= kp.shape[0]:
+                continue
+            kp[pid, pos % page] = k_new[s, t]
+            vp[pid, pos % page] = v_new[s, t]
+    return kp, vp

@@ -10,6 +10,7 @@ import torch
 
 from oracle.attn_oracle import (
     attn_fwd_oracle,
+    paged_kv_append_oracle,
     make_paged_inputs,
     make_prefill_inputs,
     paged_decode_oracle,
@@ -134,3 +135,29 @@ def test_robustness_check_counts_like_the_reference_harness():
     pred[1] += 0.01  # within
     max_abs, err, numel, _l2, cos = robustness_check(ref, pred)
     assert err == 1 and numel == 10 and abs(max_abs - 0.2) < 1e-6 and cos > 0.99
+
+
+def test_paged_append_equals_contiguous_slice_assignment():
+    """The reference updates a contiguous cache with kv_cache[b, off:off+T] = kv (mha.py:16-42); gathering the
+    paged cache through the block table after the paged append must give the same contiguous result."""
+    q, kp, vp, table, ctx = make_paged_inputs(3, 4, 2, 64, 16, 80, 30, 200, seed=11)
+    t = 5
+    gen = torch.Generator().manual_seed(1)
+    k_new = torch.randn((3, t, 2, 64), generator=gen).to(torch.bfloat16)
+    v_new = torch.randn((3, t, 2, 64), generator=gen).to(torch.bfloat16)
+    start = (ctx - t).to(torch.int32)
+    kp2, vp2 = paged_kv_append_oracle(k_new, v_new, kp, vp, table, start)
+    for s in range(3):
+        c = int(ctx[s])
+        npg = (c + 15) // 16
+        ids = table[s, :npg].long()
+        before = kp[ids].reshape(-1, 2, 64)[:c].clone()
+        before[c - t:c] = k_new[s]  # the reference's slice assignment on the contiguous view
+        after = kp2[ids].reshape(-1, 2, 64)[:c]
+        assert torch.equal(before.view(torch.int16), after.view(torch.int16))
+    # pages of other sequences are untouched
+    used = set()
+    for s in range(3):
+        used |= set(table[s, :(int(ctx[s]) + 15) // 16].tolist())
+    rest = [i for i in range(80) if i not in used]
+    assert torch.equal(kp2[rest].view(torch.int16), kp[rest].view(torch.int16))
