@@ -22,6 +22,7 @@ HK_OK, HK_EINVAL, HK_EUNSUPPORTED, HK_ECUDA, HK_ETIMEOUT, HK_EWORKSPACE, HK_EBAD
 # Every symbol declared in include/hk_attn.h.
 EXPORTED_SYMBOLS = (
     "hk_attn_fwd",
+    "hk_attn_fwd_strided",
     "hk_attn_paged_decode_workspace_bytes",
     "hk_attn_paged_decode",
     "hk_attn_paged_decode_static",
@@ -66,6 +67,9 @@ def capi() -> ctypes.CDLL:
     vp, ci, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
     lib.hk_attn_fwd.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, cf, ci, vp]
     lib.hk_attn_fwd.restype = ci
+    ll3 = ctypes.POINTER(ctypes.c_longlong)
+    lib.hk_attn_fwd_strided.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ll3, ll3, ll3, ci, cf, ci, vp]
+    lib.hk_attn_fwd_strided.restype = ci
     lib.hk_attn_paged_decode_workspace_bytes.argtypes = [ci, ci, ci, ci, ci]
     lib.hk_attn_paged_decode_workspace_bytes.restype = ctypes.c_size_t
     lib.hk_attn_paged_decode.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cf, vp,
@@ -127,12 +131,21 @@ def attn_fwd(
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """O = softmax(scale q k^T) v and L = logsumexp(scale q k^T) on the GPU.
 
-    q [B,N,H,D] bf16, k/v [B,N,H_KV,D] bf16, contiguous CUDA tensors; returns O [B,N,H,D] bf16 and
+    q [B,N,H,D] bf16, k/v [B,N,H_KV,D] bf16 CUDA tensors, contiguous or strided views with a contiguous
+    last dimension (e.g. slices of a packed qkv projection; no copy is made); returns O [B,N,H,D] bf16 and
     L [B,H,1,N] fp32 (the layouts of kernels/attn/gqa/test_python.py:97-98). Asynchronous on `stream`
     (default: torch's current stream).
     """
+    strided = not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous())
     for name, t in (("q", q), ("k", k), ("v", v)):
-        _require_cuda_bf16(name, t, 4)
+        if strided:
+            if not isinstance(t, torch.Tensor) or t.device.type != "cuda" or t.dim() != 4:
+                raise RuntimeError(f"{name} must be a 4-D CUDA tensor")
+            if t.stride(3) != 1 or any(st <= 0 or st % 8 for st in t.stride()[:3]):
+                raise RuntimeError(f"{name}: the last dimension must be contiguous and the other strides positive "
+                                   "multiples of 8 elements")
+        else:
+            _require_cuda_bf16(name, t, 4)
         if t.dtype != torch.bfloat16:
             raise RuntimeError(f"{name} must be torch.bfloat16")
     b, n, h, d = q.shape
@@ -140,7 +153,7 @@ def attn_fwd(
     if k.shape != v.shape or k.shape[0] != b or k.shape[1] != n or k.shape[3] != d:
         raise RuntimeError("k/v must be [B, N, H_KV, D] matching q")
     if out is None:
-        out = torch.empty_like(q)
+        out = torch.empty((b, n, h, d), dtype=torch.bfloat16, device=q.device)
     if lse is None:
         lse = torch.empty((b, h, 1, n), dtype=torch.float32, device=q.device)
     if out.shape != q.shape or out.dtype != torch.bfloat16 or not out.is_contiguous():
@@ -148,9 +161,15 @@ def attn_fwd(
     if lse.shape != (b, h, 1, n) or lse.dtype != torch.float32 or not lse.is_contiguous():
         raise RuntimeError("lse must be a contiguous fp32 tensor [B, H, 1, N]")
     s = stream if stream is not None else torch.cuda.current_stream(q.device)
-    rc = capi().hk_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                            b, n, h, hkv, d, int(bool(causal)), float(softmax_scale or 0.0),
-                            q.device.index, s.cuda_stream)
+    if strided:
+        arr = lambda t: (ctypes.c_longlong * 3)(*t.stride()[:3])  # noqa: E731
+        rc = capi().hk_attn_fwd_strided(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                        b, n, h, hkv, d, arr(q), arr(k), arr(v), int(bool(causal)),
+                                        float(softmax_scale or 0.0), q.device.index, s.cuda_stream)
+    else:
+        rc = capi().hk_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                b, n, h, hkv, d, int(bool(causal)), float(softmax_scale or 0.0),
+                                q.device.index, s.cuda_stream)
     _check(rc, "hk_attn_fwd")
     return out, lse
 

@@ -16,7 +16,7 @@ import torch
 import torch.nn as nn
 from torch.autograd import Function
 
-from ._native import load_tk_kernel_fwd
+from ._native import attn_fwd, device_status, load_tk_kernel_fwd
 
 _fwd_modules = {}
 
@@ -25,6 +25,12 @@ def _tk_kernel_fwd(causal: bool):
     if causal not in _fwd_modules:
         _fwd_modules[causal] = load_tk_kernel_fwd(causal)
     return _fwd_modules[causal]
+
+
+def _tma_viewable(t: torch.Tensor) -> bool:
+    """bf16, last dimension contiguous, other strides positive multiples of 8 elements (16 bytes)."""
+    return (t.dtype == torch.bfloat16 and t.dim() == 4 and t.stride(3) == 1
+            and all(st > 0 and st % 8 == 0 for st in t.stride()[:3]))
 
 
 class HipAttnFunction(Function):
@@ -41,13 +47,22 @@ class HipAttnFunction(Function):
         assert q_bnhd.device == k_bnhd.device == v_bnhd.device, "All tensors must be on same device"
         assert H % HKV == 0, f"H ({H}) must be divisible by HKV ({HKV}) for GQA"
 
-        q = q_bnhd.to(torch.bfloat16).contiguous()
-        k = k_bnhd.to(torch.bfloat16).contiguous()
-        v = v_bnhd.to(torch.bfloat16).contiguous()
         O = torch.empty((B, N, H, D), dtype=torch.bfloat16, device=dev)
         L = torch.empty((B, H, 1, N), dtype=torch.float32, device=dev)
-
-        _tk_kernel_fwd(bool(causal)).dispatch_fwd(q, k, v, O, L, softmax_scale=softmax_scale)
+        if all(_tma_viewable(t) for t in (q_bnhd, k_bnhd, v_bnhd)) and not all(
+                t.is_contiguous() for t in (q_bnhd, k_bnhd, v_bnhd)):
+            # bf16 views of a packed projection (what qkv.unbind(2) gives): the kernel reads them through
+            # strided TMA descriptors, so the reference's three .contiguous() copies (hipkittens.py:37-39) go
+            q, k, v = q_bnhd, k_bnhd, v_bnhd
+            attn_fwd(q, k, v, causal=bool(causal), softmax_scale=softmax_scale, out=O, lse=L)
+            status = device_status(dev.index)  # blocks on the device like dispatch_fwd does
+            if status != 0:
+                raise RuntimeError(f"attention forward failed on the device (status {status})")
+        else:
+            q = q_bnhd.to(torch.bfloat16).contiguous()
+            k = k_bnhd.to(torch.bfloat16).contiguous()
+            v = v_bnhd.to(torch.bfloat16).contiguous()
+            _tk_kernel_fwd(bool(causal)).dispatch_fwd(q, k, v, O, L, softmax_scale=softmax_scale)
 
         ctx.save_for_backward(q, k, v, O, L)
         ctx.causal = bool(causal)

@@ -87,7 +87,7 @@ template <bool CAUSAL>
 __device__ __forceinline__ WorkItem decode_item(const FwdParams& p, int idx) {
   WorkItem w;
   const int G = p.H / p.H_KV;
-  const int NQB = p.N / kBlockM;
+  const int NQB = (p.N + kBlockM - 1) / kBlockM;  // the last block may be partial
   const int units = p.B * p.H_KV;
   int unit, qb0, qb1, h0, h1;
   if (p.pair_heads) {
@@ -274,6 +274,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
           for (int i = 0; i < kBlockN; ++i) su[i] = (i > row) ? 0xff800000u : su[i];
         }
+        if (!CAUSAL && j == nkv - 1 && (p.N & (kBlockN - 1)) != 0) {
+          // partial last tile: keys at or beyond N do not exist (TMA filled their rows with zeros)
+          const int rem = p.N - j * kBlockN;
+#pragma unroll
+          for (int i = 0; i < kBlockN; ++i) su[i] = (i >= rem) ? 0xff800000u : su[i];
+        }
 #if defined(HK_DEBUG_MINSOFTMAX)
         // timing experiment only: the shortest possible softmax stage (load S, store something as P)
 #pragma unroll
@@ -389,12 +395,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const int qrow = w.qb[slot] * kBlockM + row;
       const int head = w.head[slot];
       __nv_bfloat16* orow = p.o + ((static_cast<size_t>(w.b) * p.N + qrow) * p.H + head) * D;
+      const bool row_exists = qrow < p.N;  // rows of a partial last block beyond N are computed but not stored
 #pragma unroll
       for (int cc = 0; cc < D / 32; ++cc) {
         uint32_t o[32];
         tmem_ld32(tO + cc * 32, o);
         tmem_wait_ld();
         uint4* dst = reinterpret_cast<uint4*>(orow + cc * 32);
+        if (row_exists) {
 #pragma unroll
         for (int v4 = 0; v4 < 4; ++v4) {
           uint4 val;
@@ -404,8 +412,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           val.w = pack_bf16x2(__uint_as_float(o[v4 * 8 + 6]) * inv_l, __uint_as_float(o[v4 * 8 + 7]) * inv_l);
           dst[v4] = val;
         }
+        }
       }
-      p.lse[(static_cast<size_t>(w.b) * p.H + head) * p.N + qrow] = m * p.scale + __logf(l);
+      if (row_exists) p.lse[(static_cast<size_t>(w.b) * p.H + head) * p.N + qrow] = m * p.scale + __logf(l);
       // order this slot's TMEM reads before the next item's PV (published through p_full)
       tc_fence_before();
     }

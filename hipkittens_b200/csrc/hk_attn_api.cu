@@ -114,14 +114,16 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 
 // 4-D map over a contiguous bf16 [B, N, heads, D] tensor, box = 64 columns x 1 head x 128 rows,
 // 128-byte swizzle (rows of the box are 128 B, the layout tcgen05 descriptors expect).
-int make_bnhd_map(CUtensorMap* map, const void* base, int B, int N, int heads, int D) {
+// `st` = element strides of the batch, sequence and head dimensions (the D dimension is contiguous); every
+// stride must be a multiple of 8 elements (16 bytes), which TMA requires.
+int make_bnhd_map(CUtensorMap* map, const void* base, int B, int N, int heads, int D, const long long* st) {
   EncodeTiledFn enc = get_encode();
   if (!enc) {
     snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled not available from the driver");
     return HK_ECUDA;
   }
   cuuint64_t dims[4] = {cuuint64_t(D), cuuint64_t(heads), cuuint64_t(N), cuuint64_t(B)};
-  cuuint64_t strides[3] = {cuuint64_t(D) * 2, cuuint64_t(heads) * D * 2, cuuint64_t(N) * heads * D * 2};
+  cuuint64_t strides[3] = {cuuint64_t(st[2]) * 2, cuuint64_t(st[1]) * 2, cuuint64_t(st[0]) * 2};
   cuuint32_t box[4] = {64, 1, cuuint32_t(hk::kBlockM), 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
@@ -167,10 +169,24 @@ void hk_debug_set_trace(long long* buf) { g_trace_buf = buf; }
 
 int hk_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int N, int H, int H_KV,
                 int D, int causal, float softmax_scale, int device, void* cuda_stream) {
-  if (!q || !k || !v || !o || !lse) return HK_EINVAL;
+  const long long qs[3] = {(long long)N * H * D, (long long)H * D, D};
+  const long long ks[3] = {(long long)N * H_KV * D, (long long)H_KV * D, D};
+  return hk_attn_fwd_strided(q, k, v, o, lse, B, N, H, H_KV, D, qs, ks, ks, causal, softmax_scale, device, cuda_stream);
+}
+
+int hk_attn_fwd_strided(const void* q, const void* k, const void* v, void* o, float* lse, int B, int N, int H,
+                        int H_KV, int D, const long long* q_strides, const long long* k_strides,
+                        const long long* v_strides, int causal, float softmax_scale, int device,
+                        void* cuda_stream) {
+  if (!q || !k || !v || !o || !lse || !q_strides || !k_strides || !v_strides) return HK_EINVAL;
   if (B <= 0 || N <= 0 || H <= 0 || H_KV <= 0) return HK_EINVAL;
   if (D != 64 && D != 128) return HK_EUNSUPPORTED;
-  if (H % H_KV != 0 || N % hk::kBlockM != 0) return HK_EINVAL;
+  if (H % H_KV != 0) return HK_EINVAL;
+  for (int i = 0; i < 3; ++i) {
+    const long long s3[3] = {q_strides[i], k_strides[i], v_strides[i]};
+    for (long long st_i : s3)
+      if (st_i <= 0 || st_i % 8 != 0 || st_i >= (1ll << 39)) return HK_EINVAL;
+  }
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || (reinterpret_cast<uintptr_t>(lse) & 3))
     return HK_EINVAL;
   DeviceState* st = nullptr;
@@ -178,12 +194,12 @@ int hk_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse
   if (rc != HK_OK) return rc;
 
   CUtensorMap tq, tk, tv;
-  if ((rc = make_bnhd_map(&tq, q, B, N, H, D)) != HK_OK) return rc;
-  if ((rc = make_bnhd_map(&tk, k, B, N, H_KV, D)) != HK_OK) return rc;
-  if ((rc = make_bnhd_map(&tv, v, B, N, H_KV, D)) != HK_OK) return rc;
+  if ((rc = make_bnhd_map(&tq, q, B, N, H, D, q_strides)) != HK_OK) return rc;
+  if ((rc = make_bnhd_map(&tk, k, B, N, H_KV, D, k_strides)) != HK_OK) return rc;
+  if ((rc = make_bnhd_map(&tv, v, B, N, H_KV, D, v_strides)) != HK_OK) return rc;
 
   const int G = H / H_KV;
-  const int nqb = N / hk::kBlockM;
+  const int nqb = (N + hk::kBlockM - 1) / hk::kBlockM;
   hk::FwdParams p;
   p.o = static_cast<__nv_bfloat16*>(o);
   p.lse = lse;

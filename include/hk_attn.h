@@ -28,12 +28,23 @@ extern "C" {
  * kernels/attn/gqa_causal/kernel.cpp) and dispatch_fwd<D> (training/llama/csrc/attn_fwd_causal.cpp:624-630).
  *   q, o   : bf16 [B, N, H, D] contiguous          k, v : bf16 [B, N, H_KV, D] contiguous
  *   lse    : fp32 [B, H, 1, N] contiguous, natural-log logsumexp of the scaled logits
- *   D in {64, 128}; N a multiple of 128; H a multiple of H_KV; pointers 16-byte aligned.
+ *   D in {64, 128}; any N >= 1 (the reference needs a multiple of 256: kernels/attn/gqa/kernel.cpp:26,29,97);
+ *   H a multiple of H_KV; pointers 16-byte aligned.
  *   causal != 0 applies the lower-triangular mask; softmax_scale <= 0 selects 1/sqrt(D).
  * Shapes, causality and scale are compile-time constants in the reference; here they are arguments. */
 int hk_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
                 int B, int N, int H, int H_KV, int D, int causal, float softmax_scale,
                 int device, void* cuda_stream);
+
+/* Same forward for q, k, v that are strided views: q_strides / k_strides / v_strides are HOST arrays of three element
+ * strides (batch, sequence, head); the D dimension must be contiguous and every stride a multiple of 8 elements.
+ * This reads q, k, v straight out of a packed projection output ([B,N,3,H,D] or [B,N,2,H_KV,D]) without the
+ * `.contiguous()` copies the reference's call site makes (training/llama/llama/models/attentions/hipkittens.py:37-39,
+ * after mha.py:213-243 split the projection). o and lse are contiguous as in hk_attn_fwd. */
+int hk_attn_fwd_strided(const void* q, const void* k, const void* v, void* o, float* lse,
+                        int B, int N, int H, int H_KV, int D,
+                        const long long* q_strides, const long long* k_strides, const long long* v_strides,
+                        int causal, float softmax_scale, int device, void* cuda_stream);
 
 /* Paged-KV decode: one query token per sequence attends to its whole context. No counterpart exists in
  * the reference (its nearest relative is the contiguous cache update training/llama/llama/models/mha.py:16-42).

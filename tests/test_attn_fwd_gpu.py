@@ -53,6 +53,13 @@ SMALL = [
     (2, 256, 8, 8, 64, True),      # MHA, D=64, causal
     (1, 1024, 16, 2, 128, False),  # group of 8
     (3, 256, 12, 4, 64, False),    # group of 3 (q-block pairing under GQA)
+    # sequence lengths that are not a multiple of the 128-row tile (the reference cannot run these)
+    (2, 200, 4, 2, 128, False),
+    (1, 333, 8, 2, 64, True),
+    (2, 129, 2, 2, 128, True),
+    (1, 1000, 8, 1, 128, False),
+    (1, 1, 2, 1, 64, False),       # a single token
+    (1, 77, 3, 3, 64, True),
 ]
 
 
@@ -110,6 +117,31 @@ def test_autograd_function_forward(dev):
     q, k, v = make_prefill_inputs(1, 256, 8, 2, 64, seed=13)
     out = HipCrossAttention(causal=False)(q.to(dev), torch.stack([k, v], dim=2).to(dev))
     o_ref, _ = attn_fwd_oracle(q, k, v, False)
+    assert float((out.float().cpu() - o_ref.float()).abs().max()) <= TOL_O
+
+
+def test_strided_views_of_a_packed_projection(dev):
+    """q, k, v as views of [B,N,3,H,D] / [B,N,2,H_KV,D] (what mha.py:213-243 produces) give the same bits as
+    contiguous copies, without any copy being made."""
+    from hipkittens_b200.attention import HipCrossAttention, HipSelfAttention
+
+    gen = torch.Generator().manual_seed(21)
+    qkv = torch.randn((2, 384, 3, 4, 128), generator=gen).to(torch.bfloat16).to(dev)
+    q, k, v = qkv.unbind(dim=2)
+    assert not q.is_contiguous()
+    o_s, l_s = hk.attn_fwd(q, k, v, causal=True)
+    o_c, l_c = hk.attn_fwd(q.contiguous(), k.contiguous(), v.contiguous(), causal=True)
+    assert _native.device_status(0) == 0
+    assert torch.equal(o_s, o_c) and torch.equal(l_s, l_c)
+    o_ref, l_ref = attn_fwd_oracle(q.cpu(), k.cpu(), v.cpu(), True)
+    assert_parity(o_s.cpu(), l_s.cpu(), o_ref, l_ref)
+    out = HipSelfAttention(causal=True)(qkv)
+    assert torch.equal(out, o_c)
+    # GQA: q from its own projection, k/v views of a packed [B,N,2,H_KV,D]
+    qg = torch.randn((2, 256, 8, 64), generator=gen).to(torch.bfloat16).to(dev)
+    kv = torch.randn((2, 256, 2, 2, 64), generator=gen).to(torch.bfloat16).to(dev)
+    out = HipCrossAttention(causal=False)(qg, kv)
+    o_ref, _ = attn_fwd_oracle(qg.cpu(), kv[:, :, 0].cpu(), kv[:, :, 1].cpu(), False)
     assert float((out.float().cpu() - o_ref.float()).abs().max()) <= TOL_O
 
 

@@ -117,7 +117,7 @@ def test_added_shape_and_dtype_checks(mods):
 def test_c_abi_errors_surface_as_runtime_errors(mods):
     f = mods["micro"].dispatch_micro
     with pytest.raises(RuntimeError, match="invalid argument"):
-        f(*_five(N=192))  # N not a multiple of 128
+        f(*_five(H=3, HKV=2))  # H not a multiple of H_KV
     with pytest.raises(RuntimeError, match="unsupported"):
         f(*_five(D=32))
 

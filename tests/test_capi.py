@@ -45,11 +45,26 @@ def test_fwd_rejects_bad_arguments_before_cuda(native_built):
     assert _fwd(lib, q=None) == _native.HK_EINVAL
     assert _fwd(lib, l=None) == _native.HK_EINVAL
     assert _fwd(lib, q=72) == _native.HK_EINVAL  # not 16-byte aligned
-    assert _fwd(lib, N=100) == _native.HK_EINVAL  # N must be a multiple of 128
+    assert _fwd(lib, N=0) == _native.HK_EINVAL
     assert _fwd(lib, H=3, HKV=2) == _native.HK_EINVAL
     assert _fwd(lib, B=0) == _native.HK_EINVAL
     assert _fwd(lib, D=96) == _native.HK_EUNSUPPORTED
     assert _fwd(lib, D=256) == _native.HK_EUNSUPPORTED
+
+
+def test_strided_fwd_rejects_bad_strides_before_cuda(native_built):
+    lib = hk.capi()
+    arr = lambda *v: (ctypes.c_longlong * 3)(*v)  # noqa: E731
+
+    def call(qs, ks=None, vs=None):
+        ks = ks or arr(128 * 1 * 128, 128, 128)
+        vs = vs or ks
+        return lib.hk_attn_fwd_strided(64, 64, 64, 64, 64, 1, 128, 2, 1, 128, qs, ks, vs, 0, 0.0, 0, None)
+
+    assert call(arr(128 * 2 * 128, 2 * 128 + 4, 128)) == _native.HK_EINVAL  # not a multiple of 8 elements
+    assert call(arr(128 * 2 * 128, 0, 128)) == _native.HK_EINVAL
+    assert call(arr(128 * 2 * 128, 2 * 128, -128)) == _native.HK_EINVAL
+    assert call(None) == _native.HK_EINVAL
 
 
 def test_decode_rejects_bad_arguments_before_cuda(native_built):
