@@ -46,7 +46,7 @@ constexpr float kRescaleThresholdLog2 = 8.0f;
 #endif
 constexpr int kEmuMod = HK_EMU_MOD;   // of every kEmuMod column pairs ...
 constexpr int kEmuCnt = HK_EMU_CNT;   // ... this many compute exp2 with the polynomial instead of the MUFU
-constexpr uint64_t kWaitLimitNs = 8000ull * 1000 * 1000;  // SM cycles, > 4 s: far beyond any legitimate wait
+constexpr uint64_t kWaitLimitCycles = 8000ull * 1000 * 1000;  // SM cycles, > 4 s: far beyond any legitimate wait
 
 // Device status codes written to FwdParams::status (0 = OK).
 enum : int { kStatusOk = 0, kStatusTimeout = 1 };
@@ -251,7 +251,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       float m = 0.f, l = 0.f;
       for (int j = 0; j < nkv && ok; ++j) {
         HK_STAMP2(slot, 0);
-        ok = mbar_wait(&s_full[slot], s_cnt & 1, abortp, kWaitLimitNs);
+        ok = mbar_wait(&s_full[slot], s_cnt & 1, abortp, kWaitLimitCycles);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         ++s_cnt;
@@ -300,7 +300,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (kSepP && pv_cnt > 0) {
           // S(j) may be ready before O += P(j-1) V(j-1) has finished: wait for that product before
           // rescaling O or overwriting P
-          ok = mbar_wait(&p_free[slot], (pv_cnt - 1) & 1, abortp, kWaitLimitNs);
+          ok = mbar_wait(&p_free[slot], (pv_cnt - 1) & 1, abortp, kWaitLimitCycles);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
@@ -386,7 +386,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
       if (!ok) break;
       // ---- epilogue of this slot: O / l -> bf16, L = m*scale + ln(l)
-      ok = mbar_wait(&o_full[slot], o_cnt & 1, abortp, kWaitLimitNs);
+      ok = mbar_wait(&o_full[slot], o_cnt & 1, abortp, kWaitLimitCycles);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ++o_cnt;
@@ -432,7 +432,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       bool ok = true;
       auto push_kv = [&](const CUtensorMap* tm, int b, int kvh, int tile) -> bool {
         const int st = ring_st;
-        if (!mbar_wait(&kv_empty[st], ring_par ^ 1, abortp, kWaitLimitNs)) return false;
+        if (!mbar_wait(&kv_empty[st], ring_par ^ 1, abortp, kWaitLimitCycles)) return false;
         mbar_expect_tx(&kv_full[st], kTile);
         uint8_t* dst = sKV + st * kTile;
 #pragma unroll
@@ -453,7 +453,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const WorkItem w = decode_item<CAUSAL>(p, idx);
         for (int s = 0; s < 2 && ok; ++s) {
           if (w.n[s] == 0) continue;
-          ok = mbar_wait(&q_empty[s], (q_cnt[s] & 1) ^ 1, abortp, kWaitLimitNs);
+          ok = mbar_wait(&q_empty[s], (q_cnt[s] & 1) ^ 1, abortp, kWaitLimitCycles);
           if (!ok) break;
           ++q_cnt[s];
           mbar_expect_tx(&q_full[s], kTile);
@@ -544,8 +544,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const int n0 = w.n[0], n1 = w.n[1];
         const int nmax = max(n0, n1);
         // ---- first K tile: S = Q K0^T for both slots
-        ok = mbar_wait(&kv_full[ring_st], ring_par, abortp, kWaitLimitNs) &&
-             mbar_wait(&q_full[0], q_par[0], abortp, kWaitLimitNs);
+        ok = mbar_wait(&kv_full[ring_st], ring_par, abortp, kWaitLimitCycles) &&
+             mbar_wait(&q_full[0], q_par[0], abortp, kWaitLimitCycles);
         if (!ok) break;
         q_par[0] ^= 1;
         tc_fence_after();
@@ -553,7 +553,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         umma_commit(&s_full[0]);
         if (n0 == 1) umma_commit(&q_empty[0]);
         if (n1 > 0) {
-          ok = mbar_wait(&q_full[1], q_par[1], abortp, kWaitLimitNs);
+          ok = mbar_wait(&q_full[1], q_par[1], abortp, kWaitLimitCycles);
           if (!ok) break;
           q_par[1] ^= 1;
           tc_fence_after();
@@ -575,9 +575,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             const uint32_t par_k = ring_par;
             if (has_next) {
               ring_next();
-              ok = mbar_wait(&kv_full[st_k], par_k, abortp, kWaitLimitNs);
+              ok = mbar_wait(&kv_full[st_k], par_k, abortp, kWaitLimitCycles);
               if (ok && j + 1 < n0) {
-                ok = mbar_wait(&s_free[0], sf_par[0], abortp, kWaitLimitNs);
+                ok = mbar_wait(&s_free[0], sf_par[0], abortp, kWaitLimitCycles);
                 sf_par[0] ^= 1;
                 if (!ok) break;
                 tc_fence_after();
@@ -586,7 +586,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 if (j + 2 == n0) umma_commit(&q_empty[0]);
               }
               if (ok && j + 1 < n1) {
-                ok = mbar_wait(&s_free[1], sf_par[1], abortp, kWaitLimitNs);
+                ok = mbar_wait(&s_free[1], sf_par[1], abortp, kWaitLimitCycles);
                 sf_par[1] ^= 1;
                 if (!ok) break;
                 tc_fence_after();
@@ -597,9 +597,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               if (!ok) break;
               umma_commit(&kv_empty[st_k]);
             }
-            ok = mbar_wait(&kv_full[st_v], par_v, abortp, kWaitLimitNs);
+            ok = mbar_wait(&kv_full[st_v], par_v, abortp, kWaitLimitCycles);
             if (ok && j < n0) {
-              ok = mbar_wait(&p_full[0], p_par[0], abortp, kWaitLimitNs);
+              ok = mbar_wait(&p_full[0], p_par[0], abortp, kWaitLimitCycles);
               if (!ok) break;
               p_par[0] ^= 1;
               tc_fence_after();
@@ -608,7 +608,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               if (j + 1 == n0) umma_commit(&o_full[0]);
             }
             if (ok && j < n1) {
-              ok = mbar_wait(&p_full[1], p_par[1], abortp, kWaitLimitNs);
+              ok = mbar_wait(&p_full[1], p_par[1], abortp, kWaitLimitCycles);
               if (!ok) break;
               p_par[1] ^= 1;
               tc_fence_after();
@@ -622,18 +622,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         } else {
           // stages of V(0) and K(1)
           int st_v = ring_st;
-          ok = mbar_wait(&kv_full[st_v], ring_par, abortp, kWaitLimitNs);
+          ok = mbar_wait(&kv_full[st_v], ring_par, abortp, kWaitLimitCycles);
           ring_next();
           int st_k = ring_st;
           if (ok && nmax > 1) {
-            ok = mbar_wait(&kv_full[st_k], ring_par, abortp, kWaitLimitNs);
+            ok = mbar_wait(&kv_full[st_k], ring_par, abortp, kWaitLimitCycles);
             ring_next();
           }
           for (int j = 0; j < nmax && ok; ++j) {
             int nst_v = 0, nst_k = 0;
             // ---- slot 0
             if (j < n0) {
-              ok = mbar_wait(&p_full[0], p_par[0], abortp, kWaitLimitNs);
+              ok = mbar_wait(&p_full[0], p_par[0], abortp, kWaitLimitCycles);
               if (!ok) break;
               p_par[0] ^= 1;
               HK_STAMP(2, 12);
@@ -651,7 +651,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
             // ---- slot 1
             if (j < n1) {
-              ok = mbar_wait(&p_full[1], p_par[1], abortp, kWaitLimitNs);
+              ok = mbar_wait(&p_full[1], p_par[1], abortp, kWaitLimitCycles);
               if (!ok) break;
               p_par[1] ^= 1;
               HK_STAMP(2, 13);
@@ -661,11 +661,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             // next trip's tiles V(j+1), K(j+2): requested long ago, these waits normally pass at once
             if (j + 1 < nmax) {
               nst_v = ring_st;
-              ok = mbar_wait(&kv_full[nst_v], ring_par, abortp, kWaitLimitNs);
+              ok = mbar_wait(&kv_full[nst_v], ring_par, abortp, kWaitLimitCycles);
               ring_next();
               if (ok && j + 2 < nmax) {
                 nst_k = ring_st;
-                ok = mbar_wait(&kv_full[nst_k], ring_par, abortp, kWaitLimitNs);
+                ok = mbar_wait(&kv_full[nst_k], ring_par, abortp, kWaitLimitCycles);
                 ring_next();
               }
               if (!ok) break;
