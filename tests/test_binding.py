@@ -126,3 +126,31 @@ def test_c_abi_errors_surface_as_runtime_errors(mods):
 def test_no_silent_fallback_without_gpu(mods):
     with pytest.raises(RuntimeError, match="CUDA call failed"):
         mods["micro"].dispatch_micro(*_five())
+
+
+def test_harness_keeps_both_reference_argument_orders(native_built):
+    """kernels/attn/gqa/test_python.py takes B D H H_KV N causal, gqa_causal/test_python.py B N H H_KV causal D
+    (test_python.py:22-27 in each directory); the harnesses shipped beside the modules keep both."""
+    import importlib.util
+    import os
+    import sys
+
+    base = os.path.join(os.path.dirname(hk.__file__), "kernels", "attn")
+    got = {}
+    for d in ("gqa", "gqa_causal"):
+        path = os.path.join(base, d, "test_python.py")
+        sys_path = list(sys.path)
+        mods = {k: v for k, v in sys.modules.items() if k == "tk_kernel"}
+        try:
+            sys.modules.pop("tk_kernel", None)
+            spec = importlib.util.spec_from_file_location(f"harness_{d}", path)
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            got[d] = mod.parse(["x", "2", "64", "8", "4", "256", "1"]) if d == "gqa" else mod.parse(
+                ["x", "2", "256", "8", "4", "1", "64"])
+            assert os.path.exists(os.path.join(base, d, "Makefile"))
+        finally:
+            sys.path[:] = sys_path
+            sys.modules.pop("tk_kernel", None)
+            sys.modules.update(mods)
+    assert got["gqa"] == got["gqa_causal"] == {"B": 2, "D": 64, "H": 8, "H_KV": 4, "N": 256, "causal": 1}
