@@ -57,6 +57,7 @@ struct FwdParams {
   int B, N, H, H_KV;
   int n_items;          // number of work items (slot pairs)
   int pair_heads;       // 1: slots = two heads of one group at the same q block; 0: two q blocks of one head
+  int group_units;      // causal order: (batch, kv-head) units swept together, sized so their K/V fit in L2
   float scale;          // softmax scale
   float scale_log2;     // scale * log2(e)
   int* status;          // device word: first non-zero status wins
@@ -81,8 +82,10 @@ struct WorkItem {
 };
 
 // Work-item order. Non-causal: (batch, kv head) outermost so one unit's K/V stay in L2 while all of
-// its query tiles stream through. Causal: longest rows first (q block descending) so the tail of the
-// launch is made of short items, with the slot pairs that share a K/V prefix adjacent.
+// its query tiles stream through. Causal: units are swept in groups whose K/V fit in L2 together; inside
+// a group the longest rows come first (q block descending), with the slot pairs that share a K/V prefix
+// adjacent. (One sweep over all units at once keeps every unit's K/V live at the same time - 128 MB at
+// N = 8192 - and was measured to re-read K/V from HBM 2.6 times over.)
 template <bool CAUSAL>
 __device__ __forceinline__ WorkItem decode_item(const FwdParams& p, int idx) {
   WorkItem w;
@@ -94,10 +97,13 @@ __device__ __forceinline__ WorkItem decode_item(const FwdParams& p, int idx) {
     const int hp_n = G / 2;
     int qb, hp;
     if (CAUSAL) {
-      const int per_qb = units * hp_n;
-      qb = NQB - 1 - idx / per_qb;
-      const int rem = idx % per_qb;
-      unit = rem / hp_n;
+      const int U = p.group_units;
+      const int grp = min(idx / (U * hp_n * NQB), (units - 1) / U);
+      const int within = idx - grp * (U * hp_n * NQB);
+      const int per_qb = min(U, units - grp * U) * hp_n;
+      qb = NQB - 1 - within / per_qb;
+      const int rem = within % per_qb;
+      unit = grp * U + rem / hp_n;
       hp = rem % hp_n;
     } else {
       const int per_unit = hp_n * NQB;
@@ -113,10 +119,13 @@ __device__ __forceinline__ WorkItem decode_item(const FwdParams& p, int idx) {
     const int NQP = (NQB + 1) / 2;
     int qp, hg;
     if (CAUSAL) {
-      const int per_qp = units * G;
-      qp = NQP - 1 - idx / per_qp;
-      const int rem = idx % per_qp;
-      unit = rem / G;
+      const int U = p.group_units;
+      const int grp = min(idx / (U * G * NQP), (units - 1) / U);
+      const int within = idx - grp * (U * G * NQP);
+      const int per_qp = min(U, units - grp * U) * G;
+      qp = NQP - 1 - within / per_qp;
+      const int rem = within % per_qp;
+      unit = grp * U + rem / G;
       hg = rem % G;
     } else {
       const int per_unit = G * NQP;
