@@ -50,8 +50,9 @@ DEFAULT_WORKLOAD = "gqa_fwd_b16_n2048_h64_kv8_d128"
 NCU_TRAFFIC_BYTES = {
     # 4 x the B=4 capture (260.2 MB per launch; traffic grows with the (batch, kv-head) units)
     "gqa_fwd_b16_n2048_h64_kv8_d128": 4 * 260.2e6,
-    "gqa_causal_fwd_b4_n8192_h64_kv8_d128": None,
-    "mha_fwd_b16_n4096_h16_d64": None,
+    # metric captures of the full workloads (profiles/attn_fwd_kernel_causal_d128_and_mha_d64.md)
+    "gqa_causal_fwd_b4_n8192_h64_kv8_d128": 1.109e9 + 0.520e9,
+    "mha_fwd_b16_n4096_h16_d64": 0.404e9 + 0.118e9,
     # 14-sequence capture (280.26 MB for sum ctx 66 608) scaled by sum ctx to 275 479; split + combine
     "paged_decode_s64_ctx512_8192_h64_kv8_d128": (280.26e6 + 4.64e6) * 275479 / 66608,
 }
