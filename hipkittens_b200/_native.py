@@ -23,6 +23,7 @@ HK_OK, HK_EINVAL, HK_EUNSUPPORTED, HK_ECUDA, HK_ETIMEOUT, HK_EWORKSPACE, HK_EBAD
 EXPORTED_SYMBOLS = (
     "hk_attn_fwd",
     "hk_attn_fwd_strided",
+    "hk_attn_fwd_varlen",
     "hk_attn_paged_decode_workspace_bytes",
     "hk_attn_paged_decode",
     "hk_attn_paged_decode_static",
@@ -70,6 +71,8 @@ def capi() -> ctypes.CDLL:
     ll3 = ctypes.POINTER(ctypes.c_longlong)
     lib.hk_attn_fwd_strided.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ll3, ll3, ll3, ci, cf, ci, vp]
     lib.hk_attn_fwd_strided.restype = ci
+    lib.hk_attn_fwd_varlen.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ll3, ll3, ll3, vp, ci, cf, ci, vp]
+    lib.hk_attn_fwd_varlen.restype = ci
     lib.hk_attn_paged_decode_workspace_bytes.argtypes = [ci, ci, ci, ci, ci]
     lib.hk_attn_paged_decode_workspace_bytes.restype = ctypes.c_size_t
     lib.hk_attn_paged_decode.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cf, vp,
@@ -128,13 +131,15 @@ def attn_fwd(
     out: Optional[torch.Tensor] = None,
     lse: Optional[torch.Tensor] = None,
     stream: Optional[torch.cuda.Stream] = None,
+    kv_lens: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """O = softmax(scale q k^T) v and L = logsumexp(scale q k^T) on the GPU.
 
     q [B,N,H,D] bf16, k/v [B,N,H_KV,D] bf16 CUDA tensors, contiguous or strided views with a contiguous
     last dimension (e.g. slices of a packed qkv projection; no copy is made); returns O [B,N,H,D] bf16 and
     L [B,H,1,N] fp32 (the layouts of kernels/attn/gqa/test_python.py:97-98). Asynchronous on `stream`
-    (default: torch's current stream).
+    (default: torch's current stream). `kv_lens` (int32 [B], non-causal only) restricts batch element b to its
+    first kv_lens[b] keys, the reference's key_padding_mask (base.py:97-103).
     """
     strided = not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous())
     for name, t in (("q", q), ("k", k), ("v", v)):
@@ -161,7 +166,14 @@ def attn_fwd(
     if lse.shape != (b, h, 1, n) or lse.dtype != torch.float32 or not lse.is_contiguous():
         raise RuntimeError("lse must be a contiguous fp32 tensor [B, H, 1, N]")
     s = stream if stream is not None else torch.cuda.current_stream(q.device)
-    if strided:
+    if kv_lens is not None:
+        if kv_lens.dtype != torch.int32 or kv_lens.shape != (b,) or kv_lens.device != q.device:
+            raise RuntimeError("kv_lens must be an int32 tensor [B] on q's device")
+        arr = lambda t: (ctypes.c_longlong * 3)(*t.stride()[:3])  # noqa: E731
+        rc = capi().hk_attn_fwd_varlen(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                       b, n, h, hkv, d, arr(q), arr(k), arr(v), kv_lens.data_ptr(),
+                                       int(bool(causal)), float(softmax_scale or 0.0), q.device.index, s.cuda_stream)
+    elif strided:
         arr = lambda t: (ctypes.c_longlong * 3)(*t.stride()[:3])  # noqa: E731
         rc = capi().hk_attn_fwd_strided(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
                                         b, n, h, hkv, d, arr(q), arr(k), arr(v), int(bool(causal)),

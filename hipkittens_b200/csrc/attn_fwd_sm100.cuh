@@ -60,6 +60,7 @@ struct FwdParams {
   int group_units;      // causal order: (batch, kv-head) units swept together, sized so their K/V fit in L2
   float scale;          // softmax scale
   float scale_log2;     // scale * log2(e)
+  const int* kv_lens;   // optional device [B]: batch b attends to keys [0, kv_lens[b]) only (non-causal); null = N
   int* status;          // device word: first non-zero status wins
 #ifdef HK_TRACE
   long long* trace;     // [3 roles][4096] clock stamps of CTA 0 (debug builds only)
@@ -76,6 +77,7 @@ struct FwdSmem {
 
 struct WorkItem {
   int b, kvh;
+  int kv_len;  // keys this batch element attends to
   int head[2];
   int qb[2];
   int n[2];  // KV tiles each slot consumes (0 = slot unused)
@@ -144,8 +146,11 @@ __device__ __forceinline__ WorkItem decode_item(const FwdParams& p, int idx) {
   w.head[1] = w.kvh * G + h1;
   w.qb[0] = qb0;
   w.qb[1] = qb1;
-  w.n[0] = CAUSAL ? qb0 + 1 : NQB;
-  w.n[1] = (qb1 < NQB) ? (CAUSAL ? qb1 + 1 : NQB) : 0;
+  // key-padding lengths (non-causal only): tiles beyond the batch element's own length are never loaded
+  w.kv_len = (!CAUSAL && p.kv_lens) ? min(max(p.kv_lens[w.b], 1), p.N) : p.N;
+  const int n_kv = (w.kv_len + kBlockN - 1) / kBlockN;
+  w.n[0] = CAUSAL ? qb0 + 1 : n_kv;
+  w.n[1] = (qb1 < NQB) ? (CAUSAL ? qb1 + 1 : n_kv) : 0;
   return w;
 }
 
@@ -283,9 +288,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
           for (int i = 0; i < kBlockN; ++i) su[i] = (i > row) ? 0xff800000u : su[i];
         }
-        if (!CAUSAL && j == nkv - 1 && (p.N & (kBlockN - 1)) != 0) {
-          // partial last tile: keys at or beyond N do not exist (TMA filled their rows with zeros)
-          const int rem = p.N - j * kBlockN;
+        if (!CAUSAL && j == nkv - 1 && (w.kv_len & (kBlockN - 1)) != 0) {
+          // partial last tile: keys at or beyond the length are padding (or, beyond N, zeros filled by TMA)
+          const int rem = w.kv_len - j * kBlockN;
 #pragma unroll
           for (int i = 0; i < kBlockN; ++i) su[i] = (i >= rem) ? 0xff800000u : su[i];
         }

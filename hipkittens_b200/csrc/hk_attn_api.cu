@@ -178,6 +178,15 @@ int hk_attn_fwd_strided(const void* q, const void* k, const void* v, void* o, fl
                         int H_KV, int D, const long long* q_strides, const long long* k_strides,
                         const long long* v_strides, int causal, float softmax_scale, int device,
                         void* cuda_stream) {
+  return hk_attn_fwd_varlen(q, k, v, o, lse, B, N, H, H_KV, D, q_strides, k_strides, v_strides, nullptr, causal,
+                            softmax_scale, device, cuda_stream);
+}
+
+int hk_attn_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* lse, int B, int N, int H,
+                       int H_KV, int D, const long long* q_strides, const long long* k_strides,
+                       const long long* v_strides, const int32_t* kv_lens, int causal, float softmax_scale,
+                       int device, void* cuda_stream) {
+  if (kv_lens && causal) return HK_EUNSUPPORTED;
   if (!q || !k || !v || !o || !lse || !q_strides || !k_strides || !v_strides) return HK_EINVAL;
   if (B <= 0 || N <= 0 || H <= 0 || H_KV <= 0) return HK_EINVAL;
   if (D != 64 && D != 128) return HK_EUNSUPPORTED;
@@ -220,6 +229,7 @@ int hk_attn_fwd_strided(const void* q, const void* k, const void* v, void* o, fl
   p.n_items = p.pair_heads ? B * H_KV * (G / 2) * nqb : B * H_KV * G * ((nqb + 1) / 2);
   p.scale = softmax_scale > 0.f ? softmax_scale : 1.0f / std::sqrt(float(D));
   p.scale_log2 = p.scale * 1.4426950408889634f;
+  p.kv_lens = kv_lens;
   p.status = st->status;
 #ifdef HK_TRACE
   p.trace = g_trace_buf;

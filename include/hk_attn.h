@@ -46,6 +46,16 @@ int hk_attn_fwd_strided(const void* q, const void* k, const void* v, void* o, fl
                         const long long* q_strides, const long long* k_strides, const long long* v_strides,
                         int causal, float softmax_scale, int device, void* cuda_stream);
 
+/* Same forward with key padding: kv_lens is a DEVICE array int32 [B] (or NULL); batch element b attends to keys
+ * [0, kv_lens[b]) only, as the reference's PyTorch path does with key_padding_mask
+ * (training/llama/llama/models/attentions/base.py:97-103, used by training/bert through attention_mask). Lengths are
+ * clamped to [1, N]; all N query rows are still computed. Non-causal only (HK_EUNSUPPORTED with causal != 0); strides
+ * as in hk_attn_fwd_strided. KV tiles beyond a batch element's length are neither loaded nor multiplied. */
+int hk_attn_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* lse,
+                       int B, int N, int H, int H_KV, int D,
+                       const long long* q_strides, const long long* k_strides, const long long* v_strides,
+                       const int32_t* kv_lens, int causal, float softmax_scale, int device, void* cuda_stream);
+
 /* Paged-KV decode: one query token per sequence attends to its whole context. No counterpart exists in
  * the reference (its nearest relative is the contiguous cache update training/llama/llama/models/mha.py:16-42).
  *   q, o        : bf16 [S, 1, H, D]                 lse : fp32 [S, H, 1, 1]

@@ -73,8 +73,12 @@ def attn_fwd_oracle(
     v: torch.Tensor,
     causal: bool = False,
     softmax_scale: Optional[float] = None,
+    kv_lens: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """q [B,N,H,D], k/v [B,S,H_KV,D] (any float dtype; values are used as given, math in fp32).
+
+    ``kv_lens`` [B] restricts batch element b to its first kv_lens[b] keys: the reference's
+    ``key_padding_mask`` (``base.py:97-103``, True = keep), with masked logits at -inf instead of -10000.
 
     Returns O [B,N,H,D] bf16 and L [B,H,1,N] fp32. Work is chunked per (batch, kv-head) so that the
     largest benchmark shapes fit in host memory.
@@ -89,7 +93,9 @@ def attn_fwd_oracle(
     for bi in range(b):
         for kh in range(hkv):
             qg = q[bi, :, kh * g:(kh + 1) * g, :].float()
-            o_u, l_u = _unit(qg, k[bi, :, kh, :].float(), v[bi, :, kh, :].float(), scale, causal)
+            klen = k.shape[1] if kv_lens is None else int(kv_lens[bi])
+            assert kv_lens is None or not causal
+            o_u, l_u = _unit(qg, k[bi, :klen, kh, :].float(), v[bi, :klen, kh, :].float(), scale, causal)
             out[bi, :, kh * g:(kh + 1) * g, :] = o_u.to(torch.bfloat16)
             lse[bi, kh * g:(kh + 1) * g, 0, :] = l_u
     return out, lse

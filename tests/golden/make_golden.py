@@ -30,6 +30,8 @@ CASES = [
     ("b2_n128_h2_kv1_d128_causal", 2, 128, 2, 1, 128, True, 2),
     ("b1_n256_h2_kv2_d128_nc", 1, 256, 2, 2, 128, False, 3),
 ]
+# key-padding case: (name, B, N, H, H_KV, D, seed, kv_lens); run through CrossAttention's key_padding_mask
+PADDED = ("b3_n256_h4_kv2_d64_keypad", 3, 256, 4, 2, 64, 4, [256, 100, 129])
 
 
 def bf16_bits(t: torch.Tensor) -> np.ndarray:
@@ -70,6 +72,24 @@ def main() -> None:
         path = os.path.join(HERE, f"case_{name}.npz")
         np.savez_compressed(path, **out)
         print("wrote", path, os.path.getsize(path), "bytes")
+
+    name, b, n, h, hkv, d, seed, lens = PADDED
+    gen = torch.Generator().manual_seed(seed)
+    q = torch.randn((b, n, h, d), generator=gen).to(torch.bfloat16)
+    k = torch.randn((b, n, hkv, d), generator=gen).to(torch.bfloat16)
+    v = torch.randn((b, n, hkv, d), generator=gen).to(torch.bfloat16)
+    keep = torch.arange(n).view(1, n) < torch.tensor(lens).view(b, 1)  # True = keep (base.py:88-89)
+    with torch.no_grad():
+        o32 = CrossAttention(causal=False)(q.float(), torch.stack([k.float(), v.float()], dim=2), key_padding_mask=keep)
+        kk = k.double().repeat_interleave(h // hkv, dim=2)
+        scores = torch.einsum("bthd,bshd->bhts", q.double(), kk * (1.0 / math.sqrt(d)))
+        scores = scores.masked_fill(~keep.view(b, 1, 1, n), float("-inf"))
+        lse = torch.logsumexp(scores, dim=-1).numpy()
+    path = os.path.join(HERE, f"case_{name}.npz")
+    np.savez_compressed(path, q=bf16_bits(q), k=bf16_bits(k), v=bf16_bits(v), o_ref_fp32=o32.numpy().astype(np.float32),
+                        lse_def_fp64=lse, kv_lens=np.array(lens, dtype=np.int32),
+                        shape=np.array([b, n, h, hkv, d, 0, seed], dtype=np.int64))
+    print("wrote", path, os.path.getsize(path), "bytes")
 
 
 if __name__ == "__main__":

@@ -24,12 +24,12 @@ def dev():
     return torch.device("cuda:0")
 
 
-def run_fwd(q, k, v, causal, dev, scale=None):
+def run_fwd(q, k, v, causal, dev, scale=None, kv_lens=None):
     """Poison the outputs with NaN first so rows the kernel failed to write are caught."""
     b, n, h, d = q.shape
     o = torch.full((b, n, h, d), float("nan"), dtype=torch.bfloat16, device=dev)
     l = torch.full((b, h, 1, n), float("nan"), dtype=torch.float32, device=dev)
-    hk.attn_fwd(q.to(dev), k.to(dev), v.to(dev), causal=causal, softmax_scale=scale, out=o, lse=l)
+    hk.attn_fwd(q.to(dev), k.to(dev), v.to(dev), causal=causal, softmax_scale=scale, out=o, lse=l, kv_lens=kv_lens)
     assert _native.device_status(0) == 0
     return o.cpu(), l.cpu()
 
@@ -81,7 +81,8 @@ def test_parity_against_reference_module_outputs(dev, path):
     b, n, h, hkv, d, causal, _ = [int(x) for x in z["shape"]]
     bits = lambda a: torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16)  # noqa: E731
     q, k, v = bits(z["q"]), bits(z["k"]), bits(z["v"])
-    o, l = run_fwd(q, k, v, bool(causal), dev)
+    kv_lens = torch.from_numpy(z["kv_lens"]).to(dev) if "kv_lens" in z.files else None
+    o, l = run_fwd(q, k, v, bool(causal), dev, kv_lens=kv_lens)
     assert float((o.float() - torch.from_numpy(z["o_ref_fp32"])).abs().max()) <= TOL_O
     assert float((l[:, :, 0, :] - torch.from_numpy(z["lse_def_fp64"]).float()).abs().max()) <= TOL_L
 
@@ -143,6 +144,38 @@ def test_strided_views_of_a_packed_projection(dev):
     out = HipCrossAttention(causal=False)(qg, kv)
     o_ref, _ = attn_fwd_oracle(qg.cpu(), kv[:, :, 0].cpu(), kv[:, :, 1].cpu(), False)
     assert float((out.float().cpu() - o_ref.float()).abs().max()) <= TOL_O
+
+
+def test_key_padding_lengths(dev):
+    """Per-batch key lengths (the reference's key_padding_mask), including a length inside the first tile, one on a
+    tile boundary and the full length; whole KV tiles beyond a length are skipped by the kernel."""
+    q, k, v = make_prefill_inputs(4, 512, 8, 2, 128, seed=22)
+    lens = torch.tensor([512, 5, 256, 300], dtype=torch.int32)
+    o, l = run_fwd(q, k, v, False, dev, kv_lens=lens.to(dev))
+    o_ref, l_ref = attn_fwd_oracle(q, k, v, False, kv_lens=lens)
+    assert_parity(o, l, o_ref, l_ref)
+    # poisoning the padded keys must not change anything
+    k2, v2 = k.clone(), v.clone()
+    for b in range(4):
+        k2[b, int(lens[b]):] = 1e4
+        v2[b, int(lens[b]):] = -3e4  # finite: a padded key inside a loaded tile still meets p = 0 in the product
+    o2, l2 = run_fwd(q, k2, v2, False, dev, kv_lens=lens.to(dev))
+    assert torch.equal(o, o2) and torch.equal(l, l2)
+    with pytest.raises(RuntimeError):
+        hk.attn_fwd(q.to(dev), k.to(dev), v.to(dev), causal=True, kv_lens=lens.to(dev))
+
+
+def test_long_sequence_n16384(dev):
+    """The longest length of the reference's sweeps (analysis/attn/fwd/benchmark/mi355x_benchmark.sh:18)."""
+    q, k, v = make_prefill_inputs(1, 16384, 8, 1, 128, seed=23)
+    o, l = run_fwd(q, k, v, True, dev)
+    rows = slice(16384 - 256, 16384)
+    o_ref, l_ref = _band_oracle(q, k, v, True, rows)
+    assert float((o[0, rows].float() - o_ref[0].float()).abs().max()) <= TOL_O
+    assert float((l[0, :, 0, rows] - l_ref[0, :, 0]).abs().max()) <= TOL_L
+    rows = slice(0, 128)
+    o_ref, l_ref = _band_oracle(q, k, v, True, rows)
+    assert float((o[0, rows].float() - o_ref[0].float()).abs().max()) <= TOL_O
 
 
 def test_custom_softmax_scale(dev):

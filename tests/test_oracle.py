@@ -25,7 +25,7 @@ def _bf16(bits: np.ndarray) -> torch.Tensor:
 
 
 def test_golden_files_present():
-    assert len(GOLDEN) >= 4
+    assert len(GOLDEN) >= 5
 
 
 @pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
@@ -34,7 +34,8 @@ def test_oracle_matches_reference_module(path):
     b, n, h, hkv, d, causal, _seed = [int(x) for x in z["shape"]]
     q, k, v = _bf16(z["q"]), _bf16(z["k"]), _bf16(z["v"])
     assert q.shape == (b, n, h, d) and k.shape == (b, n, hkv, d)
-    o, lse = attn_fwd_oracle(q, k, v, causal=bool(causal))
+    kv_lens = torch.from_numpy(z["kv_lens"]) if "kv_lens" in z.files else None
+    o, lse = attn_fwd_oracle(q, k, v, causal=bool(causal), kv_lens=kv_lens)
     o_ref = torch.from_numpy(z["o_ref_fp32"])
     # The reference module run on fp32 copies computes the same math; the only difference left is the
     # oracle's final rounding of O to bf16 (half an ulp: 2^-9 relative).
