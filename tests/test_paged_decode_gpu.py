@@ -39,6 +39,7 @@ CASES = [
     (2, 2, 1, 300, 1030, 1100, 3),    # group 2, three chunks with a short tail
     (5, 4, 1, 64, 1, 16, 4),          # everything inside the first page
     (2, 64, 8, 1200, 8000, 8192, 5),  # the configuration's head counts at maximum context
+    (10, 16, 8, 5300, 6000, 8192, 6),  # enough CTAs for the launcher to pick 1024-token chunks
 ]
 
 
