@@ -54,7 +54,7 @@ NCU_TRAFFIC_BYTES = {
     "gqa_causal_fwd_b4_n8192_h64_kv8_d128": 1.109e9 + 0.520e9,
     "mha_fwd_b16_n4096_h16_d64": 0.404e9 + 0.118e9,
     # 14-sequence capture (280.26 MB for sum ctx 66 608) scaled by sum ctx to 275 479; split + combine
-    "paged_decode_s64_ctx512_8192_h64_kv8_d128": (280.26e6 + 4.64e6) * 275479 / 66608,
+    "paged_decode_s64_ctx512_8192_h64_kv8_d128": (273.46e6 + 4.73e6 + 2.47e6) * 275479 / 66608,
 }
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
