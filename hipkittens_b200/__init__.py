@@ -6,16 +6,22 @@ sm_100 device is present, calls raise.
 
 Public surface
 --------------
-* ``attn_fwd(q, k, v, causal=False, ...) -> (O, L)``, ``paged_decode(...) -> (O, L)`` and
-  ``paged_kv_append(...)``: torch-tensor front ends over the C ABI (ctypes).
+* ``attn_fwd(q, k, v, causal=False, ...) -> (O, L)``, ``attn_bwd_prep`` / ``attn_bwd`` / ``dq_shuffle`` (the
+  backward pass), ``paged_decode(...) -> (O, L)`` and ``paged_kv_append(...)``: torch-tensor front ends over
+  the C ABI (ctypes).
 * ``load_tk_kernel(causal)`` / ``load_tk_kernel_fwd(causal)``: the reference's extension modules
   (``tk_kernel.dispatch_micro``, ``tk_kernel_fwd.dispatch_fwd``) built for B200.
 * ``HipAttnFunction`` in :mod:`hipkittens_b200.attention`: the reference's autograd-function forward.
 """
 from ._native import (  # noqa: F401
+    HK_DQ_BHND,
+    HK_DQ_BNHD,
     HkError,
+    attn_bwd,
+    attn_bwd_prep,
     attn_fwd,
     capi,
+    dq_shuffle,
     kernel_launch_count,
     lib_path,
     load_tk_kernel,
@@ -26,9 +32,14 @@ from ._native import (  # noqa: F401
 )
 
 __all__ = [
+    "HK_DQ_BHND",
+    "HK_DQ_BNHD",
     "HkError",
+    "attn_bwd",
+    "attn_bwd_prep",
     "attn_fwd",
     "capi",
+    "dq_shuffle",
     "kernel_launch_count",
     "lib_path",
     "load_tk_kernel",

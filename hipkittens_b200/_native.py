@@ -24,6 +24,9 @@ EXPORTED_SYMBOLS = (
     "hk_attn_fwd",
     "hk_attn_fwd_strided",
     "hk_attn_fwd_varlen",
+    "hk_attn_bwd_prep",
+    "hk_attn_bwd",
+    "hk_attn_dq_shuffle",
     "hk_attn_paged_decode_workspace_bytes",
     "hk_attn_paged_decode",
     "hk_attn_paged_decode_static",
@@ -73,6 +76,12 @@ def capi() -> ctypes.CDLL:
     lib.hk_attn_fwd_strided.restype = ci
     lib.hk_attn_fwd_varlen.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ll3, ll3, ll3, vp, ci, cf, ci, vp]
     lib.hk_attn_fwd_varlen.restype = ci
+    lib.hk_attn_bwd_prep.argtypes = [vp, vp, vp, ci, ci, ci, ci, ci, vp]
+    lib.hk_attn_bwd_prep.restype = ci
+    lib.hk_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, cf, ci, ci, vp]
+    lib.hk_attn_bwd.restype = ci
+    lib.hk_attn_dq_shuffle.argtypes = [vp, vp, ci, ci, ci, ci, ci, vp]
+    lib.hk_attn_dq_shuffle.restype = ci
     lib.hk_attn_paged_decode_workspace_bytes.argtypes = [ci, ci, ci, ci, ci]
     lib.hk_attn_paged_decode_workspace_bytes.restype = ctypes.c_size_t
     lib.hk_attn_paged_decode.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cf, vp,
@@ -184,6 +193,96 @@ def attn_fwd(
                                 q.device.index, s.cuda_stream)
     _check(rc, "hk_attn_fwd")
     return out, lse
+
+
+HK_DQ_BNHD, HK_DQ_BHND = 0, 1
+
+
+def attn_bwd_prep(o: torch.Tensor, d_o: torch.Tensor, delta: Optional[torch.Tensor] = None,
+                  stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """delta [B,H,1,N] fp32 = rowsum(O * dO) for O, dO [B,N,H,D] bf16 (the reference's ``dispatch_prep``,
+    kernels/attn/gqa_backwards/attn_bkwd_prep.cpp:164-195)."""
+    for name, t in (("o", o), ("d_o", d_o)):
+        _require_cuda_bf16(name, t, 4)
+        if t.dtype != torch.bfloat16:
+            raise RuntimeError(f"{name} must be torch.bfloat16")
+    if o.shape != d_o.shape:
+        raise RuntimeError("o and d_o must have the same shape")
+    b, n, h, d = o.shape
+    if delta is None:
+        delta = torch.empty((b, h, 1, n), dtype=torch.float32, device=o.device)
+    if delta.shape != (b, h, 1, n) or delta.dtype != torch.float32 or not delta.is_contiguous():
+        raise RuntimeError("delta must be a contiguous fp32 tensor [B, H, 1, N]")
+    s = stream if stream is not None else torch.cuda.current_stream(o.device)
+    _check(capi().hk_attn_bwd_prep(o.data_ptr(), d_o.data_ptr(), delta.data_ptr(), b, n, h, d, o.device.index,
+                                   s.cuda_stream), "hk_attn_bwd_prep")
+    return delta
+
+
+def attn_bwd(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    d_o: torch.Tensor,
+    lse: torch.Tensor,
+    delta: torch.Tensor,
+    causal: bool = False,
+    softmax_scale: Optional[float] = None,
+    dq: Optional[torch.Tensor] = None,
+    dk: Optional[torch.Tensor] = None,
+    dv: Optional[torch.Tensor] = None,
+    dq_layout: int = HK_DQ_BNHD,
+    stream: Optional[torch.cuda.Stream] = None,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """dQ, dK, dV of the attention forward (the reference's ``dispatch_bwd_combined``,
+    kernels/attn/gqa_backwards/attn_bkwd_non_causal.cpp:37-49). q, d_o [B,N,H,D], k, v [B,N,H_KV,D] bf16;
+    lse, delta [B,H,1,N] fp32. dQ comes back as [B,N,H,D], or [B,H,N,D] with ``dq_layout=HK_DQ_BHND``
+    (the reference's pre-shuffle layout). N must be a multiple of 128."""
+    for name, t in (("q", q), ("k", k), ("v", v), ("d_o", d_o)):
+        _require_cuda_bf16(name, t, 4)
+        if t.dtype != torch.bfloat16:
+            raise RuntimeError(f"{name} must be torch.bfloat16")
+    b, n, h, d = q.shape
+    hkv = k.shape[2]
+    if k.shape != v.shape or k.shape[0] != b or k.shape[1] != n or k.shape[3] != d or d_o.shape != q.shape:
+        raise RuntimeError("k/v must be [B, N, H_KV, D] and d_o [B, N, H, D] matching q")
+    for name, t in (("lse", lse), ("delta", delta)):
+        if t.shape != (b, h, 1, n) or t.dtype != torch.float32 or not t.is_contiguous() or t.device != q.device:
+            raise RuntimeError(f"{name} must be a contiguous fp32 tensor [B, H, 1, N] on q's device")
+    dq_shape = (b, n, h, d) if dq_layout == HK_DQ_BNHD else (b, h, n, d)
+    if dq is None:
+        dq = torch.empty(dq_shape, dtype=torch.bfloat16, device=q.device)
+    if dk is None:
+        dk = torch.empty_like(k)
+    if dv is None:
+        dv = torch.empty_like(v)
+    for name, t, shp in (("dq", dq, dq_shape), ("dk", dk, tuple(k.shape)), ("dv", dv, tuple(v.shape))):
+        if tuple(t.shape) != tuple(shp) or t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise RuntimeError(f"{name} must be a contiguous bf16 tensor of shape {tuple(shp)}")
+    s = stream if stream is not None else torch.cuda.current_stream(q.device)
+    rc = capi().hk_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), d_o.data_ptr(), lse.data_ptr(),
+                            delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), b, n, h, hkv, d,
+                            int(bool(causal)), float(softmax_scale or 0.0), int(dq_layout), q.device.index,
+                            s.cuda_stream)
+    _check(rc, "hk_attn_bwd")
+    return dq, dk, dv
+
+
+def dq_shuffle(dq_bhnd: torch.Tensor, dq_bnhd: Optional[torch.Tensor] = None,
+               stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """[B,H,N,D] -> [B,N,H,D] (the reference's ``dispatch_dq_shuffle``, attn_bkwd_prep.cpp:199-223)."""
+    _require_cuda_bf16("dq_bhnd", dq_bhnd, 4)
+    b, h, n, d = dq_bhnd.shape
+    if dq_bnhd is None:
+        dq_bnhd = torch.empty((b, n, h, d), dtype=dq_bhnd.dtype, device=dq_bhnd.device)
+    if dq_bnhd.shape != (b, n, h, d) or dq_bnhd.dtype != dq_bhnd.dtype or not dq_bnhd.is_contiguous():
+        raise RuntimeError("dq_bnhd must be a contiguous tensor [B, N, H, D] of the source's dtype")
+    if dq_bhnd.dtype != torch.bfloat16:
+        raise RuntimeError("dq_bhnd must be torch.bfloat16")
+    s = stream if stream is not None else torch.cuda.current_stream(dq_bhnd.device)
+    _check(capi().hk_attn_dq_shuffle(dq_bhnd.data_ptr(), dq_bnhd.data_ptr(), b, n, h, d, dq_bhnd.device.index,
+                                     s.cuda_stream), "hk_attn_dq_shuffle")
+    return dq_bnhd
 
 
 def paged_decode_workspace_bytes(s: int, h: int, d: int, max_pages: int, page_size: int = 16) -> int:

@@ -1,0 +1,847 @@
+// bf16 grouped-query flash-attention backward for sm_100a (B200).
+//
+// Replaces the reference's three backward entry points: attend_prep_ker
+// (kernels/attn/gqa_backwards/attn_bkwd_prep.cpp:164-186, delta = rowsum(dO * O)),
+// attend_bwd_combined_ker (kernels/attn/gqa_backwards/attn_bkwd_non_causal.cpp:48-49 and
+// kernels/attn/gqa_causal_backwards/attn_bkwd_causal.cpp:50; dQ, dK, dV) and attend_dq_shuffle_ker
+// (attn_bkwd_prep.cpp:199-223, dQ [B,H,N,D] -> [B,N,H,D]).
+//
+// With P = exp(scale * Q K^T - L), dP = dO V^T and dS = P * (dP - delta):
+//     dV = P^T dO        dK = scale * dS^T Q        dQ = scale * dS K
+// The reference accumulates dQ with packed-bf16 atomic adds from the kernel that owns a K/V block. Here
+// nothing is accumulated across thread blocks: two kernels each own their outputs outright, which makes
+// every gradient bit-reproducible from run to run, at the price of computing S and dP twice.
+//   attn_bwd_dkdv_kernel  one K/V block of 128 keys stays in shared memory; the query tiles of all heads
+//                         of the group stream past it. Everything is computed transposed (S^T = K Q^T,
+//                         dP^T = V dO^T) so that the key index is the TMEM lane: P^T and dS^T are then
+//                         already in the A-operand position of dV += P^T dO and dK += dS^T Q.
+//   attn_bwd_dq_kernel    one query tile of 128 rows stays in shared memory; the K/V tiles stream past it:
+//                         S = Q K^T, dP = dO V^T, dQ += dS K.
+// Both kernels are persistent (one CTA per SM, 384 threads): warps 0-7 do the element-wise work (two
+// threads per TMEM lane, 64 columns each), warp 8 is the TMA producer, warp 9 issues the UMMAs.
+// The two score-shaped accumulators are overwritten in place by their bf16 successors (P over S, dS over
+// dP), each half-row thread writing into the columns it has just read.
+//
+// Sequence lengths must be a multiple of 128 (the reference's kernels need a multiple of 256).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "attn_fwd_sm100.cuh"
+#include "sm100_ptx.cuh"
+
+namespace hk {
+
+constexpr int kBwdThreads = 384;
+constexpr int kBwdRegsAtLaunch = 168;  // see the setmaxnreg calls; same budget as the forward kernel
+
+enum : int { kStatusSmemAlign = 3 };  // dynamic shared memory did not start on a 1024-byte boundary
+
+struct BwdParams {
+  const float* lse;     // [B,H,1,N] from the forward pass (natural log)
+  const float* delta;   // [B,H,1,N] rowsum(dO * O)
+  __nv_bfloat16* dq;    // written through the three strides below
+  __nv_bfloat16* dk;    // [B,N,H_KV,D]
+  __nv_bfloat16* dv;    // [B,N,H_KV,D]
+  long long dq_stride_b, dq_stride_n, dq_stride_h;  // elements; [B,N,H,D] or [B,H,N,D]
+  int B, N, H, H_KV;
+  int n_items;
+  int group_units;      // causal order: (batch, kv-head) units swept together (L2 residency)
+  float scale;
+  float scale_log2;
+  int* status;
+};
+
+template <int D>
+struct BwdSmem {
+  static constexpr int kTileBytes = kBlockM * D * 2;
+  static constexpr int kSubTileBytes = kBlockM * 128;
+  static constexpr int kRingA = (D == 128) ? 3 : 6;  // tiles that live for a whole iteration (Q resp. K)
+  static constexpr int kRingB = (D == 128) ? 2 : 4;  // tiles that are consumed early (dO resp. V)
+  static constexpr int kTiles = 2 + kRingA + kRingB;
+  static constexpr int kStatBytes = 2 * 2 * kBlockM * 4;  // two stages of (L, delta) for one query tile
+  static constexpr int kBarBytes = 512;
+  static constexpr int kDynBytes = kTiles * kTileBytes + kStatBytes + kBarBytes;
+};
+static_assert(BwdSmem<128>::kDynBytes <= 232448, "shared memory budget of one CTA");
+
+// ------------------------------------------------------------------------------------ delta = rowsum(dO * O)
+// One warp per (batch, position, head) row; memory-bound (reads O and dO once).
+// grid = ceil(B*N*H / 8), block = 256.
+template <int D>
+__global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o,
+                                                            const __nv_bfloat16* __restrict__ d_o,
+                                                            float* __restrict__ delta, int B, int N, int H) {
+  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const long long rows = static_cast<long long>(B) * N * H;
+  if (row >= rows) return;
+  constexpr int kPerLane = D / 32;  // 2 or 4 bf16 per lane
+  const __nv_bfloat16* po = o + row * D + lane * kPerLane;
+  const __nv_bfloat16* pd = d_o + row * D + lane * kPerLane;
+  float acc = 0.f;
+  if constexpr (kPerLane == 4) {
+    const uint2 a = *reinterpret_cast<const uint2*>(po);
+    const uint2 b = *reinterpret_cast<const uint2*>(pd);
+    const __nv_bfloat162 a0 = *reinterpret_cast<const __nv_bfloat162*>(&a.x);
+    const __nv_bfloat162 a1 = *reinterpret_cast<const __nv_bfloat162*>(&a.y);
+    const __nv_bfloat162 b0 = *reinterpret_cast<const __nv_bfloat162*>(&b.x);
+    const __nv_bfloat162 b1 = *reinterpret_cast<const __nv_bfloat162*>(&b.y);
+    acc = __low2float(a0) * __low2float(b0) + __high2float(a0) * __high2float(b0) +
+          __low2float(a1) * __low2float(b1) + __high2float(a1) * __high2float(b1);
+  } else {
+    const __nv_bfloat162 a0 = *reinterpret_cast<const __nv_bfloat162*>(po);
+    const __nv_bfloat162 b0 = *reinterpret_cast<const __nv_bfloat162*>(pd);
+    acc = __low2float(a0) * __low2float(b0) + __high2float(a0) * __high2float(b0);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) {
+    const long long bn = row / H;
+    const int h = static_cast<int>(row - bn * H);
+    const long long b = bn / N;
+    const int n = static_cast<int>(bn - b * N);
+    delta[(b * H + h) * N + n] = acc;
+  }
+}
+
+// ------------------------------------------------------------------------------------ dQ [B,H,N,D] -> [B,N,H,D]
+// Pure byte movement, 16 bytes per thread. grid = ceil(B*N*H*D/8 / 256), block = 256.
+__global__ void __launch_bounds__(256) attn_dq_shuffle_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                                              int B, int N, int H, int vec_per_row) {
+  const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  const long long total = static_cast<long long>(B) * N * H * vec_per_row;
+  if (idx >= total) return;
+  // idx enumerates the destination [B,N,H,vec]
+  const int v = static_cast<int>(idx % vec_per_row);
+  long long r = idx / vec_per_row;
+  const int h = static_cast<int>(r % H);
+  r /= H;
+  const int n = static_cast<int>(r % N);
+  const long long b = r / N;
+  dst[idx] = src[((b * H + h) * N + n) * vec_per_row + v];
+}
+
+// Dynamic shared memory of both main kernels: tiles first (1024-byte aligned for the 128-byte swizzle),
+// then the (L, delta) stages, then the mbarriers and two control words.
+
+// ------------------------------------------------------------------------------------ shared helpers
+// S-shaped product with both operands in shared memory, K-major, 128 B swizzle: d[128 x 128] = a * b^T
+// over D. `a_lo` / `b_lo` are descriptor low words of the two 128 x D tiles.
+template <int D>
+__device__ __forceinline__ void bwd_issue_ss(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo) {
+  constexpr uint32_t idesc = ptx::make_idesc_bf16(kBlockM, kBlockN, false);
+  constexpr uint32_t desc_hi = ptx::smem_desc_hi(1024);
+  constexpr uint32_t sub16 = BwdSmem<D>::kSubTileBytes >> 4;
+#pragma unroll
+  for (int k = 0; k < D / 16; ++k) {
+    const uint32_t off = (k / 4) * sub16 + (k % 4) * 2;  // 32 bytes per 16-element step inside a 128-byte row
+    ptx::umma_ss_lohi(d_tmem, a_lo + off, b_lo + off, desc_hi, idesc, k > 0 ? 1u : 0u);
+  }
+}
+// Gradient-shaped product: d[128 x D] (+)= a * b, a = bf16 [128 x 128] in TMEM (written by the two half-row
+// thread groups: 16-element steps 0-3 start at column 0, steps 4-7 at column 64 of the score buffer),
+// b = a 128 x D tile in shared memory read MN-major (its rows are the contraction index).
+template <int D>
+__device__ __forceinline__ void bwd_issue_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo_mn, bool acc) {
+  constexpr uint32_t idesc = ptx::make_idesc_bf16(kBlockM, D, true);
+  constexpr uint32_t desc_hi = ptx::smem_desc_hi(1024);
+#pragma unroll
+  for (int k = 0; k < kBlockN / 16; ++k)
+    ptx::umma_ts_lohi(d_tmem, a_tmem + (k / 4) * 64 + (k % 4) * 8, b_lo_mn + k * 128, desc_hi, idesc,
+                      (acc || k > 0) ? 1u : 0u);
+}
+
+// Accumulator rows (this thread's TMEM lane, D/2 columns from `taddr`) -> bf16 -> global, scaled.
+template <int D>
+__device__ __forceinline__ void bwd_store_half_row(uint32_t taddr, __nv_bfloat16* dst, float mul) {
+#pragma unroll
+  for (int cc = 0; cc < D / 64; ++cc) {
+    uint32_t o[32];
+    ptx::tmem_ld32(taddr + cc * 32, o);
+    ptx::tmem_wait_ld();
+    uint4* out = reinterpret_cast<uint4*>(dst + cc * 32);
+#pragma unroll
+    for (int v4 = 0; v4 < 4; ++v4) {
+      uint4 val;
+      val.x = ptx::pack_bf16x2(__uint_as_float(o[v4 * 8 + 0]) * mul, __uint_as_float(o[v4 * 8 + 1]) * mul);
+      val.y = ptx::pack_bf16x2(__uint_as_float(o[v4 * 8 + 2]) * mul, __uint_as_float(o[v4 * 8 + 3]) * mul);
+      val.z = ptx::pack_bf16x2(__uint_as_float(o[v4 * 8 + 4]) * mul, __uint_as_float(o[v4 * 8 + 5]) * mul);
+      val.w = ptx::pack_bf16x2(__uint_as_float(o[v4 * 8 + 6]) * mul, __uint_as_float(o[v4 * 8 + 7]) * mul);
+      out[v4] = val;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------ dK, dV
+struct DkdvItem {
+  int b, kvh, j;   // batch, kv head, key block
+  int cnt_i;       // query tiles per head this key block meets
+  int n_iter;      // heads of the group x query tiles
+};
+
+// Work order: one (batch, kv head) unit's key blocks are adjacent so that the CTAs running at the same
+// time read the same Q / dO tiles from L2. Causal: units are swept in L2-sized groups, key block 0 (the
+// longest) first inside a group.
+template <bool CAUSAL>
+__device__ __forceinline__ DkdvItem decode_dkdv_item(const BwdParams& p, int idx) {
+  DkdvItem w;
+  const int NB = p.N / kBlockN;
+  const int units = p.B * p.H_KV;
+  int unit;
+  if (CAUSAL) {
+    const int U = p.group_units;
+    const int grp = min(idx / (U * NB), (units - 1) / U);
+    const int within = idx - grp * (U * NB);
+    const int in_grp = min(U, units - grp * U);
+    w.j = within / in_grp;
+    unit = grp * U + within % in_grp;
+  } else {
+    unit = idx / NB;
+    w.j = idx % NB;
+  }
+  w.b = unit / p.H_KV;
+  w.kvh = unit % p.H_KV;
+  w.cnt_i = CAUSAL ? NB - w.j : NB;
+  w.n_iter = (p.H / p.H_KV) * w.cnt_i;
+  return w;
+}
+
+template <int D, bool CAUSAL>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                     const BwdParams p) {
+  using namespace ptx;
+  using SM = BwdSmem<D>;
+  constexpr int kTile = SM::kTileBytes;
+  constexpr int kSub = SM::kSubTileBytes;
+  constexpr int kChunks = D / 64;
+  constexpr int RA = SM::kRingA, RB = SM::kRingB;
+  enum { KV_FULL = 0, KV_EMPTY, ST_FULL, DP_FULL, P_FULL, DS_FULL, ACC_FULL, QA_FULL = 8, QA_EMPTY = 14,
+         RB_FULL = 20, RB_EMPTY = 24, STAT_FULL = 28, STAT_EMPTY = 30, CTRL = 32 };
+
+  extern __shared__ __align__(1024) uint8_t bwd_smem[];
+  uint8_t* sK = bwd_smem;
+  uint8_t* sV = bwd_smem + kTile;
+  uint8_t* sQ = bwd_smem + 2 * kTile;          // RA stages
+  uint8_t* sDO = sQ + RA * kTile;              // RB stages
+  float* sStat = reinterpret_cast<float*>(bwd_smem + SM::kTiles * kTile);  // [2 stages][L 128 | delta 128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(bwd_smem + SM::kTiles * kTile + SM::kStatBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + CTRL);
+  uint32_t* abort_word = tmem_slot + 1;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  if ((smem_u32(bwd_smem) & 1023u) != 0) {  // uniform over the CTA; nothing has been allocated yet
+    if (tid == 0) atomicCAS(p.status, kStatusOk, kStatusSmemAlign);
+    return;
+  }
+  if (tid == 0) {
+    *abort_word = 0;
+    mbar_init(bars + KV_FULL, 1);
+    mbar_init(bars + KV_EMPTY, 1);
+    mbar_init(bars + ST_FULL, 1);
+    mbar_init(bars + DP_FULL, 1);
+    mbar_init(bars + P_FULL, 8);   // one arrival per compute warp
+    mbar_init(bars + DS_FULL, 8);
+    mbar_init(bars + ACC_FULL, 1);
+    for (int s = 0; s < RA; ++s) {
+      mbar_init(bars + QA_FULL + s, 1);
+      mbar_init(bars + QA_EMPTY + s, 1);
+    }
+    for (int s = 0; s < RB; ++s) {
+      mbar_init(bars + RB_FULL + s, 1);
+      mbar_init(bars + RB_EMPTY + s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bars + STAT_FULL + s, 1);
+      mbar_init(bars + STAT_EMPTY + s, 8);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  volatile uint32_t* abortp = abort_word;
+  const int G = p.H / p.H_KV;
+  // TMEM columns: S^T [0,128)  dP^T [128,256)  dK [256,256+D)  dV [256+D,256+2D)
+  constexpr uint32_t cST = 0, cDP = 128, cDK = 256, cDV = 256 + D;
+
+  if (warp < 8) {
+    // ------------------------------------------------------------------ element-wise warps
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    const int hf = warp >> 2;                          // which 64 query columns of the tile
+    const int row = (warp & 3) * 32 + lane;            // key row inside the block == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + lane_addr + cST + hf * 64;
+    const uint32_t tP = tmem + lane_addr + cDP + hf * 64;
+    const float c = p.scale_log2;
+    constexpr float kNegLog2e = -1.4426950408889634f;
+    uint32_t it = 0, acc_cnt = 0;
+    bool ok = true;
+    for (int round = 0; ok; ++round) {
+      const int idx = item_for_round(round, blockIdx.x, gridDim.x);
+      if (idx >= p.n_items) {
+        if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
+        continue;
+      }
+      const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
+      for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
+        const bool diag = CAUSAL && (n % w.cnt_i == 0);  // the query tile at the key block's own position
+        const float* sL = sStat + (it & 1) * 256 + hf * 64;
+        const float* sDl = sL + 128;
+        // ---- P^T = exp2(S^T * c - L * log2(e))
+        ok = mbar_wait(bars + ST_FULL, it & 1, abortp, kWaitLimitCycles) &&
+             mbar_wait(bars + STAT_FULL + (it & 1), (it >> 1) & 1, abortp, kWaitLimitCycles);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t su[64];
+        tmem_ld32(tS, su);
+        tmem_ld32(tS + 32, su + 32);
+        tmem_wait_ld();
+#pragma unroll
+        for (int q4 = 0; q4 < 16; ++q4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(sL + q4 * 4);
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int col = q4 * 4 + e;
+            float pe = ex2_approx(fmaf(__uint_as_float(su[col]), c, lv[e] * kNegLog2e));
+            if (diag && (hf * 64 + col) < row) pe = 0.f;  // query earlier than the key
+            su[col] = __float_as_uint(pe);
+          }
+        }
+        {
+          uint32_t pk[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pk[i] = pack_bf16x2(__uint_as_float(su[2 * i]), __uint_as_float(su[2 * i + 1]));
+          tmem_st32(tS, pk);  // P^T over the first 32 columns this thread has just read
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + P_FULL);
+        // ---- dS^T = P^T * (dP^T - delta)
+        ok = mbar_wait(bars + DP_FULL, it & 1, abortp, kWaitLimitCycles);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        {
+          uint32_t du[64];
+          tmem_ld32(tP, du);
+          tmem_ld32(tP + 32, du + 32);
+          tmem_wait_ld();
+          uint32_t pk[32];
+#pragma unroll
+          for (int q4 = 0; q4 < 16; ++q4) {
+            const float4 d4 = *reinterpret_cast<const float4*>(sDl + q4 * 4);
+            const float ds0 = __uint_as_float(su[q4 * 4 + 0]) * (__uint_as_float(du[q4 * 4 + 0]) - d4.x);
+            const float ds1 = __uint_as_float(su[q4 * 4 + 1]) * (__uint_as_float(du[q4 * 4 + 1]) - d4.y);
+            const float ds2 = __uint_as_float(su[q4 * 4 + 2]) * (__uint_as_float(du[q4 * 4 + 2]) - d4.z);
+            const float ds3 = __uint_as_float(su[q4 * 4 + 3]) * (__uint_as_float(du[q4 * 4 + 3]) - d4.w);
+            pk[q4 * 2] = pack_bf16x2(ds0, ds1);
+            pk[q4 * 2 + 1] = pack_bf16x2(ds2, ds3);
+          }
+          tmem_st32(tP, pk);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bars + DS_FULL);
+          mbar_arrive(bars + STAT_EMPTY + (it & 1));
+        }
+      }
+      if (!ok) break;
+      // ---- epilogue: dK = scale * acc, dV = acc
+      ok = mbar_wait(bars + ACC_FULL, acc_cnt & 1, abortp, kWaitLimitCycles);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ++acc_cnt;
+      tc_fence_after();
+      const size_t off = ((static_cast<size_t>(w.b) * p.N + w.j * kBlockN + row) * p.H_KV + w.kvh) * D + hf * (D / 2);
+      bwd_store_half_row<D>(tmem + lane_addr + cDK + hf * (D / 2), p.dk + off, p.scale);
+      bwd_store_half_row<D>(tmem + lane_addr + cDV + hf * (D / 2), p.dv + off, 1.0f);
+      tc_fence_before();  // orders these reads before the next item's first dV product (published through P_FULL)
+    }
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+    if (warp == 8 && lane == 0) {
+      // ---------------- TMA producer
+      prefetch_tmap(&tmap_q);
+      prefetch_tmap(&tmap_k);
+      prefetch_tmap(&tmap_v);
+      prefetch_tmap(&tmap_do);
+      uint32_t item_cnt = 0, it = 0;
+      int qa = 0, rb = 0;
+      uint32_t qa_par = 0, rb_par = 0;
+      bool ok = true;
+      for (int round = 0; ok; ++round) {
+        const int idx = item_for_round(round, blockIdx.x, gridDim.x);
+        if (idx >= p.n_items) {
+          if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
+          continue;
+        }
+        const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
+        ok = mbar_wait(bars + KV_EMPTY, (item_cnt & 1) ^ 1, abortp, kWaitLimitCycles);
+        if (!ok) break;
+        ++item_cnt;
+        mbar_expect_tx(bars + KV_FULL, 2 * kTile);
+#pragma unroll
+        for (int ch = 0; ch < kChunks; ++ch) {
+          tma_load_4d(sK + ch * kSub, &tmap_k, bars + KV_FULL, ch * 64, w.kvh, w.j * kBlockN, w.b);
+          tma_load_4d(sV + ch * kSub, &tmap_v, bars + KV_FULL, ch * 64, w.kvh, w.j * kBlockN, w.b);
+        }
+        for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
+          const int head = w.kvh * G + n / w.cnt_i;
+          const int i = (CAUSAL ? w.j : 0) + n % w.cnt_i;
+          ok = mbar_wait(bars + QA_EMPTY + qa, qa_par ^ 1, abortp, kWaitLimitCycles);
+          if (!ok) break;
+          mbar_expect_tx(bars + QA_FULL + qa, kTile);
+#pragma unroll
+          for (int ch = 0; ch < kChunks; ++ch)
+            tma_load_4d(sQ + qa * kTile + ch * kSub, &tmap_q, bars + QA_FULL + qa, ch * 64, head, i * kBlockM, w.b);
+          if (++qa == RA) {
+            qa = 0;
+            qa_par ^= 1;
+          }
+          const int ss = it & 1;
+          ok = mbar_wait(bars + STAT_EMPTY + ss, ((it >> 1) & 1) ^ 1, abortp, kWaitLimitCycles);
+          if (!ok) break;
+          mbar_expect_tx(bars + STAT_FULL + ss, 2 * kBlockM * 4);
+          const size_t soff = (static_cast<size_t>(w.b) * p.H + head) * p.N + static_cast<size_t>(i) * kBlockM;
+          bulk_load_1d(sStat + ss * 256, p.lse + soff, kBlockM * 4, bars + STAT_FULL + ss);
+          bulk_load_1d(sStat + ss * 256 + 128, p.delta + soff, kBlockM * 4, bars + STAT_FULL + ss);
+          ok = mbar_wait(bars + RB_EMPTY + rb, rb_par ^ 1, abortp, kWaitLimitCycles);
+          if (!ok) break;
+          mbar_expect_tx(bars + RB_FULL + rb, kTile);
+#pragma unroll
+          for (int ch = 0; ch < kChunks; ++ch)
+            tma_load_4d(sDO + rb * kTile + ch * kSub, &tmap_do, bars + RB_FULL + rb, ch * 64, head, i * kBlockM, w.b);
+          if (++rb == RB) {
+            rb = 0;
+            rb_par ^= 1;
+          }
+        }
+      }
+    } else if (warp == 9 && lane == 0) {
+      // ---------------- UMMA issuer
+      // Per iteration: dV += P^T dO, S^T(next), dK += dS^T Q, dP^T(next). The two chains S^T -> P^T -> dV and
+      // dP^T -> dS^T -> dK interleave, so the pipe works on one while the element-wise warps finish the other.
+      constexpr uint32_t tile16 = kTile >> 4;
+      const uint32_t k_lo = smem_desc_lo(smem_u32(sK), 16);
+      const uint32_t v_lo = smem_desc_lo(smem_u32(sV), 16);
+      const uint32_t q_lo0 = smem_desc_lo(smem_u32(sQ), 16);       // K-major view (B of S^T)
+      const uint32_t q_mn0 = smem_desc_lo(smem_u32(sQ), kSub);     // MN-major view (B of dK)
+      const uint32_t do_lo0 = smem_desc_lo(smem_u32(sDO), 16);
+      const uint32_t do_mn0 = smem_desc_lo(smem_u32(sDO), kSub);
+      uint32_t item_cnt = 0, it = 0;
+      int qa = 0, rb = 0;
+      uint32_t qa_par = 0, rb_par = 0;
+      bool ok = true;
+      for (int round = 0; ok; ++round) {
+        const int idx = item_for_round(round, blockIdx.x, gridDim.x);
+        if (idx >= p.n_items) {
+          if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
+          continue;
+        }
+        const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
+        ok = mbar_wait(bars + KV_FULL, item_cnt & 1, abortp, kWaitLimitCycles) &&
+             mbar_wait(bars + QA_FULL + qa, qa_par, abortp, kWaitLimitCycles);
+        if (!ok) break;
+        ++item_cnt;
+        tc_fence_after();
+        bwd_issue_ss<D>(tmem + cST, k_lo, q_lo0 + qa * tile16);
+        umma_commit(bars + ST_FULL);
+        ok = mbar_wait(bars + RB_FULL + rb, rb_par, abortp, kWaitLimitCycles);
+        if (!ok) break;
+        tc_fence_after();
+        bwd_issue_ss<D>(tmem + cDP, v_lo, do_lo0 + rb * tile16);
+        umma_commit(bars + DP_FULL);
+        for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
+          const int cur_q = qa, cur_do = rb;
+          if (++qa == RA) {
+            qa = 0;
+            qa_par ^= 1;
+          }
+          if (++rb == RB) {
+            rb = 0;
+            rb_par ^= 1;
+          }
+          const bool more = (n + 1 < w.n_iter);
+          ok = mbar_wait(bars + P_FULL, it & 1, abortp, kWaitLimitCycles);
+          if (!ok) break;
+          tc_fence_after();
+          bwd_issue_ts<D>(tmem + cDV, tmem + cST, do_mn0 + cur_do * tile16, n > 0);
+          umma_commit(bars + RB_EMPTY + cur_do);
+          if (more) {
+            ok = mbar_wait(bars + QA_FULL + qa, qa_par, abortp, kWaitLimitCycles);
+            if (!ok) break;
+            tc_fence_after();
+            bwd_issue_ss<D>(tmem + cST, k_lo, q_lo0 + qa * tile16);
+            umma_commit(bars + ST_FULL);
+          }
+          ok = mbar_wait(bars + DS_FULL, it & 1, abortp, kWaitLimitCycles);
+          if (!ok) break;
+          tc_fence_after();
+          bwd_issue_ts<D>(tmem + cDK, tmem + cDP, q_mn0 + cur_q * tile16, n > 0);
+          umma_commit(bars + QA_EMPTY + cur_q);
+          if (more) {
+            ok = mbar_wait(bars + RB_FULL + rb, rb_par, abortp, kWaitLimitCycles);
+            if (!ok) break;
+            tc_fence_after();
+            bwd_issue_ss<D>(tmem + cDP, v_lo, do_lo0 + rb * tile16);
+            umma_commit(bars + DP_FULL);
+          }
+        }
+        if (!ok) break;
+        umma_commit(bars + ACC_FULL);
+        umma_commit(bars + KV_EMPTY);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_word != 0) {
+    // Give copies and MMAs that are still in flight time to land before TMEM and shared memory go away.
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 2000000ull) {
+    }
+    if (tid == 0) atomicCAS(p.status, kStatusOk, kStatusTimeout);
+    __syncthreads();
+  }
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------ dQ
+struct DqItem {
+  int b, h, kvh, i;  // batch, query head, its kv head, query tile
+  int n_iter;        // key tiles this query tile meets
+};
+
+// Work order: the query tiles of one (batch, kv head) unit are adjacent so that concurrently running CTAs
+// stream the same K / V tiles from L2. Causal: L2-sized groups of units, last query tile (the longest) first.
+template <bool CAUSAL>
+__device__ __forceinline__ DqItem decode_dq_item(const BwdParams& p, int idx) {
+  DqItem w;
+  const int NB = p.N / kBlockM;
+  const int G = p.H / p.H_KV;
+  const int units = p.B * p.H_KV;
+  int unit, g;
+  if (CAUSAL) {
+    const int U = p.group_units;
+    const int grp = min(idx / (U * G * NB), (units - 1) / U);
+    const int within = idx - grp * (U * G * NB);
+    const int in_grp = min(U, units - grp * U) * G;
+    w.i = NB - 1 - within / in_grp;
+    const int rem = within % in_grp;
+    unit = grp * U + rem / G;
+    g = rem % G;
+  } else {
+    const int per_unit = G * NB;
+    unit = idx / per_unit;
+    const int rem = idx % per_unit;
+    g = rem / NB;
+    w.i = rem % NB;
+  }
+  w.b = unit / p.H_KV;
+  w.kvh = unit % p.H_KV;
+  w.h = w.kvh * G + g;
+  w.n_iter = CAUSAL ? w.i + 1 : NB;
+  return w;
+}
+
+template <int D, bool CAUSAL>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                   const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                   const BwdParams p) {
+  using namespace ptx;
+  using SM = BwdSmem<D>;
+  constexpr int kTile = SM::kTileBytes;
+  constexpr int kSub = SM::kSubTileBytes;
+  constexpr int kChunks = D / 64;
+  constexpr int RA = SM::kRingA, RB = SM::kRingB;
+  enum { QDO_FULL = 0, QDO_EMPTY, S_FULL0, S_FULL1, DP_FULL, DS_FULL, DQ_FULL, KA_FULL = 8, KA_EMPTY = 14,
+         VB_FULL = 20, VB_EMPTY = 24, CTRL = 32 };
+
+  extern __shared__ __align__(1024) uint8_t bwd_smem[];
+  uint8_t* sQ = bwd_smem;
+  uint8_t* sDO = bwd_smem + kTile;
+  uint8_t* sK = bwd_smem + 2 * kTile;   // RA stages
+  uint8_t* sV = sK + RA * kTile;        // RB stages
+  uint64_t* bars = reinterpret_cast<uint64_t*>(bwd_smem + SM::kTiles * kTile + SM::kStatBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + CTRL);
+  uint32_t* abort_word = tmem_slot + 1;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  if ((smem_u32(bwd_smem) & 1023u) != 0) {
+    if (tid == 0) atomicCAS(p.status, kStatusOk, kStatusSmemAlign);
+    return;
+  }
+  if (tid == 0) {
+    *abort_word = 0;
+    mbar_init(bars + QDO_FULL, 1);
+    mbar_init(bars + QDO_EMPTY, 1);
+    mbar_init(bars + S_FULL0, 1);
+    mbar_init(bars + S_FULL1, 1);
+    mbar_init(bars + DP_FULL, 1);
+    mbar_init(bars + DS_FULL, 8);
+    mbar_init(bars + DQ_FULL, 1);
+    for (int s = 0; s < RA; ++s) {
+      mbar_init(bars + KA_FULL + s, 1);
+      mbar_init(bars + KA_EMPTY + s, 1);
+    }
+    for (int s = 0; s < RB; ++s) {
+      mbar_init(bars + VB_FULL + s, 1);
+      mbar_init(bars + VB_EMPTY + s, 1);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  volatile uint32_t* abortp = abort_word;
+  // TMEM columns: S (even iterations) [0,128)  dP [128,256)  dQ [256,256+D)  S (odd iterations) [384,512)
+  constexpr uint32_t cS0 = 0, cDP = 128, cDQ = 256, cS1 = 384;
+
+  if (warp < 8) {
+    // ------------------------------------------------------------------ element-wise warps
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    const int hf = warp >> 2;                          // which 64 key columns of the tile
+    const int row = (warp & 3) * 32 + lane;            // query row inside the tile == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tP = tmem + lane_addr + cDP + hf * 64;
+    const float c = p.scale_log2;
+    uint32_t it = 0, s_cnt0 = 0, s_cnt1 = 0, dq_cnt = 0;
+    bool ok = true;
+    for (int round = 0; ok; ++round) {
+      const int idx = item_for_round(round, blockIdx.x, gridDim.x);
+      if (idx >= p.n_items) {
+        if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
+        continue;
+      }
+      const DqItem w = decode_dq_item<CAUSAL>(p, idx);
+      const size_t srow = (static_cast<size_t>(w.b) * p.H + w.h) * p.N + static_cast<size_t>(w.i) * kBlockM + row;
+      const float nl = p.lse[srow] * -1.4426950408889634f;
+      const float dl = p.delta[srow];
+      for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
+        const int buf = n & 1;
+        const bool diag = CAUSAL && (n == w.n_iter - 1);
+        ok = mbar_wait(bars + S_FULL0 + buf, (buf ? s_cnt1 : s_cnt0) & 1, abortp, kWaitLimitCycles);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (buf) ++s_cnt1; else ++s_cnt0;
+        tc_fence_after();
+        uint32_t su[64];
+        const uint32_t tS = tmem + lane_addr + (buf ? cS1 : cS0) + hf * 64;
+        tmem_ld32(tS, su);
+        tmem_ld32(tS + 32, su + 32);
+        tmem_wait_ld();
+#pragma unroll
+        for (int col = 0; col < 64; ++col) {
+          float pe = ex2_approx(fmaf(__uint_as_float(su[col]), c, nl));
+          if (diag && (hf * 64 + col) > row) pe = 0.f;  // key later than the query
+          su[col] = __float_as_uint(pe);
+        }
+        ok = mbar_wait(bars + DP_FULL, it & 1, abortp, kWaitLimitCycles);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        {
+          uint32_t du[64];
+          tmem_ld32(tP, du);
+          tmem_ld32(tP + 32, du + 32);
+          tmem_wait_ld();
+          uint32_t pk[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float ds0 = __uint_as_float(su[2 * i]) * (__uint_as_float(du[2 * i]) - dl);
+            const float ds1 = __uint_as_float(su[2 * i + 1]) * (__uint_as_float(du[2 * i + 1]) - dl);
+            pk[i] = pack_bf16x2(ds0, ds1);
+          }
+          tmem_st32(tP, pk);  // dS over the first 32 columns this thread has just read
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + DS_FULL);
+      }
+      if (!ok) break;
+      // ---- epilogue: dQ = scale * acc
+      ok = mbar_wait(bars + DQ_FULL, dq_cnt & 1, abortp, kWaitLimitCycles);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ++dq_cnt;
+      tc_fence_after();
+      __nv_bfloat16* dst = p.dq + w.b * p.dq_stride_b + (static_cast<long long>(w.i) * kBlockM + row) * p.dq_stride_n +
+                           w.h * p.dq_stride_h + hf * (D / 2);
+      bwd_store_half_row<D>(tmem + lane_addr + cDQ + hf * (D / 2), dst, p.scale);
+      tc_fence_before();  // orders these reads before the next item's first dQ product (published through DS_FULL)
+    }
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+    if (warp == 8 && lane == 0) {
+      // ---------------- TMA producer
+      prefetch_tmap(&tmap_q);
+      prefetch_tmap(&tmap_k);
+      prefetch_tmap(&tmap_v);
+      prefetch_tmap(&tmap_do);
+      uint32_t item_cnt = 0;
+      int ka = 0, vb = 0;
+      uint32_t ka_par = 0, vb_par = 0;
+      bool ok = true;
+      for (int round = 0; ok; ++round) {
+        const int idx = item_for_round(round, blockIdx.x, gridDim.x);
+        if (idx >= p.n_items) {
+          if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
+          continue;
+        }
+        const DqItem w = decode_dq_item<CAUSAL>(p, idx);
+        ok = mbar_wait(bars + QDO_EMPTY, (item_cnt & 1) ^ 1, abortp, kWaitLimitCycles);
+        if (!ok) break;
+        ++item_cnt;
+        mbar_expect_tx(bars + QDO_FULL, 2 * kTile);
+#pragma unroll
+        for (int ch = 0; ch < kChunks; ++ch) {
+          tma_load_4d(sQ + ch * kSub, &tmap_q, bars + QDO_FULL, ch * 64, w.h, w.i * kBlockM, w.b);
+          tma_load_4d(sDO + ch * kSub, &tmap_do, bars + QDO_FULL, ch * 64, w.h, w.i * kBlockM, w.b);
+        }
+        for (int n = 0; n < w.n_iter && ok; ++n) {
+          ok = mbar_wait(bars + KA_EMPTY + ka, ka_par ^ 1, abortp, kWaitLimitCycles);
+          if (!ok) break;
+          mbar_expect_tx(bars + KA_FULL + ka, kTile);
+#pragma unroll
+          for (int ch = 0; ch < kChunks; ++ch)
+            tma_load_4d(sK + ka * kTile + ch * kSub, &tmap_k, bars + KA_FULL + ka, ch * 64, w.kvh, n * kBlockN, w.b);
+          if (++ka == RA) {
+            ka = 0;
+            ka_par ^= 1;
+          }
+          ok = mbar_wait(bars + VB_EMPTY + vb, vb_par ^ 1, abortp, kWaitLimitCycles);
+          if (!ok) break;
+          mbar_expect_tx(bars + VB_FULL + vb, kTile);
+#pragma unroll
+          for (int ch = 0; ch < kChunks; ++ch)
+            tma_load_4d(sV + vb * kTile + ch * kSub, &tmap_v, bars + VB_FULL + vb, ch * 64, w.kvh, n * kBlockN, w.b);
+          if (++vb == RB) {
+            vb = 0;
+            vb_par ^= 1;
+          }
+        }
+      }
+    } else if (warp == 9 && lane == 0) {
+      // ---------------- UMMA issuer
+      // Order: S(0) dP(0) S(1) | dQ(n) dP(n+1) S(n+2) | ... S alternates between two TMEM buffers, so S(n+1) is
+      // complete long before the element-wise warps finish tile n; dP(n+1) and dQ(n) share columns (dS(n) sits
+      // in the dP buffer) and simply follow each other in the pipe.
+      constexpr uint32_t tile16 = kTile >> 4;
+      const uint32_t q_lo = smem_desc_lo(smem_u32(sQ), 16);
+      const uint32_t do_lo = smem_desc_lo(smem_u32(sDO), 16);
+      const uint32_t k_lo0 = smem_desc_lo(smem_u32(sK), 16);      // K-major view (B of S)
+      const uint32_t k_mn0 = smem_desc_lo(smem_u32(sK), kSub);    // MN-major view (B of dQ)
+      const uint32_t v_lo0 = smem_desc_lo(smem_u32(sV), 16);
+      uint32_t item_cnt = 0, it = 0;
+      int ks = 0, kq = 0, vb = 0;            // K stage of the next S, K stage of the next dQ, V stage of the next dP
+      uint32_t ks_par = 0, vb_par = 0;
+      bool ok = true;
+      auto issue_s = [&](int buf) -> bool {
+        if (!mbar_wait(bars + KA_FULL + ks, ks_par, abortp, kWaitLimitCycles)) return false;
+        tc_fence_after();
+        bwd_issue_ss<D>(tmem + (buf ? cS1 : cS0), q_lo, k_lo0 + ks * tile16);
+        umma_commit(bars + S_FULL0 + buf);
+        if (++ks == RA) {
+          ks = 0;
+          ks_par ^= 1;
+        }
+        return true;
+      };
+      auto issue_dp = [&]() -> bool {
+        if (!mbar_wait(bars + VB_FULL + vb, vb_par, abortp, kWaitLimitCycles)) return false;
+        tc_fence_after();
+        bwd_issue_ss<D>(tmem + cDP, do_lo, v_lo0 + vb * tile16);
+        umma_commit(bars + DP_FULL);
+        umma_commit(bars + VB_EMPTY + vb);
+        if (++vb == RB) {
+          vb = 0;
+          vb_par ^= 1;
+        }
+        return true;
+      };
+      for (int round = 0; ok; ++round) {
+        const int idx = item_for_round(round, blockIdx.x, gridDim.x);
+        if (idx >= p.n_items) {
+          if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
+          continue;
+        }
+        const DqItem w = decode_dq_item<CAUSAL>(p, idx);
+        ok = mbar_wait(bars + QDO_FULL, item_cnt & 1, abortp, kWaitLimitCycles);
+        if (!ok) break;
+        ++item_cnt;
+        tc_fence_after();
+        ok = issue_s(0) && issue_dp();
+        if (ok && w.n_iter > 1) ok = issue_s(1);
+        if (!ok) break;
+        if (w.n_iter == 1) umma_commit(bars + QDO_EMPTY);  // Q and dO have fed their last products
+        for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
+          ok = mbar_wait(bars + DS_FULL, it & 1, abortp, kWaitLimitCycles);
+          if (!ok) break;
+          tc_fence_after();
+          bwd_issue_ts<D>(tmem + cDQ, tmem + cDP, k_mn0 + kq * tile16, n > 0);
+          umma_commit(bars + KA_EMPTY + kq);
+          if (++kq == RA) kq = 0;
+          if (n + 1 < w.n_iter) {
+            ok = issue_dp();
+            if (!ok) break;
+            if (n + 2 == w.n_iter) umma_commit(bars + QDO_EMPTY);
+          }
+          if (n + 2 < w.n_iter) ok = issue_s(n & 1);
+        }
+        if (!ok) break;
+        umma_commit(bars + DQ_FULL);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_word != 0) {
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 2000000ull) {
+    }
+    if (tid == 0) atomicCAS(p.status, kStatusOk, kStatusTimeout);
+    __syncthreads();
+  }
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+}  // namespace hk

@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "../../include/hk_attn.h"
+#include "attn_bwd_sm100.cuh"
 #include "attn_fwd_sm100.cuh"
 #include "paged_decode_sm100.cuh"
 #include "paged_kv_append_sm100.cuh"
@@ -72,6 +73,32 @@ int prepare_fwd_kernel() {
   return HK_OK;
 }
 
+template <typename Kernel>
+int prepare_bwd_kernel(Kernel* fn, int dyn_bytes, const char* name) {
+  HK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn_bytes));
+  cudaFuncAttributes attr;
+  HK_CUDA(cudaFuncGetAttributes(&attr, fn));
+  // same register re-balancing as the forward kernel: refuse to launch a build it would not add up in
+  if (attr.numRegs != hk::kBwdRegsAtLaunch) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "%s compiled to %d registers, expected %d", name, attr.numRegs,
+             hk::kBwdRegsAtLaunch);
+    return HK_EUNSUPPORTED;
+  }
+  if (attr.sharedSizeBytes != 0) {  // the kernels assume their dynamic shared memory starts the CTA's window
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "%s has %zu bytes of static shared memory, expected none", name,
+             attr.sharedSizeBytes);
+    return HK_EUNSUPPORTED;
+  }
+  return HK_OK;
+}
+
+template <int D, bool CAUSAL>
+int prepare_bwd_kernels() {
+  int rc = prepare_bwd_kernel(hk::attn_bwd_dkdv_kernel<D, CAUSAL>, hk::BwdSmem<D>::kDynBytes, "attn_bwd_dkdv_kernel");
+  if (rc != HK_OK) return rc;
+  return prepare_bwd_kernel(hk::attn_bwd_dq_kernel<D, CAUSAL>, hk::BwdSmem<D>::kDynBytes, "attn_bwd_dq_kernel");
+}
+
 int init_device(int device) {
   DeviceState& st = g_dev[device];
   cudaDeviceProp prop;
@@ -91,6 +118,10 @@ int init_device(int device) {
   if ((rc = prepare_fwd_kernel<64, false>()) != HK_OK) return rc;
   if ((rc = prepare_fwd_kernel<64, true>()) != HK_OK) return rc;
   if ((rc = hk::prepare_decode_kernels(g_cuda_err, sizeof(g_cuda_err))) != HK_OK) return rc;
+  if ((rc = prepare_bwd_kernels<128, false>()) != HK_OK) return rc;
+  if ((rc = prepare_bwd_kernels<128, true>()) != HK_OK) return rc;
+  if ((rc = prepare_bwd_kernels<64, false>()) != HK_OK) return rc;
+  if ((rc = prepare_bwd_kernels<64, true>()) != HK_OK) return rc;
   return HK_OK;
 }
 
@@ -154,6 +185,23 @@ template <int D, bool CAUSAL>
 int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const hk::FwdParams& p,
                int grid, cudaStream_t stream) {
   hk::attn_fwd_kernel<D, CAUSAL><<<grid, hk::kFwdThreads, hk::FwdSmem<D>::kDynBytes, stream>>>(tq, tk, tv, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  HK_CUDA(cudaGetLastError());
+  return HK_OK;
+}
+
+template <int D, bool CAUSAL>
+int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+               hk::BwdParams p, int B, int N, int H, int H_KV, int sm_count, cudaStream_t stream) {
+  const int nb = N / hk::kBlockM;
+  p.n_items = B * H_KV * nb;
+  int grid = p.n_items < sm_count ? p.n_items : sm_count;
+  hk::attn_bwd_dkdv_kernel<D, CAUSAL><<<grid, hk::kBwdThreads, hk::BwdSmem<D>::kDynBytes, stream>>>(tq, tk, tv, tdo, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  HK_CUDA(cudaGetLastError());
+  p.n_items = B * H * nb;
+  grid = p.n_items < sm_count ? p.n_items : sm_count;
+  hk::attn_bwd_dq_kernel<D, CAUSAL><<<grid, hk::kBwdThreads, hk::BwdSmem<D>::kDynBytes, stream>>>(tq, tk, tv, tdo, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   HK_CUDA(cudaGetLastError());
   return HK_OK;
@@ -242,6 +290,102 @@ int hk_attn_fwd_varlen(const void* q, const void* k, const void* v, void* o, flo
                 : launch_fwd<64, false>(tq, tk, tv, p, grid, stream);
 }
 
+int hk_attn_bwd_prep(const void* o, const void* d_o, float* delta, int B, int N, int H, int D, int device,
+                     void* cuda_stream) {
+  if (!o || !d_o || !delta) return HK_EINVAL;
+  if (B <= 0 || N <= 0 || H <= 0) return HK_EINVAL;
+  if (D != 64 && D != 128) return HK_EUNSUPPORTED;
+  if (!aligned16(o) || !aligned16(d_o) || (reinterpret_cast<uintptr_t>(delta) & 3)) return HK_EINVAL;
+  DeviceState* st = nullptr;
+  int rc = use_device(device, &st);
+  if (rc != HK_OK) return rc;
+  const long long rows = static_cast<long long>(B) * N * H;
+  const long long blocks = (rows + 7) / 8;
+  if (blocks > 0x7fffffffll) return HK_EINVAL;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  const auto* po = static_cast<const __nv_bfloat16*>(o);
+  const auto* pd = static_cast<const __nv_bfloat16*>(d_o);
+  if (D == 128) hk::attn_bwd_prep_kernel<128><<<unsigned(blocks), 256, 0, stream>>>(po, pd, delta, B, N, H);
+  else hk::attn_bwd_prep_kernel<64><<<unsigned(blocks), 256, 0, stream>>>(po, pd, delta, B, N, H);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  HK_CUDA(cudaGetLastError());
+  return HK_OK;
+}
+
+int hk_attn_bwd(const void* q, const void* k, const void* v, const void* d_o, const float* lse, const float* delta,
+                void* dq, void* dk, void* dv, int B, int N, int H, int H_KV, int D, int causal, float softmax_scale,
+                int dq_layout, int device, void* cuda_stream) {
+  if (!q || !k || !v || !d_o || !lse || !delta || !dq || !dk || !dv) return HK_EINVAL;
+  if (B <= 0 || N <= 0 || H <= 0 || H_KV <= 0) return HK_EINVAL;
+  if (D != 64 && D != 128) return HK_EUNSUPPORTED;
+  if (H % H_KV != 0) return HK_EINVAL;
+  if (N % hk::kBlockM != 0) return HK_EUNSUPPORTED;
+  if (dq_layout != HK_DQ_BNHD && dq_layout != HK_DQ_BHND) return HK_EINVAL;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(d_o) || !aligned16(dq) || !aligned16(dk) ||
+      !aligned16(dv) || !aligned16(lse) || !aligned16(delta))
+    return HK_EINVAL;
+  DeviceState* st = nullptr;
+  int rc = use_device(device, &st);
+  if (rc != HK_OK) return rc;
+
+  const long long qs[3] = {(long long)N * H * D, (long long)H * D, D};
+  const long long ks[3] = {(long long)N * H_KV * D, (long long)H_KV * D, D};
+  CUtensorMap tq, tk, tv, tdo;
+  if ((rc = make_bnhd_map(&tq, q, B, N, H, D, qs)) != HK_OK) return rc;
+  if ((rc = make_bnhd_map(&tk, k, B, N, H_KV, D, ks)) != HK_OK) return rc;
+  if ((rc = make_bnhd_map(&tv, v, B, N, H_KV, D, ks)) != HK_OK) return rc;
+  if ((rc = make_bnhd_map(&tdo, d_o, B, N, H, D, qs)) != HK_OK) return rc;
+
+  hk::BwdParams p;
+  p.lse = lse;
+  p.delta = delta;
+  p.dq = static_cast<__nv_bfloat16*>(dq);
+  p.dk = static_cast<__nv_bfloat16*>(dk);
+  p.dv = static_cast<__nv_bfloat16*>(dv);
+  p.dq_stride_b = (long long)N * H * D;
+  p.dq_stride_n = dq_layout == HK_DQ_BNHD ? (long long)H * D : D;
+  p.dq_stride_h = dq_layout == HK_DQ_BNHD ? D : (long long)N * D;
+  p.B = B;
+  p.N = N;
+  p.H = H;
+  p.H_KV = H_KV;
+  p.n_items = 0;
+  {
+    // causal sweep groups: units whose Q, dO, K and V together stay within ~64 MB of L2
+    const int G = H / H_KV;
+    const long long unit_bytes = (4ll * G + 4ll) * N * D;
+    long long u = (64ll << 20) / unit_bytes;
+    p.group_units = int(u < 1 ? 1 : (u > B * H_KV ? B * H_KV : u));
+  }
+  p.scale = softmax_scale > 0.f ? softmax_scale : 1.0f / std::sqrt(float(D));
+  p.scale_log2 = p.scale * 1.4426950408889634f;
+  p.status = st->status;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (D == 128) return causal ? launch_bwd<128, true>(tq, tk, tv, tdo, p, B, N, H, H_KV, st->sm_count, stream)
+                              : launch_bwd<128, false>(tq, tk, tv, tdo, p, B, N, H, H_KV, st->sm_count, stream);
+  return causal ? launch_bwd<64, true>(tq, tk, tv, tdo, p, B, N, H, H_KV, st->sm_count, stream)
+                : launch_bwd<64, false>(tq, tk, tv, tdo, p, B, N, H, H_KV, st->sm_count, stream);
+}
+
+int hk_attn_dq_shuffle(const void* dq_bhnd, void* dq_bnhd, int B, int N, int H, int D, int device,
+                       void* cuda_stream) {
+  if (!dq_bhnd || !dq_bnhd || dq_bhnd == dq_bnhd) return HK_EINVAL;
+  if (B <= 0 || N <= 0 || H <= 0 || D <= 0 || D % 8 != 0) return HK_EINVAL;
+  if (!aligned16(dq_bhnd) || !aligned16(dq_bnhd)) return HK_EINVAL;
+  DeviceState* st = nullptr;
+  int rc = use_device(device, &st);
+  if (rc != HK_OK) return rc;
+  const int vec = D / 8;
+  const long long total = static_cast<long long>(B) * N * H * vec;
+  const long long blocks = (total + 255) / 256;
+  if (blocks > 0x7fffffffll) return HK_EINVAL;
+  hk::attn_dq_shuffle_kernel<<<unsigned(blocks), 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const uint4*>(dq_bhnd), static_cast<uint4*>(dq_bnhd), B, N, H, vec);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  HK_CUDA(cudaGetLastError());
+  return HK_OK;
+}
+
 size_t hk_attn_paged_decode_workspace_bytes(int S, int H, int D, int max_pages_per_seq, int page_size) {
   return hk::decode_workspace_bytes(S, H, D, max_pages_per_seq, page_size);
 }
@@ -325,6 +469,7 @@ int hk_last_device_status(int device) {
   HK_CUDA(cudaMemcpy(&word, st->status, sizeof(int), cudaMemcpyDeviceToHost));
   if (word != 0) HK_CUDA(cudaMemset(st->status, 0, sizeof(int)));
   if (word == hk::kStatusOk) return HK_OK;
+  if (word == hk::kStatusSmemAlign) return HK_EUNSUPPORTED;
   return word == hk::kStatusBadPage ? HK_EBADPAGE : HK_ETIMEOUT;
 }
 

@@ -73,6 +73,41 @@ int hk_attn_paged_decode(const void* q, const void* k_pages, const void* v_pages
                          float softmax_scale, void* workspace, size_t workspace_bytes,
                          int device, void* cuda_stream);
 
+/* ---- attention backward ------------------------------------------------------------------------------
+ * The reference runs three kernels per backward pass (training/llama/llama/models/attentions/hipkittens.py:
+ * 110-112): tk_kernel_bkwd_prep.dispatch_prep(O, dO, delta), tk_kernel_bkwd.dispatch_bwd_combined(q, k, v,
+ * dO, dQ_in, dK, dV, L, delta) and tk_kernel_bkwd_prep.dispatch_dq_shuffle(dQ_in, dQ). The three entry
+ * points below replace them one for one. All are asynchronous on `cuda_stream`. */
+
+/* delta[b,h,0,n] = sum_d O[b,n,h,d] * dO[b,n,h,d] in fp32.
+ * Replaces dispatch_prep (kernels/attn/gqa_backwards/attn_bkwd_prep.cpp:164-195,230-234).
+ *   o, d_o : bf16 [B,N,H,D] contiguous      delta : fp32 [B,H,1,N]      D in {64, 128} */
+int hk_attn_bwd_prep(const void* o, const void* d_o, float* delta, int B, int N, int H, int D, int device,
+                     void* cuda_stream);
+
+/* Layout in which hk_attn_bwd writes dQ. */
+#define HK_DQ_BNHD 0 /* [B,N,H,D], the layout of q: no shuffle pass needed afterwards */
+#define HK_DQ_BHND 1 /* [B,H,N,D], the reference's pre-shuffle scratch layout (dQ_in) */
+
+/* dQ, dK, dV of O = softmax(scale * Q K^T) V given dO, the forward pass's L and delta from hk_attn_bwd_prep.
+ * Replaces dispatch_bwd_combined (kernels/attn/gqa_backwards/attn_bkwd_non_causal.cpp:37-49,3164-3185;
+ * causal twin kernels/attn/gqa_causal_backwards/attn_bkwd_causal.cpp). The reference accumulates dQ with
+ * atomic adds into a zero-filled [B,H,N,D] scratch and needs dispatch_dq_shuffle afterwards; here dQ is
+ * written once, in the layout `dq_layout` names, and does not need to be zero-filled.
+ *   q, d_o, dq : bf16 [B,N,H,D] (dq as dq_layout says)    k, v, dk, dv : bf16 [B,N,H_KV,D]
+ *   lse, delta : fp32 [B,H,1,N]
+ *   D in {64, 128}; N a multiple of 128 (HK_EUNSUPPORTED otherwise; the reference needs a multiple of 256);
+ *   all pointers 16-byte aligned; softmax_scale <= 0 selects 1/sqrt(D).
+ * Results are bit-identical from run to run (no atomics). */
+int hk_attn_bwd(const void* q, const void* k, const void* v, const void* d_o, const float* lse, const float* delta,
+                void* dq, void* dk, void* dv, int B, int N, int H, int H_KV, int D, int causal, float softmax_scale,
+                int dq_layout, int device, void* cuda_stream);
+
+/* dq_bnhd[b,n,h,:] = dq_bhnd[b,h,n,:]. Replaces dispatch_dq_shuffle (attn_bkwd_prep.cpp:199-223,236-239); only
+ * needed after hk_attn_bwd with HK_DQ_BHND. D a multiple of 8; the two buffers must not alias. */
+int hk_attn_dq_shuffle(const void* dq_bhnd, void* dq_bnhd, int B, int N, int H, int D, int device,
+                       void* cuda_stream);
+
 /* Appends T new tokens per sequence to the paged KV cache read by hk_attn_paged_decode.
  * Paged counterpart of the reference's contiguous cache update, kv_cache[b, offset : offset + T] = kv
  * (training/llama/llama/models/mha.py:16-42, _update_kv_cache).
