@@ -9,8 +9,10 @@ Public surface
 * ``attn_fwd(q, k, v, causal=False, ...) -> (O, L)``, ``attn_bwd_prep`` / ``attn_bwd`` / ``dq_shuffle`` (the
   backward pass), ``paged_decode(...) -> (O, L)`` and ``paged_kv_append(...)``: torch-tensor front ends over
   the C ABI (ctypes).
-* ``load_tk_kernel(causal)`` / ``load_tk_kernel_fwd(causal)``: the reference's extension modules
-  (``tk_kernel.dispatch_micro``, ``tk_kernel_fwd.dispatch_fwd``) built for B200.
+* ``load_tk_kernel(causal)`` / ``load_tk_kernel_fwd(causal)`` / ``load_tk_kernel_bkwd(causal)`` /
+  ``load_tk_kernel_bkwd_prep(causal)``: the reference's extension modules (``tk_kernel.dispatch_micro``,
+  ``tk_kernel_fwd.dispatch_fwd``, ``tk_kernel_bkwd.dispatch_bwd_combined``, ``tk_kernel_bkwd_prep.dispatch_prep``
+  and ``.dispatch_dq_shuffle``) built for B200.
 * ``HipAttnFunction`` in :mod:`hipkittens_b200.attention`: the reference's autograd-function forward.
 """
 from ._native import (  # noqa: F401
@@ -25,6 +27,8 @@ from ._native import (  # noqa: F401
     kernel_launch_count,
     lib_path,
     load_tk_kernel,
+    load_tk_kernel_bkwd,
+    load_tk_kernel_bkwd_prep,
     load_tk_kernel_fwd,
     paged_decode,
     paged_decode_workspace_bytes,
@@ -43,6 +47,8 @@ __all__ = [
     "kernel_launch_count",
     "lib_path",
     "load_tk_kernel",
+    "load_tk_kernel_bkwd",
+    "load_tk_kernel_bkwd_prep",
     "load_tk_kernel_fwd",
     "paged_decode",
     "paged_kv_append",

@@ -9,6 +9,8 @@ into directories that mirror the reference's:
     kernels/attn/gqa_causal/tk_kernel              dispatch_micro, causal default
     kernels/attn/gqa_backwards/tk_kernel_fwd       dispatch_fwd (blocking), non-causal default
     kernels/attn/gqa_causal_backwards/tk_kernel_fwd  dispatch_fwd (blocking), causal default
+    kernels/attn/gqa{,_causal}_backwards/tk_kernel_bkwd       dispatch_bwd_combined
+    kernels/attn/gqa{,_causal}_backwards/tk_kernel_bkwd_prep  dispatch_prep, dispatch_dq_shuffle
 
 Run as ``python -m hipkittens_b200._build``. nvcc cross-compiles without a GPU.
 """
@@ -37,6 +39,16 @@ SHIMS = [
     ("kernels/attn/gqa_causal", "tk_kernel", "dispatch_micro", 1, 0),
     ("kernels/attn/gqa_backwards", "tk_kernel_fwd", "dispatch_fwd", 0, 1),
     ("kernels/attn/gqa_causal_backwards", "tk_kernel_fwd", "dispatch_fwd", 1, 1),
+]
+
+
+# (directory under the package, module name, HK_BKWD_PREP, default causal): the reference's two backward modules
+# (kernels/attn/gqa_backwards/Makefile: tk_kernel_bkwd, tk_kernel_bkwd_prep)
+BKWD_SHIMS = [
+    ("kernels/attn/gqa_backwards", "tk_kernel_bkwd", 0, 0),
+    ("kernels/attn/gqa_backwards", "tk_kernel_bkwd_prep", 1, 0),
+    ("kernels/attn/gqa_causal_backwards", "tk_kernel_bkwd", 0, 1),
+    ("kernels/attn/gqa_causal_backwards", "tk_kernel_bkwd_prep", 1, 1),
 ]
 
 
@@ -76,11 +88,12 @@ def build_shims(force: bool = False):
     import pybind11
 
     src = os.path.join(CSRC, "tk_kernel_shim.cpp")
+    common = os.path.join(CSRC, "shim_common.h")
     out = []
     for subdir, module, entry, causal, sync in SHIMS:
         target = shim_path(subdir, module)
         out.append(target)
-        if not force and _newer(target, [src, os.path.join(INCLUDE, "hk_attn.h"), LIB_PATH]):
+        if not force and _newer(target, [src, common, os.path.join(INCLUDE, "hk_attn.h"), LIB_PATH]):
             continue
         os.makedirs(os.path.dirname(target), exist_ok=True)
         rel = os.path.relpath(LIB_DIR, os.path.dirname(target))
@@ -90,6 +103,21 @@ def build_shims(force: bool = False):
             f"-DHK_DEFAULT_CAUSAL={causal}", f"-DHK_SYNC_AFTER={sync}",
             "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
             src, "-o", target,
+            "-L", LIB_DIR, "-lhk_attn", f"-Wl,-rpath,$ORIGIN/{rel}",
+        ])
+    bsrc = os.path.join(CSRC, "tk_kernel_bkwd_shim.cpp")
+    for subdir, module, prep, causal in BKWD_SHIMS:
+        target = shim_path(subdir, module)
+        out.append(target)
+        if not force and _newer(target, [bsrc, common, os.path.join(INCLUDE, "hk_attn.h"), LIB_PATH]):
+            continue
+        os.makedirs(os.path.dirname(target), exist_ok=True)
+        rel = os.path.relpath(LIB_DIR, os.path.dirname(target))
+        _run([
+            "g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden",
+            f"-DHK_BKWD_PREP={prep}", f"-DHK_DEFAULT_CAUSAL={causal}",
+            "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
+            bsrc, "-o", target,
             "-L", LIB_DIR, "-lhk_attn", f"-Wl,-rpath,$ORIGIN/{rel}",
         ])
     return out

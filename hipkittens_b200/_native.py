@@ -397,3 +397,17 @@ def load_tk_kernel_fwd(causal: bool = True):
     """The ``tk_kernel_fwd`` module of the training call site: blocking ``dispatch_fwd(q,k,v,O,L)``."""
     return _load_ext("kernels/attn/gqa_causal_backwards" if causal else "kernels/attn/gqa_backwards",
                      "tk_kernel_fwd")
+
+
+def load_tk_kernel_bkwd(causal: bool = True):
+    """The ``tk_kernel_bkwd`` module of kernels/attn/gqa_backwards (or gqa_causal_backwards):
+    blocking ``dispatch_bwd_combined(Q, K, V, dO, dQ_in, dK, dV, L, delta)``."""
+    return _load_ext("kernels/attn/gqa_causal_backwards" if causal else "kernels/attn/gqa_backwards",
+                     "tk_kernel_bkwd")
+
+
+def load_tk_kernel_bkwd_prep(causal: bool = True):
+    """The ``tk_kernel_bkwd_prep`` module: blocking ``dispatch_prep(O, dO, delta)`` and
+    ``dispatch_dq_shuffle(dQ_in, dQ)``. (Both builds are identical; `causal` only picks the directory.)"""
+    return _load_ext("kernels/attn/gqa_causal_backwards" if causal else "kernels/attn/gqa_backwards",
+                     "tk_kernel_bkwd_prep")

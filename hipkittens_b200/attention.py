@@ -1,13 +1,15 @@
-"""Host-side mirror of the reference's attention call site for the forward path.
+"""Host-side mirror of the reference's attention call site (forward and backward).
 
 ``HipAttnFunction`` / ``HipSelfAttention`` / ``HipCrossAttention`` follow
 ``training/llama/llama/models/attentions/hipkittens.py:17-61,122-202``: inputs and outputs are BNHD,
 q/k/v are cast to bf16 and made contiguous, O [B,N,H,D] bf16 and L [B,H,1,N] fp32 are allocated by the
 caller side and filled by the blocking ``tk_kernel_fwd.dispatch_fwd(q, k, v, O, L)``; O is returned in the
-input dtype and (q, k, v, O, L) are saved for a backward pass.
+input dtype and (q, k, v, O, L) are saved for the backward pass, which runs the reference's three calls
+(hipkittens.py:64-119): ``dispatch_prep(O, dO, delta)``, ``dispatch_bwd_combined(q, k, v, dO, dQ_in, dK, dV,
+L, delta)`` and ``dispatch_dq_shuffle(dQ_in, dQ)``.
 
-Differences: the backward kernels are not part of this build, so ``backward`` raises; and causality and
-the softmax scale are honoured here (they are baked into the reference's compiled module, and its modules
+Differences: the backward needs N to be a multiple of 128; dQ_in is not zero-filled (nothing is accumulated
+into it); and causality and the softmax scale are honoured here (they are baked into the reference's compiled module, and its modules
 ignore the ``causal`` and ``softmax_scale`` they are constructed with, hipkittens.py:147-162).
 """
 from __future__ import annotations
@@ -16,9 +18,16 @@ import torch
 import torch.nn as nn
 from torch.autograd import Function
 
-from ._native import attn_fwd, device_status, load_tk_kernel_fwd
+from ._native import attn_fwd, device_status, load_tk_kernel_bkwd, load_tk_kernel_bkwd_prep, load_tk_kernel_fwd
 
 _fwd_modules = {}
+_bkwd_modules = {}
+
+
+def _tk_kernel_bkwd(causal: bool):
+    if causal not in _bkwd_modules:
+        _bkwd_modules[causal] = (load_tk_kernel_bkwd(causal), load_tk_kernel_bkwd_prep(causal))
+    return _bkwd_modules[causal]
 
 
 def _tk_kernel_fwd(causal: bool):
@@ -66,14 +75,35 @@ class HipAttnFunction(Function):
 
         ctx.save_for_backward(q, k, v, O, L)
         ctx.causal = bool(causal)
+        ctx.softmax_scale = softmax_scale
         return O.to(out_dtype)
 
     @staticmethod
     def backward(ctx, dO_bnhd: torch.Tensor):
-        raise NotImplementedError(
-            "attention backward (dispatch_prep / dispatch_bwd_combined / dispatch_dq_shuffle) is outside this "
-            "build; q, k, v, O and L are saved on ctx for it"
-        )
+        q, k, v, O, L = ctx.saved_tensors
+        B, N, H, D = O.shape
+        HKV = k.shape[2]
+        dev = dO_bnhd.device
+        assert dO_bnhd.shape == (B, N, H, D), f"dO shape mismatch: expected ({B}, {N}, {H}, {D}), got {dO_bnhd.shape}"
+        assert dO_bnhd.is_cuda and dO_bnhd.device == O.device, "dO must be on correct CUDA device"
+
+        # the strided forward path saves views; the backward kernels read contiguous tensors
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        dO = dO_bnhd.to(torch.bfloat16).contiguous()
+
+        dQ_in = torch.empty((B, H, N, D), dtype=torch.bfloat16, device=dev)  # BHND (pre-shuffle)
+        dQ = torch.empty((B, N, H, D), dtype=torch.bfloat16, device=dev)
+        dK = torch.empty((B, N, HKV, D), dtype=torch.bfloat16, device=dev)
+        dV = torch.empty((B, N, HKV, D), dtype=torch.bfloat16, device=dev)
+        delta = torch.empty((B, H, 1, N), dtype=torch.float32, device=dev)
+
+        tk_kernel_bkwd, tk_kernel_bkwd_prep = _tk_kernel_bkwd(ctx.causal)
+        tk_kernel_bkwd_prep.dispatch_prep(O, dO, delta)
+        tk_kernel_bkwd.dispatch_bwd_combined(q, k, v, dO, dQ_in, dK, dV, L, delta, causal=ctx.causal,
+                                             softmax_scale=ctx.softmax_scale)
+        tk_kernel_bkwd_prep.dispatch_dq_shuffle(dQ_in, dQ)
+
+        return dQ.to(dO_bnhd.dtype), dK.to(dO_bnhd.dtype), dV.to(dO_bnhd.dtype), None, None
 
 
 class HipSelfAttention(nn.Module):

@@ -69,37 +69,35 @@ struct BwdSmem {
 static_assert(BwdSmem<128>::kDynBytes <= 232448, "shared memory budget of one CTA");
 
 // ------------------------------------------------------------------------------------ delta = rowsum(dO * O)
-// One warp per (batch, position, head) row; memory-bound (reads O and dO once).
-// grid = ceil(B*N*H / 8), block = 256.
+// D/8 lanes per (batch, position, head) row, 16 bytes of O and of dO per lane; memory-bound (reads O and dO
+// once). grid = ceil(B*N*H / rows per block), block = 256.
 template <int D>
 __global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o,
                                                             const __nv_bfloat16* __restrict__ d_o,
                                                             float* __restrict__ delta, int B, int N, int H) {
-  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  constexpr int kLanesPerRow = D / 8;               // 16 or 8
+  constexpr int kRowsPerWarp = 32 / kLanesPerRow;   // 2 or 4
   const int lane = threadIdx.x & 31;
+  const int sub = lane % kLanesPerRow;
+  const long long row = (static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5)) * kRowsPerWarp + lane / kLanesPerRow;
   const long long rows = static_cast<long long>(B) * N * H;
-  if (row >= rows) return;
-  constexpr int kPerLane = D / 32;  // 2 or 4 bf16 per lane
-  const __nv_bfloat16* po = o + row * D + lane * kPerLane;
-  const __nv_bfloat16* pd = d_o + row * D + lane * kPerLane;
   float acc = 0.f;
-  if constexpr (kPerLane == 4) {
-    const uint2 a = *reinterpret_cast<const uint2*>(po);
-    const uint2 b = *reinterpret_cast<const uint2*>(pd);
-    const __nv_bfloat162 a0 = *reinterpret_cast<const __nv_bfloat162*>(&a.x);
-    const __nv_bfloat162 a1 = *reinterpret_cast<const __nv_bfloat162*>(&a.y);
-    const __nv_bfloat162 b0 = *reinterpret_cast<const __nv_bfloat162*>(&b.x);
-    const __nv_bfloat162 b1 = *reinterpret_cast<const __nv_bfloat162*>(&b.y);
-    acc = __low2float(a0) * __low2float(b0) + __high2float(a0) * __high2float(b0) +
-          __low2float(a1) * __low2float(b1) + __high2float(a1) * __high2float(b1);
-  } else {
-    const __nv_bfloat162 a0 = *reinterpret_cast<const __nv_bfloat162*>(po);
-    const __nv_bfloat162 b0 = *reinterpret_cast<const __nv_bfloat162*>(pd);
-    acc = __low2float(a0) * __low2float(b0) + __high2float(a0) * __high2float(b0);
+  if (row < rows) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(o + row * D) + sub);
+    const uint4 b = __ldg(reinterpret_cast<const uint4*>(d_o + row * D) + sub);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+    const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&aw[i]);
+      const __nv_bfloat162 y = *reinterpret_cast<const __nv_bfloat162*>(&bw[i]);
+      acc = fmaf(__low2float(x), __low2float(y), acc);
+      acc = fmaf(__high2float(x), __high2float(y), acc);
+    }
   }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (lane == 0) {
+  for (int off = kLanesPerRow / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (row < rows && sub == 0) {
     const long long bn = row / H;
     const int h = static_cast<int>(row - bn * H);
     const long long b = bn / N;

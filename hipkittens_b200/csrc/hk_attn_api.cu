@@ -300,7 +300,8 @@ int hk_attn_bwd_prep(const void* o, const void* d_o, float* delta, int B, int N,
   int rc = use_device(device, &st);
   if (rc != HK_OK) return rc;
   const long long rows = static_cast<long long>(B) * N * H;
-  const long long blocks = (rows + 7) / 8;
+  const int rows_per_block = 8 * (32 / (D / 8));  // 8 warps, D/8 lanes per row
+  const long long blocks = (rows + rows_per_block - 1) / rows_per_block;
   if (blocks > 0x7fffffffll) return HK_EINVAL;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   const auto* po = static_cast<const __nv_bfloat16*>(o);

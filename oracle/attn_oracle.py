@@ -29,6 +29,15 @@ against the reference's HIP kernels themselves is unpinned (they cannot run here
 
 The paged decode variant has no counterpart in the reference; its oracle gathers each sequence's
 pages through the block table and applies the same math to one query row.
+
+Backward
+--------
+``attn_bwd_oracle`` is the derivative of that same math path written out by hand (what autograd computes
+for ``base.py:96-119``; the reference states the same formulas in ``simple_flash_backward``,
+``kernels/attn/gqa_backwards/test_python.py:100-137``): with P the softmax, dP = dO V^T,
+delta = rowsum(dO * O) and dS = P * (dP - delta): dV = P^T dO, dK = scale * dS^T Q, dQ = scale * dS K, each
+summed over the heads of a group for dK and dV. It is pinned against gradients that autograd produced
+through the reference's own ``CrossAttention`` module (``tests/golden/make_golden.py``).
 """
 from __future__ import annotations
 
@@ -41,6 +50,7 @@ from hipkittens_b200.synthetic import make_paged_inputs, make_prefill_inputs  # 
 
 __all__ = [
     "attn_fwd_oracle",
+    "attn_bwd_oracle",
     "paged_decode_oracle",
     "paged_kv_append_oracle",
     "make_prefill_inputs",
@@ -99,6 +109,55 @@ def attn_fwd_oracle(
             out[bi, :, kh * g:(kh + 1) * g, :] = o_u.to(torch.bfloat16)
             lse[bi, kh * g:(kh + 1) * g, 0, :] = l_u
     return out, lse
+
+
+def attn_bwd_oracle(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    d_o: torch.Tensor,
+    causal: bool = False,
+    softmax_scale: Optional[float] = None,
+    dtype: torch.dtype = torch.float32,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Gradients of O = softmax(scale q k^T) v with respect to q, k, v for the upstream gradient d_o.
+
+    q, d_o [B,N,H,D], k, v [B,N,H_KV,D] (values used as given, math in `dtype`). Returns dq [B,N,H,D],
+    dk, dv [B,N,H_KV,D] and delta [B,H,1,N] = rowsum(d_o * O), all in `dtype` (no bf16 rounding: the
+    tolerance of the comparison covers the kernels' bf16 outputs). O here is the unrounded attention
+    output; the kernels compute delta from the bf16-rounded O of the forward pass
+    (kernels/attn/gqa_backwards/attn_bkwd_prep.cpp:176-185).
+    """
+    b, n, h, d = q.shape
+    hkv = k.shape[2]
+    assert h % hkv == 0 and k.shape == v.shape and d_o.shape == q.shape
+    g = h // hkv
+    scale = softmax_scale if softmax_scale else 1.0 / math.sqrt(d)
+    dq = torch.empty((b, n, h, d), dtype=dtype)
+    dk = torch.empty((b, n, hkv, d), dtype=dtype)
+    dv = torch.empty((b, n, hkv, d), dtype=dtype)
+    delta = torch.empty((b, h, 1, n), dtype=dtype)
+    row = torch.arange(n).view(n, 1)
+    col = torch.arange(n).view(1, n)
+    for bi in range(b):
+        for kh in range(hkv):
+            qg = q[bi, :, kh * g:(kh + 1) * g, :].to(dtype)      # [N, G, D]
+            dog = d_o[bi, :, kh * g:(kh + 1) * g, :].to(dtype)
+            ku = k[bi, :, kh, :].to(dtype)                       # [N, D]
+            vu = v[bi, :, kh, :].to(dtype)
+            scores = torch.einsum("tgd,sd->gts", qg, ku * scale)
+            if causal:
+                scores = scores.masked_fill((col > row).unsqueeze(0), float("-inf"))
+            p = torch.softmax(scores, dim=-1)                    # [G, N, N]
+            o = torch.einsum("gts,sd->tgd", p, vu)
+            dl = (dog * o).sum(-1)                               # [N, G]
+            dp = torch.einsum("tgd,sd->gts", dog, vu)
+            ds = p * (dp - dl.t().unsqueeze(-1))
+            dv[bi, :, kh, :] = torch.einsum("gts,tgd->sd", p, dog)
+            dk[bi, :, kh, :] = torch.einsum("gts,tgd->sd", ds, qg) * scale
+            dq[bi, :, kh * g:(kh + 1) * g, :] = torch.einsum("gts,sd->tgd", ds, ku) * scale
+            delta[bi, kh * g:(kh + 1) * g, 0, :] = dl.t()
+    return dq, dk, dv, delta
 
 
 def paged_decode_oracle(

@@ -48,12 +48,21 @@ def main() -> None:
         q = torch.randn((b, n, h, d), generator=gen).to(torch.bfloat16)
         k = torch.randn((b, n, hkv, d), generator=gen).to(torch.bfloat16)
         v = torch.randn((b, n, hkv, d), generator=gen).to(torch.bfloat16)
+        d_o = torch.randn((b, n, h, d), generator=gen).to(torch.bfloat16)  # drawn last: q, k, v keep their values
         attn = CrossAttention(causal=causal)
+        # backward of the reference module: autograd through base.py:78-120 on fp32 leaves
+        qf = q.float().requires_grad_(True)
+        kvf = torch.stack([k.float(), v.float()], dim=2).requires_grad_(True)
+        attn(qf, kvf).backward(d_o.float())
+        grads = {"d_o": bf16_bits(d_o), "dq_ref_fp32": qf.grad.numpy().astype(np.float32),
+                 "dk_ref_fp32": kvf.grad[:, :, 0].contiguous().numpy().astype(np.float32),
+                 "dv_ref_fp32": kvf.grad[:, :, 1].contiguous().numpy().astype(np.float32)}
         with torch.no_grad():
             o32 = attn(q.float(), torch.stack([k.float(), v.float()], dim=2))
             out = {"q": bf16_bits(q), "k": bf16_bits(k), "v": bf16_bits(v),
                    "o_ref_fp32": o32.numpy().astype(np.float32),
                    "shape": np.array([b, n, h, hkv, d, int(causal), seed], dtype=np.int64)}
+            out.update(grads)
             if h == hkv:
                 # MHA: the SelfAttention module must agree with CrossAttention on the same inputs.
                 o_self = SelfAttention(causal=causal)(torch.stack([q.float(), k.float(), v.float()], dim=2))

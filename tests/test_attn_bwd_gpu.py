@@ -1,0 +1,250 @@
+"""GPU parity of the attention backward (delta prep, dK/dV kernel, dQ kernel, dQ shuffle) against the CPU
+oracle and against gradients of the reference's own PyTorch module, through the C ABI, the reference's
+Python entry points and the autograd function.
+
+Tolerance (written here, floating point): every gradient element within 2e-2 + 1e-2 * |ref| of the fp32
+oracle (outputs are bf16: half an ulp is 2^-9 relative; P and dS are rounded to bf16 before the last
+products), and a relative L2 error of at most 5e-3 per tensor."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import hipkittens_b200 as hk
+from hipkittens_b200 import _native
+from hipkittens_b200.synthetic import make_prefill_inputs
+from oracle.attn_oracle import attn_bwd_oracle
+
+pytestmark = pytest.mark.gpu
+ATOL, RTOL, L2TOL = 2e-2, 1e-2, 5e-3
+GOLDEN = [p for p in sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "case_*.npz")))
+          if "dq_ref_fp32" in np.load(p).files]
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "these tests need a B200"
+    return torch.device("cuda:0")
+
+
+def make_do(shape, seed):
+    return torch.randn(shape, generator=torch.Generator().manual_seed(seed)).to(torch.bfloat16)
+
+
+def run_bwd(q, k, v, d_o, causal, dev, scale=None, dq_layout=hk.HK_DQ_BNHD):
+    """Forward + prep + backward on the GPU; gradient buffers are poisoned with NaN first."""
+    qd, kd, vd, dod = (t.to(dev) for t in (q, k, v, d_o))
+    o, lse = hk.attn_fwd(qd, kd, vd, causal=causal, softmax_scale=scale)
+    delta = hk.attn_bwd_prep(o, dod)
+    b, n, h, d = q.shape
+    dq_shape = (b, n, h, d) if dq_layout == hk.HK_DQ_BNHD else (b, h, n, d)
+    dq = torch.full(dq_shape, float("nan"), dtype=torch.bfloat16, device=dev)
+    dk = torch.full(k.shape, float("nan"), dtype=torch.bfloat16, device=dev)
+    dv = torch.full(v.shape, float("nan"), dtype=torch.bfloat16, device=dev)
+    hk.attn_bwd(qd, kd, vd, dod, lse, delta, causal=causal, softmax_scale=scale, dq=dq, dk=dk, dv=dv,
+                dq_layout=dq_layout)
+    assert _native.device_status(0) == 0
+    return dq.cpu(), dk.cpu(), dv.cpu(), delta.cpu(), o.cpu()
+
+
+def assert_grad_parity(got, ref, name):
+    got = got.float()
+    assert not torch.isnan(got).any(), f"{name} has unwritten elements"
+    diff = (got - ref).abs()
+    bad = diff > (ATOL + RTOL * ref.abs())
+    assert not bool(bad.any()), f"{name}: {int(bad.sum())} elements out of tolerance, max|diff| = {float(diff.max())}"
+    l2 = float(diff.pow(2).sum().sqrt() / ref.pow(2).sum().sqrt())
+    assert l2 <= L2TOL, f"{name}: relative L2 error {l2}"
+
+
+SHAPES = [
+    # B, N, H, H_KV, D, causal
+    (1, 256, 8, 2, 64, False),     # BASELINE config 1
+    (1, 128, 1, 1, 128, False),    # one tile, one iteration per kernel
+    (1, 128, 1, 1, 128, True),     # a single diagonal tile
+    (2, 384, 4, 2, 128, True),     # odd block count, GQA
+    (1, 512, 2, 2, 128, True),     # MHA causal
+    (1, 384, 3, 3, 64, False),     # odd head count
+    (2, 256, 8, 8, 64, True),      # MHA, D = 64, causal
+    (1, 1024, 16, 2, 128, False),  # group of 8
+    (3, 256, 12, 4, 64, False),    # group of 3
+    (1, 1152, 4, 1, 128, True),    # group of 4, nine blocks: the K ring wraps several times in one item
+]
+
+
+@pytest.mark.parametrize("b,n,h,hkv,d,causal", SHAPES)
+def test_parity_against_oracle(dev, b, n, h, hkv, d, causal):
+    q, k, v = make_prefill_inputs(b, n, h, hkv, d, seed=b * 1000 + n + h)
+    d_o = make_do((b, n, h, d), seed=7 * n + h)
+    dq, dk, dv, delta, _o = run_bwd(q, k, v, d_o, causal, dev)
+    rq, rk, rv, rdelta = attn_bwd_oracle(q, k, v, d_o, causal=causal)
+    # delta uses the bf16-rounded O of the forward kernel (half an ulp of O per term)
+    assert bool(((delta - rdelta).abs() <= ATOL + RTOL * rdelta.abs()).all())
+    assert_grad_parity(dq, rq, "dq")
+    assert_grad_parity(dk, rk, "dk")
+    assert_grad_parity(dv, rv, "dv")
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
+def test_parity_against_reference_module_gradients(dev, path):
+    """Directly against the committed autograd gradients of the reference's CrossAttention (fp32 run)."""
+    z = np.load(path)
+    b, n, h, hkv, d, causal, _ = [int(x) for x in z["shape"]]
+    bits = lambda a: torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16)  # noqa: E731
+    q, k, v, d_o = bits(z["q"]), bits(z["k"]), bits(z["v"]), bits(z["d_o"])
+    dq, dk, dv, _delta, _o = run_bwd(q, k, v, d_o, bool(causal), dev)
+    assert_grad_parity(dq, torch.from_numpy(z["dq_ref_fp32"]), "dq")
+    assert_grad_parity(dk, torch.from_numpy(z["dk_ref_fp32"]), "dk")
+    assert_grad_parity(dv, torch.from_numpy(z["dv_ref_fp32"]), "dv")
+
+
+def test_delta_prep_is_exact_rowsum(dev):
+    """delta = rowsum(O * dO) in fp32 of the bf16 values, for both head dimensions."""
+    for d in (64, 128):
+        gen = torch.Generator().manual_seed(40 + d)
+        o = torch.randn((2, 200, 6, d), generator=gen).to(torch.bfloat16)
+        d_o = torch.randn((2, 200, 6, d), generator=gen).to(torch.bfloat16)
+        delta = hk.attn_bwd_prep(o.to(dev), d_o.to(dev)).cpu()
+        ref = (o.double() * d_o.double()).sum(-1).permute(0, 2, 1).unsqueeze(2)
+        assert delta.shape == (2, 6, 1, 200)
+        assert float((delta.double() - ref).abs().max()) <= 1e-5 * float(ref.abs().max())
+
+
+def test_runs_are_bit_identical_and_layouts_agree(dev):
+    """No atomics anywhere: two runs give the same bits. The pre-shuffle [B,H,N,D] layout followed by the
+    shuffle kernel gives the same dQ as writing [B,N,H,D] directly."""
+    q, k, v = make_prefill_inputs(2, 512, 8, 2, 128, seed=41)
+    d_o = make_do((2, 512, 8, 128), seed=42)
+    a = run_bwd(q, k, v, d_o, True, dev)
+    b = run_bwd(q, k, v, d_o, True, dev)
+    for x, y in zip(a[:3], b[:3]):
+        assert torch.equal(x, y)
+    dq_bhnd = run_bwd(q, k, v, d_o, True, dev, dq_layout=hk.HK_DQ_BHND)[0]
+    assert dq_bhnd.shape == (2, 8, 512, 128)
+    assert torch.equal(dq_bhnd.permute(0, 2, 1, 3), a[0])
+    assert torch.equal(hk.dq_shuffle(dq_bhnd.to(dev)).cpu(), a[0])
+
+
+def test_through_reference_entry_points(dev):
+    """The reference's three calls, in its order and with its argument lists
+    (training/llama/llama/models/attentions/hipkittens.py:96-112, kernels/attn/gqa_backwards/test_python.py:242-263)."""
+    q, k, v = make_prefill_inputs(2, 256, 8, 2, 128, seed=43)
+    d_o = make_do((2, 256, 8, 128), seed=44)
+    for causal in (False, True):
+        Q, K, V, dO = (t.to(dev) for t in (q, k, v, d_o))
+        O = torch.zeros(2, 256, 8, 128, dtype=torch.bfloat16, device=dev)
+        L = torch.zeros(2, 8, 1, 256, dtype=torch.float32, device=dev)
+        hk.load_tk_kernel_fwd(causal).dispatch_fwd(Q, K, V, O, L)
+        tk_kernel_bkwd = hk.load_tk_kernel_bkwd(causal)
+        tk_kernel_bkwd_prep = hk.load_tk_kernel_bkwd_prep(causal)
+        assert tk_kernel_bkwd.default_causal == causal
+        dQ_in = torch.zeros((2, 8, 256, 128), dtype=torch.bfloat16, device=dev)
+        dQ = torch.empty((2, 256, 8, 128), dtype=torch.bfloat16, device=dev)
+        dK = torch.empty((2, 256, 2, 128), dtype=torch.bfloat16, device=dev)
+        dV = torch.empty((2, 256, 2, 128), dtype=torch.bfloat16, device=dev)
+        delta = torch.empty((2, 8, 1, 256), dtype=torch.float32, device=dev)
+        tk_kernel_bkwd_prep.dispatch_prep(O, dO, delta)
+        tk_kernel_bkwd.dispatch_bwd_combined(Q, K, V, dO, dQ_in, dK, dV, L, delta)
+        tk_kernel_bkwd_prep.dispatch_dq_shuffle(dQ_in, dQ)
+        rq, rk, rv, _ = attn_bwd_oracle(q, k, v, d_o, causal=causal)
+        assert_grad_parity(dQ.cpu(), rq, "dq")
+        assert_grad_parity(dK.cpu(), rk, "dk")
+        assert_grad_parity(dV.cpu(), rv, "dv")
+        # the reference's argument checks, with its messages (include/pyutils/pyutils.cuh:22,25,33)
+        with pytest.raises(RuntimeError, match="Tensor must be on CUDA device"):
+            tk_kernel_bkwd_prep.dispatch_prep(O.cpu(), dO, delta)
+        with pytest.raises(RuntimeError, match="Tensor must be contiguous"):
+            tk_kernel_bkwd.dispatch_bwd_combined(Q, K, V, dO, dQ_in.transpose(1, 2), dK, dV, L, delta)
+        with pytest.raises(RuntimeError, match="Expected a torch.Tensor"):
+            tk_kernel_bkwd_prep.dispatch_dq_shuffle(None, dQ)
+        with pytest.raises(RuntimeError, match="pre-shuffle"):
+            tk_kernel_bkwd.dispatch_bwd_combined(Q, K, V, dO, dQ, dK, dV, L, delta)
+
+
+def test_autograd_function_backward(dev):
+    """loss.backward() through the modules the training code uses (hipkittens.py:122-202)."""
+    from hipkittens_b200.attention import HipCrossAttention, HipSelfAttention
+
+    q, k, v = make_prefill_inputs(1, 256, 8, 2, 64, seed=45)
+    d_o = make_do((1, 256, 8, 64), seed=46)
+    qd = q.to(dev).requires_grad_(True)
+    kvd = torch.stack([k, v], dim=2).to(dev).requires_grad_(True)
+    out = HipCrossAttention(causal=True)(qd, kvd)
+    out.backward(d_o.to(dev))
+    rq, rk, rv, _ = attn_bwd_oracle(q, k, v, d_o, causal=True)
+    assert qd.grad.dtype == torch.bfloat16 and kvd.grad.shape == kvd.shape
+    assert_grad_parity(qd.grad.cpu(), rq, "dq")
+    assert_grad_parity(kvd.grad[:, :, 0].cpu(), rk, "dk")
+    assert_grad_parity(kvd.grad[:, :, 1].cpu(), rv, "dv")
+    # self-attention on a packed projection: the forward reads strided views, the backward makes them contiguous
+    q, k, v = make_prefill_inputs(2, 128, 4, 4, 128, seed=47)
+    d_o = make_do((2, 128, 4, 128), seed=48)
+    qkv = torch.stack([q, k, v], dim=2).to(dev).requires_grad_(True)
+    HipSelfAttention(causal=False)(qkv).backward(d_o.to(dev))
+    rq, rk, rv, _ = attn_bwd_oracle(q, k, v, d_o, causal=False)
+    assert_grad_parity(qkv.grad[:, :, 0].cpu(), rq, "dq")
+    assert_grad_parity(qkv.grad[:, :, 1].cpu(), rk, "dk")
+    assert_grad_parity(qkv.grad[:, :, 2].cpu(), rv, "dv")
+
+
+def test_custom_softmax_scale(dev):
+    q, k, v = make_prefill_inputs(1, 256, 2, 1, 128, seed=49)
+    d_o = make_do((1, 256, 2, 128), seed=50)
+    dq, dk, dv, _, _ = run_bwd(q, k, v, d_o, False, dev, scale=0.05)
+    rq, rk, rv, _ = attn_bwd_oracle(q, k, v, d_o, causal=False, softmax_scale=0.05)
+    assert_grad_parity(dq, rq, "dq")
+    assert_grad_parity(dk, rk, "dk")
+    assert_grad_parity(dv, rv, "dv")
+
+
+def test_unsupported_lengths_and_bad_arguments(dev):
+    q, k, v = make_prefill_inputs(1, 200, 2, 1, 128, seed=51)
+    d_o = make_do((1, 200, 2, 128), seed=52).to(dev)
+    o, lse = hk.attn_fwd(q.to(dev), k.to(dev), v.to(dev))
+    delta = hk.attn_bwd_prep(o, d_o)
+    with pytest.raises(hk.HkError) as e:
+        hk.attn_bwd(q.to(dev), k.to(dev), v.to(dev), d_o, lse, delta)  # N = 200 is not a multiple of 128
+    assert e.value.code == _native.HK_EUNSUPPORTED
+    lib = hk.capi()
+    assert lib.hk_attn_bwd(None, 64, 64, 64, 64, 64, 64, 64, 64, 1, 128, 2, 1, 128, 0, 0.0, 0, 0, None) == _native.HK_EINVAL
+    assert lib.hk_attn_bwd(64, 64, 64, 64, 64, 64, 64, 64, 64, 1, 128, 2, 1, 128, 0, 0.0, 7, 0, None) == _native.HK_EINVAL
+    assert lib.hk_attn_dq_shuffle(64, 64, 1, 128, 2, 128, 0, None) == _native.HK_EINVAL  # aliasing buffers
+
+
+def test_full_size_identities_config2(dev):
+    """BASELINE config 2 (B16 N2048 H64 H_KV8 D128), too large for the oracle as a whole: size-independent
+    identities over every (batch, kv head) unit plus oracle parity on one unit.
+      <q, dq> == <k, dk> per unit (the output is invariant under q -> a q, k -> k / a);
+      sum_s dv[s] == sum over the group's heads and rows of dO (softmax rows sum to one)."""
+    b, n, h, hkv, d = 16, 2048, 64, 8, 128
+    g = h // hkv
+    gen = torch.Generator(device=dev).manual_seed(53)
+    q = torch.randn((b, n, h, d), generator=gen, device=dev).to(torch.bfloat16)
+    k = torch.randn((b, n, hkv, d), generator=gen, device=dev).to(torch.bfloat16)
+    v = torch.randn((b, n, hkv, d), generator=gen, device=dev).to(torch.bfloat16)
+    d_o = torch.randn((b, n, h, d), generator=gen, device=dev).to(torch.bfloat16)
+    o, lse = hk.attn_fwd(q, k, v, causal=False)
+    delta = hk.attn_bwd_prep(o, d_o)
+    dq, dk, dv = hk.attn_bwd(q, k, v, d_o, lse, delta, causal=False)
+    assert _native.device_status(0) == 0
+    assert not torch.isnan(dq.float()).any() and not torch.isnan(dk.float()).any() and not torch.isnan(dv.float()).any()
+    qdq = (q.float() * dq.float()).view(b, n, hkv, g * d).sum((1, 3))            # [B, H_KV]
+    kdk = (k.float() * dk.float()).sum((1, 3))
+    scale_ref = (q.float() * dq.float()).abs().view(b, n, hkv, g * d).sum((1, 3))
+    assert float(((qdq - kdk).abs() / scale_ref).max()) <= 1e-3
+    dv_sum = dv.float().sum(1)                                                   # [B, H_KV, D]
+    do_sum = d_o.float().view(b, n, hkv, g, d).sum((1, 3))
+    assert float((dv_sum - do_sum).abs().max()) <= 2e-2 * float(do_sum.abs().max())
+    # one unit against the oracle
+    bi, kh = 5, 3
+    hs = slice(kh * g, (kh + 1) * g)
+    rq, rk, rv, _ = attn_bwd_oracle(q[bi:bi + 1, :, hs].cpu(), k[bi:bi + 1, :, kh:kh + 1].cpu(),
+                                    v[bi:bi + 1, :, kh:kh + 1].cpu(), d_o[bi:bi + 1, :, hs].cpu(), causal=False)
+    # gradients at this size are small (~1e-2): compare with a tolerance scaled to the tensor
+    for name, got, ref in (("dq", dq[bi:bi + 1, :, hs], rq), ("dk", dk[bi:bi + 1, :, kh:kh + 1], rk),
+                           ("dv", dv[bi:bi + 1, :, kh:kh + 1], rv)):
+        diff = (got.float().cpu() - ref).abs()
+        assert float(diff.max()) <= 2e-2 * float(ref.abs().max()) + 1e-2 * float(ref.abs().max()), name
+        assert float(diff.pow(2).sum().sqrt() / ref.pow(2).sum().sqrt()) <= L2TOL, name

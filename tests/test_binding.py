@@ -154,3 +154,64 @@ def test_harness_keeps_both_reference_argument_orders(native_built):
             sys.modules.pop("tk_kernel", None)
             sys.modules.update(mods)
     assert got["gqa"] == got["gqa_causal"] == {"B": 2, "D": 64, "H": 8, "H_KV": 4, "N": 256, "causal": 1}
+
+
+# ---------------------------------------------------------------------------------------------- backward modules
+@pytest.fixture(scope="module")
+def bkwd_mods(native_built):
+    return {c: (hk.load_tk_kernel_bkwd(c), hk.load_tk_kernel_bkwd_prep(c)) for c in (False, True)}
+
+
+def _bwd_nine(B=1, N=128, H=2, HKV=1, D=128):
+    q, kv, stat = (B, N, H, D), (B, N, HKV, D), (B, H, 1, N)
+    return [Tensor(q), Tensor(kv), Tensor(kv), Tensor(q), Tensor((B, H, N, D)), Tensor(kv), Tensor(kv),
+            Tensor(stat, dtype="torch.float32"), Tensor(stat, dtype="torch.float32")]
+
+
+def test_backward_module_and_entry_names(bkwd_mods):
+    """tk_kernel_bkwd.dispatch_bwd_combined, tk_kernel_bkwd_prep.dispatch_prep / dispatch_dq_shuffle
+    (kernels/attn/gqa_backwards/attn_bkwd_non_causal.cpp:3171-3185, attn_bkwd_prep.cpp:227-240)."""
+    for causal, (bk, prep) in bkwd_mods.items():
+        assert bk.__name__.endswith(".tk_kernel_bkwd") and hasattr(bk, "dispatch_bwd_combined")
+        assert prep.__name__.endswith(".tk_kernel_bkwd_prep")
+        assert hasattr(prep, "dispatch_prep") and hasattr(prep, "dispatch_dq_shuffle")
+        assert bk.default_causal is causal
+        assert ("gqa_causal_backwards" in bk.__name__) == causal
+
+
+def test_backward_argument_checks(bkwd_mods):
+    bk, prep = bkwd_mods[False]
+    args = _bwd_nine()
+    with pytest.raises(RuntimeError, match="Expected a torch.Tensor"):
+        bk.dispatch_bwd_combined(None, *args[1:])
+    with pytest.raises(RuntimeError, match="Tensor must be on CUDA device"):
+        bk.dispatch_bwd_combined(Tensor((1, 128, 2, 128), device="cpu"), *args[1:])
+    bad = _bwd_nine()
+    bad[4] = Tensor((1, 128, 2, 128))  # dQ_in given in the post-shuffle layout
+    with pytest.raises(RuntimeError, match="pre-shuffle"):
+        bk.dispatch_bwd_combined(*bad)
+    bad = _bwd_nine()
+    bad[7] = Tensor((1, 2, 1, 128))  # L as bf16
+    with pytest.raises(RuntimeError, match="torch.float32"):
+        bk.dispatch_bwd_combined(*bad)
+    bad = _bwd_nine()
+    bad[5] = Tensor((1, 128, 2, 128))  # dK with Q's head count
+    with pytest.raises(RuntimeError, match="dK/dV"):
+        bk.dispatch_bwd_combined(*bad)
+    with pytest.raises(RuntimeError, match="delta must be"):
+        prep.dispatch_prep(Tensor((1, 128, 2, 128)), Tensor((1, 128, 2, 128)),
+                           Tensor((1, 2, 128, 1), dtype="torch.float32"))
+    with pytest.raises(RuntimeError, match="Tensor must be contiguous"):
+        prep.dispatch_dq_shuffle(Tensor((1, 2, 128, 128), contiguous=False), Tensor((1, 128, 2, 128)))
+    with pytest.raises(RuntimeError, match=r"dQ_in must be \[B, H, N, D\]"):
+        prep.dispatch_dq_shuffle(Tensor((1, 2, 128, 128)), Tensor((1, 2, 128, 128)))
+
+
+def test_backward_has_no_silent_fallback_without_gpu(bkwd_mods):
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    bk, prep = bkwd_mods[True]
+    with pytest.raises(RuntimeError, match="CUDA call failed|unsupported"):
+        bk.dispatch_bwd_combined(*_bwd_nine())
+    with pytest.raises(RuntimeError, match="CUDA call failed|unsupported"):
+        prep.dispatch_prep(Tensor((1, 128, 2, 128)), Tensor((1, 128, 2, 128)), Tensor((1, 2, 1, 128), dtype="torch.float32"))

@@ -100,3 +100,24 @@ def test_fails_loudly_without_a_gpu(native_built):
     with pytest.raises(RuntimeError):
         hk.attn_fwd(torch.zeros(1, 128, 2, 128, dtype=torch.bfloat16), torch.zeros(1, 128, 1, 128, dtype=torch.bfloat16),
                     torch.zeros(1, 128, 1, 128, dtype=torch.bfloat16))
+
+
+def test_bwd_rejects_bad_arguments_before_cuda(native_built):
+    lib = hk.capi()
+
+    def bwd(q=64, lse=64, dq=64, B=1, N=128, H=2, HKV=1, D=128, layout=0):
+        return lib.hk_attn_bwd(q, 64, 64, 64, lse, 64, dq, 64, 64, B, N, H, HKV, D, 0, 0.0, layout, 0, None)
+
+    assert bwd(q=None) == _native.HK_EINVAL
+    assert bwd(lse=None) == _native.HK_EINVAL
+    assert bwd(dq=72) == _native.HK_EINVAL      # not 16-byte aligned
+    assert bwd(lse=68) == _native.HK_EINVAL     # L feeds 16-byte bulk copies
+    assert bwd(H=3, HKV=2) == _native.HK_EINVAL
+    assert bwd(layout=2) == _native.HK_EINVAL
+    assert bwd(D=96) == _native.HK_EUNSUPPORTED
+    assert bwd(N=200) == _native.HK_EUNSUPPORTED  # the backward needs whole 128-row tiles
+    assert lib.hk_attn_bwd_prep(None, 64, 64, 1, 128, 2, 128, 0, None) == _native.HK_EINVAL
+    assert lib.hk_attn_bwd_prep(64, 64, 64, 1, 128, 2, 96, 0, None) == _native.HK_EUNSUPPORTED
+    assert lib.hk_attn_bwd_prep(64, 64, 64, 1, 0, 2, 128, 0, None) == _native.HK_EINVAL
+    assert lib.hk_attn_dq_shuffle(64, 64, 1, 128, 2, 128, 0, None) == _native.HK_EINVAL  # aliasing buffers
+    assert lib.hk_attn_dq_shuffle(64, 128, 1, 128, 2, 100, 0, None) == _native.HK_EINVAL  # D not a multiple of 8
