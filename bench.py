@@ -1,10 +1,10 @@
 #!/usr/bin/env python
-"""Benchmark of the bf16 GQA attention forward (and paged decode) on B200.
+"""Benchmark of the bf16 GQA attention forward (and backward, and paged decode) on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
 
 A step is one pass of the hot path over one batch of synthetic input (one kernel launch for the
-forward; split + combine launches for decode). The default workload is the reference README's default
+forward; split + combine launches for decode; delta prep + dK/dV + dQ launches for the backward). The default workload is the reference README's default
 shape: B=16, N=2048, H=64, H_KV=8, D=128, non-causal (kernels/attn/gqa/test_python.py:22-27).
 TFLOPS = 4*B*N^2*H*D / (2 if causal) / time, the reference's convention (test_python.py:35-38).
 
@@ -37,9 +37,14 @@ WORKLOADS = {
     "gqa_causal_fwd_b4_n8192_h64_kv8_d128": ("fwd", 4, 8192, 64, 8, 128, True),
     "mha_fwd_b16_n4096_h16_d64": ("fwd", 16, 4096, 16, 16, 64, False),
     "paged_decode_s64_ctx512_8192_h64_kv8_d128": ("decode", 64, 0, 64, 8, 128, False),
+    # backward pass (delta prep + dK/dV kernel + dQ kernel), flops = 2.5 x forward (kernels/attn/gqa_backwards/test_python.py:45-48)
+    "gqa_bwd_b16_n2048_h64_kv8_d128": ("bwd", 16, 2048, 64, 8, 128, False),
+    "gqa_causal_bwd_b4_n8192_h64_kv8_d128": ("bwd", 4, 8192, 64, 8, 128, True),
+    "mha_bwd_b16_n4096_h16_d64": ("bwd", 16, 4096, 16, 16, 64, False),
     # reduced copies of the above for ncu captures (same kernels and tile shapes, inputs still beyond L2)
     "profile_gqa_fwd_b4_n2048_h64_kv8_d128": ("fwd", 4, 2048, 64, 8, 128, False),
     "profile_paged_decode_s14_ctx512_8192_h64_kv8_d128": ("decode", 14, 0, 64, 8, 128, False),
+    "profile_gqa_bwd_b4_n2048_h64_kv8_d128": ("bwd", 4, 2048, 64, 8, 128, False),
 }
 DECODE_POOL_PAGES = {"paged_decode_s64_ctx512_8192_h64_kv8_d128": 40000,
                      "profile_paged_decode_s14_ctx512_8192_h64_kv8_d128": 8000}
@@ -72,6 +77,11 @@ def load_peaks():
 
 def fwd_flops(b, n, h, d, causal):
     return 4 * b * n * n * h * d // (2 if causal else 1)
+
+
+def bwd_flops(b, n, h, d, causal):
+    """The reference's convention: 2.5 x the forward count (five products instead of two)."""
+    return 5 * fwd_flops(b, n, h, d, causal) // 2
 
 
 # ------------------------------------------------------------------------------------------ clocks
@@ -172,6 +182,25 @@ def cpu_prefill_sample(b, n, h, hkv, d, causal, budget_s: float, max_units: int)
     return done * fwd_flops(1, n, g, d, causal), dt, done
 
 
+def cpu_bwd_sample(b, n, h, hkv, d, causal, budget_s: float, max_units: int):
+    """Times the backward oracle on (batch, kv-head) units of the workload's shape until `budget_s` is spent."""
+    from hipkittens_b200.synthetic import make_prefill_inputs
+    from oracle.attn_oracle import attn_bwd_oracle
+
+    g = h // hkv
+    q, k, v = make_prefill_inputs(1, n, g, 1, d, seed=123)
+    d_o = make_prefill_inputs(1, n, g, 1, d, seed=124)[0]
+    attn_bwd_oracle(q[:, :128], k[:, :128], v[:, :128], d_o[:, :128], causal)  # warm the thread pool
+    done, t0 = 0, time.perf_counter()
+    while done < max_units:
+        attn_bwd_oracle(q, k, v, d_o, causal)
+        done += 1
+        if time.perf_counter() - t0 >= budget_s:
+            break
+    dt = time.perf_counter() - t0
+    return done * bwd_flops(1, n, g, d, causal), dt, done
+
+
 def cpu_decode_sample(budget_s: float):
     from hipkittens_b200.synthetic import make_paged_inputs
     from oracle.attn_oracle import paged_decode_oracle
@@ -235,7 +264,7 @@ def main() -> int:
     sampler = ClockSampler(local_rank)
 
     # ---------------- inputs resident in HBM
-    if kind == "fwd":
+    if kind in ("fwd", "bwd"):
         if args.scaling == "strong" and world > 1:
             qf, kf, vf = make_prefill_inputs(b, n, h, hkv, d, seed=0)
             parts = shard_tensors(qf, kf, vf, hkv, partition_units(b, hkv, world, rank))
@@ -246,14 +275,29 @@ def main() -> int:
             shards = [(qf.to(dev), kf.to(dev), vf.to(dev))]
         outs = [(torch.empty_like(qs), torch.empty((qs.shape[0], qs.shape[2], 1, n), dtype=torch.float32, device=dev))
                 for qs, _k, _v in shards]
-        my_flops = sum(fwd_flops(qs.shape[0], n, qs.shape[2], d, causal) for qs, _k, _v in shards)
+        flops_of = fwd_flops if kind == "fwd" else bwd_flops
+        my_flops = sum(flops_of(qs.shape[0], n, qs.shape[2], d, causal) for qs, _k, _v in shards)
         my_units = float(my_flops)
+        in_bytes = sum(t.numel() * 2 for sh in shards for t in sh)
 
-        def step():
+        if kind == "fwd":
+            def step():
+                for (qs, ks, vs), (o, l) in zip(shards, outs):
+                    hk.attn_fwd(qs, ks, vs, causal=causal, out=o, lse=l, stream=stream)
+        else:
+            # the backward's inputs: dO (seeded), and O and L from one forward pass outside the timed region
+            gen = torch.Generator(device=dev).manual_seed(1000 + rank)
+            bwd_in = []
             for (qs, ks, vs), (o, l) in zip(shards, outs):
                 hk.attn_fwd(qs, ks, vs, causal=causal, out=o, lse=l, stream=stream)
+                d_o = torch.randn(qs.shape, generator=gen, device=dev).to(torch.bfloat16)
+                bwd_in.append((d_o, torch.empty_like(l), torch.empty_like(qs), torch.empty_like(ks), torch.empty_like(vs)))
+            in_bytes += sum(t[0].numel() * 4 for t in bwd_in)
 
-        in_bytes = sum(t.numel() * 2 for sh in shards for t in sh)
+            def step():
+                for (qs, ks, vs), (o, l), (d_o, delta, dq, dk, dv) in zip(shards, outs, bwd_in):
+                    hk.attn_bwd_prep(o, d_o, delta, stream=stream)
+                    hk.attn_bwd(qs, ks, vs, d_o, l, delta, causal=causal, dq=dq, dk=dk, dv=dv, stream=stream)
     else:
         q, kp, vp, bt, cl = make_paged_inputs(b, h, hkv, d, 16, DECODE_POOL_PAGES[args.workload], 512, 8192, seed=rank,
                                                pool_on=str(dev))
@@ -295,8 +339,9 @@ def main() -> int:
     e2e = None
     if not args.no_e2e:
         e2e = measure_e2e(hk, kind, args, dev, stream, causal, b, n, h, hkv, d,
-                          shards if kind == "fwd" else None,
-                          (q, kp, vp, bt, cl, ws) if kind == "decode" else None, barrier)
+                          shards if kind != "decode" else None,
+                          (q, kp, vp, bt, cl, ws) if kind == "decode" else None, barrier,
+                          (outs, bwd_in) if kind == "bwd" else None)
     sampler.stop()
 
     # ---------------- reduce over ranks: slowest rank's time, summed work
@@ -316,12 +361,14 @@ def main() -> int:
             "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "data": "synthetic",
             "gpu_launches": int(launches), "clocks": clocks, "peaks_source": peaks_src,
         }
-        if kind == "fwd":
+        if kind in ("fwd", "bwd"):
             tflops = total_units / (ms_per_step * 1e-3) / 1e12
             per_launch_flops = my_flops / max(len(shards), 1)
             ach = my_flops / (ms_total / args.steps * 1e-3) / 1e12
             line.update({
-                "metric": "bf16 GQA attn-fwd TFLOPS (4*B*N^2*H*D, /2 causal)", "value": tflops, "unit": "TFLOP/s",
+                "metric": ("bf16 GQA attn-fwd TFLOPS (4*B*N^2*H*D, /2 causal)" if kind == "fwd" else
+                           "bf16 GQA attn-bwd TFLOPS (2.5 * 4*B*N^2*H*D, /2 causal; delta prep + dK/dV + dQ kernels)"),
+                "value": tflops, "unit": "TFLOP/s",
                 "dtype": "bf16",
                 "config": {"workload": args.workload, "B": b, "N": n, "H": h, "H_KV": hkv, "D": d,
                            "causal": causal, "per_gpu_batch": b if args.scaling == "weak" else b / world,
@@ -335,6 +382,10 @@ def main() -> int:
                              "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                              "flops_per_launch": per_launch_flops},
             })
+            if kind == "bwd":
+                line["roofline"]["note"] = ("a step is three launches (delta prep, dK/dV kernel, dQ kernel) timed together; "
+                                            "flops are the reference's 2.5 x forward count, the recomputation of S and dP "
+                                            "in the second kernel is not counted")
             if e2e:
                 line["e2e"] = {"value": total_units / (e2e_ms_max / e2e["steps"] * 1e-3) / 1e12, "unit": "TFLOP/s",
                                "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
@@ -364,7 +415,7 @@ def main() -> int:
     return 0
 
 
-def measure_e2e(hk, kind, args, dev, stream, causal, b, n, h, hkv, d, shards, dec, barrier):
+def measure_e2e(hk, kind, args, dev, stream, causal, b, n, h, hkv, d, shards, dec, barrier, bwd=None):
     """Same step, but inputs start in pinned host memory and results end in pinned host memory, through
     the reference's Python entry (tk_kernel.dispatch_micro / dispatch_paged_decode)."""
     steps = max(1, min(args.steps, 10))
@@ -388,6 +439,36 @@ def measure_e2e(hk, kind, args, dev, stream, causal, b, n, h, hkv, d, shards, de
                 ho[1].copy_(do[1], non_blocking=True)
 
         path = "pinned host -> H2D -> tk_kernel.dispatch_micro -> D2H (O and L)"
+    elif kind == "bwd":
+        # one training-step backward as the reference's autograd function runs it (hipkittens.py:96-112):
+        # q, k, v, O, L (saved by the forward) and dO arrive from pinned host memory, the three reference
+        # calls run, dQ, dK, dV go back to pinned host memory
+        outs, bwd_in = bwd
+        bk, prep = hk.load_tk_kernel_bkwd(causal), hk.load_tk_kernel_bkwd_prep(causal)
+        sets = []
+        for (qs, ks, vs), (o, l), (d_o, delta, dq, dk, dv) in zip(shards, outs, bwd_in):
+            dev_in = [qs, ks, vs, o, l, d_o]
+            hin = [t.cpu().pin_memory() for t in dev_in]
+            dq_in = torch.empty((qs.shape[0], qs.shape[2], qs.shape[1], qs.shape[3]), dtype=torch.bfloat16, device=dev)
+            hout = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (dq, dk, dv)]
+            sets.append((hin, dev_in, delta, dq_in, (dq, dk, dv), hout))
+        h2d = sum(t.numel() * t.element_size() for st in sets for t in st[0])
+        d2h = sum(t.numel() * t.element_size() for st in sets for t in st[5])
+
+        def step():
+            for hin, dev_in, delta, dq_in, (dq, dk, dv), hout in sets:
+                for src, dst in zip(hin, dev_in):
+                    dst.copy_(src, non_blocking=True)
+                qs, ks, vs, o, l, d_o = dev_in
+                prep.dispatch_prep(o, d_o, delta, stream=stream.cuda_stream)
+                bk.dispatch_bwd_combined(qs, ks, vs, d_o, dq_in, dk, dv, l, delta, causal=causal,
+                                         stream=stream.cuda_stream)
+                prep.dispatch_dq_shuffle(dq_in, dq, stream=stream.cuda_stream)
+                for src, dst in zip((dq, dk, dv), hout):
+                    dst.copy_(src, non_blocking=True)
+
+        path = ("pinned host (q, k, v, O, L, dO) -> H2D -> dispatch_prep, dispatch_bwd_combined, dispatch_dq_shuffle "
+                "(each blocking, as in the reference) -> D2H (dQ, dK, dV)")
     else:
         q, kp, vp, bt, cl, ws = dec
         # decode step inputs: the new query token, block table and lengths; the KV pool is state that
@@ -424,11 +505,13 @@ def measure_e2e(hk, kind, args, dev, stream, causal, b, n, h, hkv, d, shards, de
 def cpu_baseline(kind, b, n, h, hkv, d, causal, budget_s):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    if kind == "fwd":
-        flops, dt, units = cpu_prefill_sample(b, n, h, hkv, d, causal, budget_s, max_units=b * hkv)
+    if kind in ("fwd", "bwd"):
+        sample_fn = cpu_prefill_sample if kind == "fwd" else cpu_bwd_sample
+        flops, dt, units = sample_fn(b, n, h, hkv, d, causal, budget_s, max_units=b * hkv)
         return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                 "sample": f"{units} of {b * hkv} (batch, kv-head) units of the workload shape, {dt:.1f} s, "
-                          "oracle (fp32 PyTorch restatement of the reference math path)"}
+                          "oracle (fp32 PyTorch restatement of the reference math path"
+                          + (")" if kind == "fwd" else " and of its derivative)")}
     toks, _ctx, dt, reps = cpu_decode_sample(budget_s)
     return {"value": toks / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
             "sample": f"{reps} passes over 8 sequences with ctx ~ U{{512..8192}}, {dt:.1f} s, paged oracle"}
@@ -445,8 +528,9 @@ def run_reference_arm(args, rank, world, kind, b, n, h, hkv, d, causal) -> int:
     per_step_budget = max(0.2, min(3.0, 150.0 / total_steps))
     times, work = [], []
     for i in range(total_steps):
-        if kind == "fwd":
-            flops, dt, units = cpu_prefill_sample(b, n, h, hkv, d, causal, per_step_budget, max_units=b * hkv)
+        if kind in ("fwd", "bwd"):
+            sample_fn = cpu_prefill_sample if kind == "fwd" else cpu_bwd_sample
+            flops, dt, units = sample_fn(b, n, h, hkv, d, causal, per_step_budget, max_units=b * hkv)
             if i >= args.warmup:
                 times.append(dt)
                 work.append(flops)
@@ -456,9 +540,10 @@ def run_reference_arm(args, rank, world, kind, b, n, h, hkv, d, causal) -> int:
                 times.append(dt)
                 work.append(toks)
     total_t, total_w = sum(times), sum(work)
-    if kind == "fwd":
+    if kind in ("fwd", "bwd"):
         value, unit = total_w / total_t / 1e12, "TFLOP/s"
-        metric = "bf16 GQA attn-fwd TFLOPS (4*B*N^2*H*D, /2 causal)"
+        metric = ("bf16 GQA attn-fwd TFLOPS (4*B*N^2*H*D, /2 causal)" if kind == "fwd" else
+                  "bf16 GQA attn-bwd TFLOPS (2.5 * 4*B*N^2*H*D, /2 causal; delta prep + dK/dV + dQ kernels)")
         sample = (f"each step: as many (batch, kv-head) units of the workload shape as fit in {per_step_budget:.1f} s "
                   f"(of {b * hkv} per full pass)")
         config = {"workload": args.workload, "B": b, "N": n, "H": h, "H_KV": hkv, "D": d, "causal": causal}
