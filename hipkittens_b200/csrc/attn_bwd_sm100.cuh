@@ -18,9 +18,10 @@
 //   attn_bwd_dq_kernel    one query tile of 128 rows stays in shared memory; the K/V tiles stream past it:
 //                         S = Q K^T, dP = dO V^T, dQ += dS K.
 // Both kernels are persistent (one CTA per SM, 384 threads): warps 0-7 do the element-wise work (two
-// threads per TMEM lane, 64 columns each), warp 8 is the TMA producer, warp 9 issues the UMMAs.
-// The two score-shaped accumulators are overwritten in place by their bf16 successors (P over S, dS over
-// dP), each half-row thread writing into the columns it has just read.
+// threads per TMEM lane, 64 columns each), warp 8 is the TMA producer, warps 9 and 10 each hold one UMMA
+// issuing thread (one per dependency chain).
+// TMEM is laid out so that a score-shaped accumulator is free for the next tile as soon as the element-wise
+// warps hold it in registers (its bf16 successor goes elsewhere: see the column maps in the kernels).
 //
 // Sequence lengths must be a multiple of 128 (the reference's kernels need a multiple of 256).
 #pragma once
@@ -53,6 +54,9 @@ struct BwdParams {
   float scale;
   float scale_log2;
   int* status;
+#ifdef HK_TRACE
+  long long* trace;     // [4 roles][4096] clock stamps of CTA 0 (debug builds only)
+#endif
 };
 
 template <int D>
@@ -219,7 +223,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   constexpr int kSub = SM::kSubTileBytes;
   constexpr int kChunks = D / 64;
   constexpr int RA = SM::kRingA, RB = SM::kRingB;
-  enum { KV_FULL = 0, KV_EMPTY, ST_FULL, DP_FULL, P_FULL, DS_FULL, ACC_FULL, QA_FULL = 8, QA_EMPTY = 14,
+  enum { KV_FULL = 0, KV_EMPTY, ST_FULL, DP_FULL, P_FULL, DS_FULL, ACC_FULL, S_FREE, QA_FULL = 8, QA_EMPTY = 14,
          RB_FULL = 20, RB_EMPTY = 24, STAT_FULL = 28, STAT_EMPTY = 30, CTRL = 32 };
 
   extern __shared__ __align__(1024) uint8_t bwd_smem[];
@@ -243,11 +247,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   if (tid == 0) {
     *abort_word = 0;
     mbar_init(bars + KV_FULL, 1);
-    mbar_init(bars + KV_EMPTY, 1);
+    mbar_init(bars + KV_EMPTY, 2);  // one arrival per issuing thread (K feeds S^T, V feeds dP^T)
     mbar_init(bars + ST_FULL, 1);
     mbar_init(bars + DP_FULL, 1);
-    mbar_init(bars + P_FULL, 8);   // one arrival per compute warp
+    mbar_init(bars + P_FULL, 8);    // one arrival per element-wise warp
     mbar_init(bars + DS_FULL, 8);
+    mbar_init(bars + S_FREE, 8);
     mbar_init(bars + ACC_FULL, 1);
     for (int s = 0; s < RA; ++s) {
       mbar_init(bars + QA_FULL + s, 1);
@@ -273,8 +278,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const uint32_t tmem = *tmem_slot;
   volatile uint32_t* abortp = abort_word;
   const int G = p.H / p.H_KV;
-  // TMEM columns: S^T [0,128)  dP^T [128,256)  dK [256,256+D)  dV [256+D,256+2D)
-  constexpr uint32_t cST = 0, cDP = 128, cDK = 256, cDV = 256 + D;
+  // TMEM columns: X = S^T [0,128); Y = dP^T [128,256), later overwritten by the two bf16 operands: each half-row
+  // thread group keeps to the 64 columns it read, P^T in their first 32, dS^T in their last 32;
+  // dK [256,256+D); dV [256+D,256+2D).
+  constexpr uint32_t cST = 0, cY = 128, cDK = 256, cDV = 256 + D;
 
   if (warp < 8) {
     // ------------------------------------------------------------------ element-wise warps
@@ -283,11 +290,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const int row = (warp & 3) * 32 + lane;            // key row inside the block == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + lane_addr + cST + hf * 64;
-    const uint32_t tP = tmem + lane_addr + cDP + hf * 64;
+    const uint32_t tY = tmem + lane_addr + cY + hf * 64;
     const float c = p.scale_log2;
     constexpr float kNegLog2e = -1.4426950408889634f;
     uint32_t it = 0, acc_cnt = 0;
     bool ok = true;
+#ifdef HK_TRACE
+    const bool trace_on = (warp == 0) && lane == 0 && p.trace != nullptr;
+    int trace_n = 0;
+#endif
     for (int round = 0; ok; ++round) {
       const int idx = item_for_round(round, blockIdx.x, gridDim.x);
       if (idx >= p.n_items) {
@@ -296,19 +307,25 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       }
       const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
       for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
+        HK_STAMP(0, 0);
         const bool diag = CAUSAL && (n % w.cnt_i == 0);  // the query tile at the key block's own position
         const float* sL = sStat + (it & 1) * 256 + hf * 64;
         const float* sDl = sL + 128;
-        // ---- P^T = exp2(S^T * c - L * log2(e))
+        // ---- S^T into registers; X is free for S^T of the next iteration right away
         ok = mbar_wait(bars + ST_FULL, it & 1, abortp, kWaitLimitCycles) &&
              mbar_wait(bars + STAT_FULL + (it & 1), (it >> 1) & 1, abortp, kWaitLimitCycles);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
+        HK_STAMP(0, 1);
         uint32_t su[64];
         tmem_ld32(tS, su);
         tmem_ld32(tS + 32, su + 32);
         tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + S_FREE);
+        // ---- p = exp2(s * c - L * log2(e)), kept in fp32 for dS
 #pragma unroll
         for (int q4 = 0; q4 < 16; ++q4) {
           const float4 l4 = *reinterpret_cast<const float4*>(sL + q4 * 4);
@@ -321,26 +338,30 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             su[col] = __float_as_uint(pe);
           }
         }
+        HK_STAMP(0, 2);
+        // ---- dP^T into registers; only then may the bf16 operands overwrite Y
+        ok = mbar_wait(bars + DP_FULL, it & 1, abortp, kWaitLimitCycles);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        HK_STAMP(0, 3);
+        uint32_t du[64];
+        tmem_ld32(tY, du);
+        tmem_ld32(tY + 32, du + 32);
+        tmem_wait_ld();
         {
           uint32_t pk[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) pk[i] = pack_bf16x2(__uint_as_float(su[2 * i]), __uint_as_float(su[2 * i + 1]));
-          tmem_st32(tS, pk);  // P^T over the first 32 columns this thread has just read
+          tmem_st32(tY, pk);  // P^T: first 32 of this thread's 64 columns
         }
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + P_FULL);
+        HK_STAMP(0, 4);
         // ---- dS^T = P^T * (dP^T - delta)
-        ok = mbar_wait(bars + DP_FULL, it & 1, abortp, kWaitLimitCycles);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
         {
-          uint32_t du[64];
-          tmem_ld32(tP, du);
-          tmem_ld32(tP + 32, du + 32);
-          tmem_wait_ld();
           uint32_t pk[32];
 #pragma unroll
           for (int q4 = 0; q4 < 16; ++q4) {
@@ -352,7 +373,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             pk[q4 * 2] = pack_bf16x2(ds0, ds1);
             pk[q4 * 2 + 1] = pack_bf16x2(ds2, ds3);
           }
-          tmem_st32(tP, pk);
+          tmem_st32(tY + 32, pk);  // dS^T: last 32 of this thread's 64 columns
         }
         tmem_wait_st();
         tc_fence_before();
@@ -361,6 +382,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           mbar_arrive(bars + DS_FULL);
           mbar_arrive(bars + STAT_EMPTY + (it & 1));
         }
+        HK_STAMP(0, 5);
       }
       if (!ok) break;
       // ---- epilogue: dK = scale * acc, dV = acc
@@ -435,20 +457,65 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
       }
     } else if (warp == 9 && lane == 0) {
-      // ---------------- UMMA issuer
-      // Per iteration: dV += P^T dO, S^T(next), dK += dS^T Q, dP^T(next). The two chains S^T -> P^T -> dV and
-      // dP^T -> dS^T -> dK interleave, so the pipe works on one while the element-wise warps finish the other.
+      // ---------------- UMMA issuer A: S^T = K Q^T, as soon as the previous S^T has been read
+      // Two threads issue. This one runs ahead with the S^T products, which only wait for the Q tile and for the
+      // element-wise warps' word that X is free; issuer B follows the dependent chain dV, dK, dP^T. A thread that
+      // issues returns only a few MMAs ahead of the pipe, so its commits and mbarrier waits (~180 clocks per product)
+      // would otherwise let the pipe run dry between products.
       constexpr uint32_t tile16 = kTile >> 4;
       const uint32_t k_lo = smem_desc_lo(smem_u32(sK), 16);
-      const uint32_t v_lo = smem_desc_lo(smem_u32(sV), 16);
       const uint32_t q_lo0 = smem_desc_lo(smem_u32(sQ), 16);       // K-major view (B of S^T)
+      uint32_t item_cnt = 0, sf_cnt = 0;
+      int qa = 0;
+      uint32_t qa_par = 0;
+      bool ok = true;
+#ifdef HK_TRACE
+      const bool trace_on = p.trace != nullptr;
+      int trace_n = 0;
+#endif
+      for (int round = 0; ok; ++round) {
+        const int idx = item_for_round(round, blockIdx.x, gridDim.x);
+        if (idx >= p.n_items) {
+          if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
+          continue;
+        }
+        const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
+        ok = mbar_wait(bars + KV_FULL, item_cnt & 1, abortp, kWaitLimitCycles);
+        if (!ok) break;
+        ++item_cnt;
+        for (int n = 0; n < w.n_iter && ok; ++n, ++sf_cnt) {
+          // X has been read (first S^T ever: passes at once)
+          ok = mbar_wait(bars + S_FREE, (sf_cnt & 1) ^ 1, abortp, kWaitLimitCycles) &&
+               mbar_wait(bars + QA_FULL + qa, qa_par, abortp, kWaitLimitCycles);
+          if (!ok) break;
+          tc_fence_after();
+          HK_STAMP(2, 12);
+          bwd_issue_ss<D>(tmem + cST, k_lo, q_lo0 + qa * tile16);
+          umma_commit(bars + ST_FULL);
+          HK_STAMP(2, 13);
+          if (++qa == RA) {
+            qa = 0;
+            qa_par ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(bars + KV_EMPTY);  // K has fed its last product (issuer B arrives for V)
+      }
+    } else if (warp == 10 && lane == 0) {
+      // ---------------- UMMA issuer B: dV += P^T dO, dK += dS^T Q, then dP^T of the next iteration into Y
+      constexpr uint32_t tile16 = kTile >> 4;
+      const uint32_t v_lo = smem_desc_lo(smem_u32(sV), 16);
       const uint32_t q_mn0 = smem_desc_lo(smem_u32(sQ), kSub);     // MN-major view (B of dK)
-      const uint32_t do_lo0 = smem_desc_lo(smem_u32(sDO), 16);
-      const uint32_t do_mn0 = smem_desc_lo(smem_u32(sDO), kSub);
+      const uint32_t do_lo0 = smem_desc_lo(smem_u32(sDO), 16);     // K-major view (B of dP^T)
+      const uint32_t do_mn0 = smem_desc_lo(smem_u32(sDO), kSub);   // MN-major view (B of dV)
       uint32_t item_cnt = 0, it = 0;
       int qa = 0, rb = 0;
       uint32_t qa_par = 0, rb_par = 0;
       bool ok = true;
+#ifdef HK_TRACE
+      const bool trace_on = p.trace != nullptr;
+      int trace_n = 0;
+#endif
       for (int round = 0; ok; ++round) {
         const int idx = item_for_round(round, blockIdx.x, gridDim.x);
         if (idx >= p.n_items) {
@@ -457,19 +524,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
         const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
         ok = mbar_wait(bars + KV_FULL, item_cnt & 1, abortp, kWaitLimitCycles) &&
-             mbar_wait(bars + QA_FULL + qa, qa_par, abortp, kWaitLimitCycles);
+             mbar_wait(bars + RB_FULL + rb, rb_par, abortp, kWaitLimitCycles);
         if (!ok) break;
         ++item_cnt;
         tc_fence_after();
-        bwd_issue_ss<D>(tmem + cST, k_lo, q_lo0 + qa * tile16);
-        umma_commit(bars + ST_FULL);
-        ok = mbar_wait(bars + RB_FULL + rb, rb_par, abortp, kWaitLimitCycles);
-        if (!ok) break;
-        tc_fence_after();
-        bwd_issue_ss<D>(tmem + cDP, v_lo, do_lo0 + rb * tile16);
+        bwd_issue_ss<D>(tmem + cY, v_lo, do_lo0 + rb * tile16);  // ordered behind the previous item's dV / dK
         umma_commit(bars + DP_FULL);
         for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
           const int cur_q = qa, cur_do = rb;
+          const uint32_t cur_q_par = qa_par;
           if (++qa == RA) {
             qa = 0;
             qa_par ^= 1;
@@ -478,30 +541,29 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             rb = 0;
             rb_par ^= 1;
           }
-          const bool more = (n + 1 < w.n_iter);
           ok = mbar_wait(bars + P_FULL, it & 1, abortp, kWaitLimitCycles);
           if (!ok) break;
           tc_fence_after();
-          bwd_issue_ts<D>(tmem + cDV, tmem + cST, do_mn0 + cur_do * tile16, n > 0);
-          umma_commit(bars + RB_EMPTY + cur_do);
-          if (more) {
-            ok = mbar_wait(bars + QA_FULL + qa, qa_par, abortp, kWaitLimitCycles);
-            if (!ok) break;
-            tc_fence_after();
-            bwd_issue_ss<D>(tmem + cST, k_lo, q_lo0 + qa * tile16);
-            umma_commit(bars + ST_FULL);
-          }
-          ok = mbar_wait(bars + DS_FULL, it & 1, abortp, kWaitLimitCycles);
+          HK_STAMP(3, 10);
+          bwd_issue_ts<D>(tmem + cDV, tmem + cY, do_mn0 + cur_do * tile16, n > 0);
+          umma_commit(bars + RB_EMPTY + cur_do);  // dO fed dP^T earlier and dV now
+          HK_STAMP(3, 11);
+          ok = mbar_wait(bars + DS_FULL, it & 1, abortp, kWaitLimitCycles) &&
+               mbar_wait(bars + QA_FULL + cur_q, cur_q_par, abortp, kWaitLimitCycles);
           if (!ok) break;
           tc_fence_after();
-          bwd_issue_ts<D>(tmem + cDK, tmem + cDP, q_mn0 + cur_q * tile16, n > 0);
+          HK_STAMP(3, 14);
+          bwd_issue_ts<D>(tmem + cDK, tmem + cY + 32, q_mn0 + cur_q * tile16, n > 0);
+          // S^T of this stage (issuer A) completed before dS^T could be computed, so this one arrival frees Q
           umma_commit(bars + QA_EMPTY + cur_q);
-          if (more) {
+          HK_STAMP(3, 15);
+          if (n + 1 < w.n_iter) {
             ok = mbar_wait(bars + RB_FULL + rb, rb_par, abortp, kWaitLimitCycles);
             if (!ok) break;
             tc_fence_after();
-            bwd_issue_ss<D>(tmem + cDP, v_lo, do_lo0 + rb * tile16);
+            bwd_issue_ss<D>(tmem + cY, v_lo, do_lo0 + rb * tile16);  // overwrites P^T(n), dS^T(n): behind dV(n), dK(n)
             umma_commit(bars + DP_FULL);
+            HK_STAMP(3, 17);
           }
         }
         if (!ok) break;
@@ -577,8 +639,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   constexpr int kSub = SM::kSubTileBytes;
   constexpr int kChunks = D / 64;
   constexpr int RA = SM::kRingA, RB = SM::kRingB;
-  enum { QDO_FULL = 0, QDO_EMPTY, S_FULL0, S_FULL1, DP_FULL, DS_FULL, DQ_FULL, KA_FULL = 8, KA_EMPTY = 14,
-         VB_FULL = 20, VB_EMPTY = 24, CTRL = 32 };
+  enum { QDO_FULL = 0, QDO_EMPTY, S_FULL, S_FREE, DP_FULL, DP_FREE, DS_FULL, DS_FREE, KA_FULL = 8, KA_EMPTY = 14,
+         VB_FULL = 20, VB_EMPTY = 24, DQ_FULL = 28, CTRL = 32 };
 
   extern __shared__ __align__(1024) uint8_t bwd_smem[];
   uint8_t* sQ = bwd_smem;
@@ -600,11 +662,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   if (tid == 0) {
     *abort_word = 0;
     mbar_init(bars + QDO_FULL, 1);
-    mbar_init(bars + QDO_EMPTY, 1);
-    mbar_init(bars + S_FULL0, 1);
-    mbar_init(bars + S_FULL1, 1);
+    mbar_init(bars + QDO_EMPTY, 2);  // Q released by issuer A, dO by issuer B
+    mbar_init(bars + S_FULL, 1);
+    mbar_init(bars + S_FREE, 8);     // one arrival per element-wise warp once its part is in registers
     mbar_init(bars + DP_FULL, 1);
+    mbar_init(bars + DP_FREE, 8);
     mbar_init(bars + DS_FULL, 8);
+    mbar_init(bars + DS_FREE, 1);
     mbar_init(bars + DQ_FULL, 1);
     for (int s = 0; s < RA; ++s) {
       mbar_init(bars + KA_FULL + s, 1);
@@ -625,8 +689,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   volatile uint32_t* abortp = abort_word;
-  // TMEM columns: S (even iterations) [0,128)  dP [128,256)  dQ [256,256+D)  S (odd iterations) [384,512)
-  constexpr uint32_t cS0 = 0, cDP = 128, cDQ = 256, cS1 = 384;
+  // TMEM columns: S [0,128)  dP [128,256)  dQ [256,256+D)  dS (bf16, 64 packed columns) [384,448).
+  // Nothing aliases: S and dP are free for the next tile as soon as they are in registers.
+  constexpr uint32_t cS = 0, cDP = 128, cDQ = 256, cDS = 384;
 
   if (warp < 8) {
     // ------------------------------------------------------------------ element-wise warps
@@ -634,10 +699,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const int hf = warp >> 2;                          // which 64 key columns of the tile
     const int row = (warp & 3) * 32 + lane;            // query row inside the tile == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + lane_addr + cS + hf * 64;
     const uint32_t tP = tmem + lane_addr + cDP + hf * 64;
+    const uint32_t tDS = tmem + lane_addr + cDS + hf * 32;
     const float c = p.scale_log2;
-    uint32_t it = 0, s_cnt0 = 0, s_cnt1 = 0, dq_cnt = 0;
+    uint32_t it = 0, dq_cnt = 0;
     bool ok = true;
+#ifdef HK_TRACE
+    const bool trace_on = (warp == 0) && lane == 0 && p.trace != nullptr;
+    int trace_n = 0;
+#endif
     for (int round = 0; ok; ++round) {
       const int idx = item_for_round(round, blockIdx.x, gridDim.x);
       if (idx >= p.n_items) {
@@ -649,46 +720,59 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       const float nl = p.lse[srow] * -1.4426950408889634f;
       const float dl = p.delta[srow];
       for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
-        const int buf = n & 1;
         const bool diag = CAUSAL && (n == w.n_iter - 1);
-        ok = mbar_wait(bars + S_FULL0 + buf, (buf ? s_cnt1 : s_cnt0) & 1, abortp, kWaitLimitCycles);
+        HK_STAMP(0, 0);
+        ok = mbar_wait(bars + S_FULL, it & 1, abortp, kWaitLimitCycles);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (buf) ++s_cnt1; else ++s_cnt0;
         tc_fence_after();
+        HK_STAMP(0, 1);
         uint32_t su[64];
-        const uint32_t tS = tmem + lane_addr + (buf ? cS1 : cS0) + hf * 64;
         tmem_ld32(tS, su);
         tmem_ld32(tS + 32, su + 32);
         tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + S_FREE);  // issuer A may overwrite S with the next tile's
 #pragma unroll
         for (int col = 0; col < 64; ++col) {
           float pe = ex2_approx(fmaf(__uint_as_float(su[col]), c, nl));
           if (diag && (hf * 64 + col) > row) pe = 0.f;  // key later than the query
           su[col] = __float_as_uint(pe);
         }
+        HK_STAMP(0, 2);
         ok = mbar_wait(bars + DP_FULL, it & 1, abortp, kWaitLimitCycles);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
+        HK_STAMP(0, 3);
+        uint32_t pk[32];
         {
           uint32_t du[64];
           tmem_ld32(tP, du);
           tmem_ld32(tP + 32, du + 32);
           tmem_wait_ld();
-          uint32_t pk[32];
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bars + DP_FREE);  // issuer B may overwrite dP with the next tile's
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const float ds0 = __uint_as_float(su[2 * i]) * (__uint_as_float(du[2 * i]) - dl);
             const float ds1 = __uint_as_float(su[2 * i + 1]) * (__uint_as_float(du[2 * i + 1]) - dl);
             pk[i] = pack_bf16x2(ds0, ds1);
           }
-          tmem_st32(tP, pk);  // dS over the first 32 columns this thread has just read
         }
+        // dS of the previous tile has been consumed by its dQ product (first tile ever: passes at once)
+        ok = mbar_wait(bars + DS_FREE, (it & 1) ^ 1, abortp, kWaitLimitCycles);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        tmem_st32(tDS, pk);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + DS_FULL);
+        HK_STAMP(0, 4);
       }
       if (!ok) break;
       // ---- epilogue: dQ = scale * acc
@@ -754,33 +838,66 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         }
       }
     } else if (warp == 9 && lane == 0) {
-      // ---------------- UMMA issuer
-      // Order: S(0) dP(0) S(1) | dQ(n) dP(n+1) S(n+2) | ... S alternates between two TMEM buffers, so S(n+1) is
-      // complete long before the element-wise warps finish tile n; dP(n+1) and dQ(n) share columns (dS(n) sits
-      // in the dP buffer) and simply follow each other in the pipe.
+      // ---------------- UMMA issuer A: S = Q K^T, as soon as the previous S has been read
+      // Two issuing threads, as in the dK/dV kernel: this one runs ahead with the S products, issuer B follows
+      // with dP (as soon as the previous dP has been read) and dQ += dS K.
       constexpr uint32_t tile16 = kTile >> 4;
       const uint32_t q_lo = smem_desc_lo(smem_u32(sQ), 16);
-      const uint32_t do_lo = smem_desc_lo(smem_u32(sDO), 16);
       const uint32_t k_lo0 = smem_desc_lo(smem_u32(sK), 16);      // K-major view (B of S)
+      uint32_t item_cnt = 0, sf_cnt = 0;
+      int ks = 0;
+      uint32_t ks_par = 0;
+      bool ok = true;
+#ifdef HK_TRACE
+      const bool trace_on = p.trace != nullptr;
+      int trace_n = 0;
+#endif
+      for (int round = 0; ok; ++round) {
+        const int idx = item_for_round(round, blockIdx.x, gridDim.x);
+        if (idx >= p.n_items) {
+          if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
+          continue;
+        }
+        const DqItem w = decode_dq_item<CAUSAL>(p, idx);
+        ok = mbar_wait(bars + QDO_FULL, item_cnt & 1, abortp, kWaitLimitCycles);
+        if (!ok) break;
+        ++item_cnt;
+        for (int n = 0; n < w.n_iter && ok; ++n, ++sf_cnt) {
+          ok = mbar_wait(bars + S_FREE, (sf_cnt & 1) ^ 1, abortp, kWaitLimitCycles) &&
+               mbar_wait(bars + KA_FULL + ks, ks_par, abortp, kWaitLimitCycles);
+          if (!ok) break;
+          tc_fence_after();
+          HK_STAMP(2, 12);
+          bwd_issue_ss<D>(tmem + cS, q_lo, k_lo0 + ks * tile16);
+          umma_commit(bars + S_FULL);
+          HK_STAMP(2, 13);
+          if (++ks == RA) {
+            ks = 0;
+            ks_par ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(bars + QDO_EMPTY);  // Q has fed its last product (issuer B arrives for dO)
+      }
+    } else if (warp == 10 && lane == 0) {
+      // ---------------- UMMA issuer B: dP = dO V^T, dQ += dS K
+      constexpr uint32_t tile16 = kTile >> 4;
+      const uint32_t do_lo = smem_desc_lo(smem_u32(sDO), 16);
       const uint32_t k_mn0 = smem_desc_lo(smem_u32(sK), kSub);    // MN-major view (B of dQ)
       const uint32_t v_lo0 = smem_desc_lo(smem_u32(sV), 16);
-      uint32_t item_cnt = 0, it = 0;
-      int ks = 0, kq = 0, vb = 0;            // K stage of the next S, K stage of the next dQ, V stage of the next dP
-      uint32_t ks_par = 0, vb_par = 0;
+      uint32_t item_cnt = 0, it = 0, dpf_cnt = 0;
+      int kq = 0, vb = 0;
+      uint32_t kq_par = 0, vb_par = 0;
       bool ok = true;
-      auto issue_s = [&](int buf) -> bool {
-        if (!mbar_wait(bars + KA_FULL + ks, ks_par, abortp, kWaitLimitCycles)) return false;
-        tc_fence_after();
-        bwd_issue_ss<D>(tmem + (buf ? cS1 : cS0), q_lo, k_lo0 + ks * tile16);
-        umma_commit(bars + S_FULL0 + buf);
-        if (++ks == RA) {
-          ks = 0;
-          ks_par ^= 1;
-        }
-        return true;
-      };
+#ifdef HK_TRACE
+      const bool trace_on = p.trace != nullptr;
+      int trace_n = 0;
+#endif
       auto issue_dp = [&]() -> bool {
+        // the previous dP has been read (first dP ever: passes at once)
+        if (!mbar_wait(bars + DP_FREE, (dpf_cnt & 1) ^ 1, abortp, kWaitLimitCycles)) return false;
         if (!mbar_wait(bars + VB_FULL + vb, vb_par, abortp, kWaitLimitCycles)) return false;
+        ++dpf_cnt;
         tc_fence_after();
         bwd_issue_ss<D>(tmem + cDP, do_lo, v_lo0 + vb * tile16);
         umma_commit(bars + DP_FULL);
@@ -801,24 +918,37 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         ok = mbar_wait(bars + QDO_FULL, item_cnt & 1, abortp, kWaitLimitCycles);
         if (!ok) break;
         ++item_cnt;
-        tc_fence_after();
-        ok = issue_s(0) && issue_dp();
-        if (ok && w.n_iter > 1) ok = issue_s(1);
+        ok = issue_dp();
         if (!ok) break;
-        if (w.n_iter == 1) umma_commit(bars + QDO_EMPTY);  // Q and dO have fed their last products
+        if (w.n_iter == 1) umma_commit(bars + QDO_EMPTY);  // dO has fed its last product
         for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
-          ok = mbar_wait(bars + DS_FULL, it & 1, abortp, kWaitLimitCycles);
-          if (!ok) break;
-          tc_fence_after();
-          bwd_issue_ts<D>(tmem + cDQ, tmem + cDP, k_mn0 + kq * tile16, n > 0);
-          umma_commit(bars + KA_EMPTY + kq);
-          if (++kq == RA) kq = 0;
           if (n + 1 < w.n_iter) {
             ok = issue_dp();
             if (!ok) break;
             if (n + 2 == w.n_iter) umma_commit(bars + QDO_EMPTY);
+            HK_STAMP(3, 12);
           }
-          if (n + 2 < w.n_iter) ok = issue_s(n & 1);
+          ok = mbar_wait(bars + DS_FULL, it & 1, abortp, kWaitLimitCycles) &&
+               mbar_wait(bars + KA_FULL + kq, kq_par, abortp, kWaitLimitCycles);
+          if (!ok) break;
+          tc_fence_after();
+          HK_STAMP(3, 10);
+          {
+            constexpr uint32_t idesc = make_idesc_bf16(kBlockM, D, true);
+            constexpr uint32_t desc_hi = smem_desc_hi(1024);
+            const uint32_t b_lo = k_mn0 + kq * tile16;
+#pragma unroll
+            for (int k = 0; k < kBlockN / 16; ++k)
+              umma_ts_lohi(tmem + cDQ, tmem + cDS + k * 8, b_lo + k * 128, desc_hi, idesc, (n > 0 || k > 0) ? 1u : 0u);
+          }
+          // S of this tile (issuer A) completed before dS could be computed, so this one arrival frees the K tile
+          umma_commit(bars + KA_EMPTY + kq);
+          umma_commit(bars + DS_FREE);
+          HK_STAMP(3, 11);
+          if (++kq == RA) {
+            kq = 0;
+            kq_par ^= 1;
+          }
         }
         if (!ok) break;
         umma_commit(bars + DQ_FULL);

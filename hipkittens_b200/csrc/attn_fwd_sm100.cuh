@@ -249,7 +249,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     uint32_t s_cnt = 0, o_cnt = 0, pv_cnt = 0;
     bool ok = true;
 #ifdef HK_TRACE
-    const bool trace_on = ((warp & 3) == 0) && lane == 0;
+    const bool trace_on = ((warp & 3) == 0) && lane == 0 && p.trace != nullptr;
     int trace_n = 0;
 #endif
     for (int round = 0; ok; ++round) {
@@ -506,7 +506,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       int pending_v = -1, pending_k = -1;  // ring stages whose release is deferred (see the main loop)
       bool ok = true;
 #ifdef HK_TRACE
-      const bool trace_on = true;
+      const bool trace_on = p.trace != nullptr;
       int trace_n = 0;
 #endif
       // S[slot] = Q[slot] * K^T with K in ring stage `st`

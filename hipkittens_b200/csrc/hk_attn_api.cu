@@ -139,6 +139,7 @@ int use_device(int device, DeviceState** out) {
 
 #ifdef HK_TRACE
 long long* g_trace_buf = nullptr;
+int g_trace_bwd_kernel = 0;  // which backward kernel stamps: 0 = dK/dV, 1 = dQ
 #endif
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -196,11 +197,18 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
   const int nb = N / hk::kBlockM;
   p.n_items = B * H_KV * nb;
   int grid = p.n_items < sm_count ? p.n_items : sm_count;
+#ifdef HK_TRACE
+  long long* const trace_buf = p.trace;
+  p.trace = g_trace_bwd_kernel == 0 ? trace_buf : nullptr;
+#endif
   hk::attn_bwd_dkdv_kernel<D, CAUSAL><<<grid, hk::kBwdThreads, hk::BwdSmem<D>::kDynBytes, stream>>>(tq, tk, tv, tdo, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   HK_CUDA(cudaGetLastError());
   p.n_items = B * H * nb;
   grid = p.n_items < sm_count ? p.n_items : sm_count;
+#ifdef HK_TRACE
+  p.trace = g_trace_bwd_kernel == 1 ? trace_buf : nullptr;
+#endif
   hk::attn_bwd_dq_kernel<D, CAUSAL><<<grid, hk::kBwdThreads, hk::BwdSmem<D>::kDynBytes, stream>>>(tq, tk, tv, tdo, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   HK_CUDA(cudaGetLastError());
@@ -213,6 +221,7 @@ extern "C" {
 
 #ifdef HK_TRACE
 void hk_debug_set_trace(long long* buf) { g_trace_buf = buf; }
+void hk_debug_set_trace_bwd_kernel(int which) { g_trace_bwd_kernel = which; }
 #endif
 
 int hk_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int N, int H, int H_KV,
@@ -361,6 +370,9 @@ int hk_attn_bwd(const void* q, const void* k, const void* v, const void* d_o, co
   p.scale = softmax_scale > 0.f ? softmax_scale : 1.0f / std::sqrt(float(D));
   p.scale_log2 = p.scale * 1.4426950408889634f;
   p.status = st->status;
+#ifdef HK_TRACE
+  p.trace = g_trace_buf;
+#endif
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (D == 128) return causal ? launch_bwd<128, true>(tq, tk, tv, tdo, p, B, N, H, H_KV, st->sm_count, stream)
                               : launch_bwd<128, false>(tq, tk, tv, tdo, p, B, N, H, H_KV, st->sm_count, stream);
