@@ -63,9 +63,15 @@ template <int D>
 struct BwdSmem {
   static constexpr int kTileBytes = kBlockM * D * 2;
   static constexpr int kSubTileBytes = kBlockM * 128;
-  static constexpr int kRingA = (D == 128) ? 3 : 6;  // tiles that live for a whole iteration (Q resp. K)
-  static constexpr int kRingB = (D == 128) ? 2 : 4;  // tiles that are consumed early (dO resp. V)
+  static constexpr int kRingA = (D == 128) ? 3 : 6;  // dK/dV kernel: Q tiles (live for a whole iteration)
+  static constexpr int kRingB = (D == 128) ? 2 : 4;  // dK/dV kernel: dO tiles
+  // dQ kernel: a K tile lives from S(n) to dQ(n), more than an iteration, so its ring is the deep one; a V tile is
+  // consumed by one early product, and its successor is not needed for another ~1500 clocks: one stage is enough
+  // at D = 128, where shared memory holds 7 tiles.
+  static constexpr int kRingK = (D == 128) ? 4 : 7;
+  static constexpr int kRingV = (D == 128) ? 1 : 3;
   static constexpr int kTiles = 2 + kRingA + kRingB;
+  static_assert(2 + kRingK + kRingV == kTiles, "both kernels use the same shared-memory footprint");
   static constexpr int kStatBytes = 2 * 2 * kBlockM * 4;  // two stages of (L, delta) for one query tile
   static constexpr int kBarBytes = 512;
   static constexpr int kDynBytes = kTiles * kTileBytes + kStatBytes + kBarBytes;
@@ -225,6 +231,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   constexpr int RA = SM::kRingA, RB = SM::kRingB;
   enum { KV_FULL = 0, KV_EMPTY, ST_FULL, DP_FULL, P_FULL, DS_FULL, ACC_FULL, S_FREE, QA_FULL = 8, QA_EMPTY = 14,
          RB_FULL = 20, RB_EMPTY = 24, STAT_FULL = 28, STAT_EMPTY = 30, CTRL = 32 };
+  static_assert(RA <= 6 && RB <= 4, "barrier slots");
 
   extern __shared__ __align__(1024) uint8_t bwd_smem[];
   uint8_t* sK = bwd_smem;
@@ -325,17 +332,29 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + S_FREE);
-        // ---- p = exp2(s * c - L * log2(e)), kept in fp32 for dS
+        // ---- p = exp2(s * c - L * log2(e)), kept in fp32 for dS (two columns per packed fp32x2 instruction)
+        {
+          const uint64_t c2 = pack2(c, c);
+          const uint64_t k2 = pack2(kNegLog2e, kNegLog2e);
 #pragma unroll
-        for (int q4 = 0; q4 < 16; ++q4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(sL + q4 * 4);
-          const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+          for (int q4 = 0; q4 < 16; ++q4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(sL + q4 * 4);
+            const uint64_t xa = fma2(pack2(__uint_as_float(su[q4 * 4 + 0]), __uint_as_float(su[q4 * 4 + 1])), c2,
+                                     mul2(pack2(l4.x, l4.y), k2));
+            const uint64_t xb = fma2(pack2(__uint_as_float(su[q4 * 4 + 2]), __uint_as_float(su[q4 * 4 + 3])), c2,
+                                     mul2(pack2(l4.z, l4.w), k2));
+            float x0, x1, x2, x3;
+            unpack2(xa, x0, x1);
+            unpack2(xb, x2, x3);
+            su[q4 * 4 + 0] = __float_as_uint(ex2_approx(x0));
+            su[q4 * 4 + 1] = __float_as_uint(ex2_approx(x1));
+            su[q4 * 4 + 2] = __float_as_uint(ex2_approx(x2));
+            su[q4 * 4 + 3] = __float_as_uint(ex2_approx(x3));
+          }
+          if (diag) {
+            // the query tile at the key block's own position: queries earlier than the key see nothing
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int col = q4 * 4 + e;
-            float pe = ex2_approx(fmaf(__uint_as_float(su[col]), c, lv[e] * kNegLog2e));
-            if (diag && (hf * 64 + col) < row) pe = 0.f;  // query earlier than the key
-            su[col] = __float_as_uint(pe);
+            for (int col = 0; col < 64; ++col) su[col] = (hf * 64 + col) < row ? 0u : su[col];
           }
         }
         HK_STAMP(0, 2);
@@ -366,10 +385,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
           for (int q4 = 0; q4 < 16; ++q4) {
             const float4 d4 = *reinterpret_cast<const float4*>(sDl + q4 * 4);
-            const float ds0 = __uint_as_float(su[q4 * 4 + 0]) * (__uint_as_float(du[q4 * 4 + 0]) - d4.x);
-            const float ds1 = __uint_as_float(su[q4 * 4 + 1]) * (__uint_as_float(du[q4 * 4 + 1]) - d4.y);
-            const float ds2 = __uint_as_float(su[q4 * 4 + 2]) * (__uint_as_float(du[q4 * 4 + 2]) - d4.z);
-            const float ds3 = __uint_as_float(su[q4 * 4 + 3]) * (__uint_as_float(du[q4 * 4 + 3]) - d4.w);
+            const uint64_t m1 = pack2(-1.0f, -1.0f);
+            const uint64_t ta = fma2(pack2(d4.x, d4.y), m1,
+                                     pack2(__uint_as_float(du[q4 * 4 + 0]), __uint_as_float(du[q4 * 4 + 1])));
+            const uint64_t tb = fma2(pack2(d4.z, d4.w), m1,
+                                     pack2(__uint_as_float(du[q4 * 4 + 2]), __uint_as_float(du[q4 * 4 + 3])));
+            float ds0, ds1, ds2, ds3;
+            unpack2(mul2(pack2(__uint_as_float(su[q4 * 4 + 0]), __uint_as_float(su[q4 * 4 + 1])), ta), ds0, ds1);
+            unpack2(mul2(pack2(__uint_as_float(su[q4 * 4 + 2]), __uint_as_float(su[q4 * 4 + 3])), tb), ds2, ds3);
             pk[q4 * 2] = pack_bf16x2(ds0, ds1);
             pk[q4 * 2 + 1] = pack_bf16x2(ds2, ds3);
           }
@@ -638,9 +661,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   constexpr int kTile = SM::kTileBytes;
   constexpr int kSub = SM::kSubTileBytes;
   constexpr int kChunks = D / 64;
-  constexpr int RA = SM::kRingA, RB = SM::kRingB;
-  enum { QDO_FULL = 0, QDO_EMPTY, S_FULL, S_FREE, DP_FULL, DP_FREE, DS_FULL, DS_FREE, KA_FULL = 8, KA_EMPTY = 14,
-         VB_FULL = 20, VB_EMPTY = 24, DQ_FULL = 28, CTRL = 32 };
+  constexpr int RA = SM::kRingK, RB = SM::kRingV;
+  enum { QDO_FULL = 0, QDO_EMPTY, S_FULL, S_FREE, DP_FULL, DP_FREE, DS_FULL, DS_FREE, KA_FULL = 8, KA_EMPTY = 15,
+         VB_FULL = 22, VB_EMPTY = 25, DQ_FULL = 28, CTRL = 32 };
+  static_assert(RA <= 7 && RB <= 3, "barrier slots");
 
   extern __shared__ __align__(1024) uint8_t bwd_smem[];
   uint8_t* sQ = bwd_smem;
@@ -734,11 +758,20 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + S_FREE);  // issuer A may overwrite S with the next tile's
+        {
+          const uint64_t c2 = pack2(c, c), nl2 = pack2(nl, nl);
 #pragma unroll
-        for (int col = 0; col < 64; ++col) {
-          float pe = ex2_approx(fmaf(__uint_as_float(su[col]), c, nl));
-          if (diag && (hf * 64 + col) > row) pe = 0.f;  // key later than the query
-          su[col] = __float_as_uint(pe);
+          for (int i = 0; i < 32; ++i) {
+            float x0, x1;
+            unpack2(fma2(pack2(__uint_as_float(su[2 * i]), __uint_as_float(su[2 * i + 1])), c2, nl2), x0, x1);
+            su[2 * i] = __float_as_uint(ex2_approx(x0));
+            su[2 * i + 1] = __float_as_uint(ex2_approx(x1));
+          }
+          if (diag) {
+            // diagonal tile: keys later than the query see nothing
+#pragma unroll
+            for (int col = 0; col < 64; ++col) su[col] = (hf * 64 + col) > row ? 0u : su[col];
+          }
         }
         HK_STAMP(0, 2);
         ok = mbar_wait(bars + DP_FULL, it & 1, abortp, kWaitLimitCycles);
@@ -755,10 +788,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bars + DP_FREE);  // issuer B may overwrite dP with the next tile's
+          const uint64_t ndl2 = pack2(-dl, -dl);
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const float ds0 = __uint_as_float(su[2 * i]) * (__uint_as_float(du[2 * i]) - dl);
-            const float ds1 = __uint_as_float(su[2 * i + 1]) * (__uint_as_float(du[2 * i + 1]) - dl);
+            float ds0, ds1;
+            unpack2(mul2(pack2(__uint_as_float(su[2 * i]), __uint_as_float(su[2 * i + 1])),
+                         add2(pack2(__uint_as_float(du[2 * i]), __uint_as_float(du[2 * i + 1])), ndl2)),
+                    ds0, ds1);
             pk[i] = pack_bf16x2(ds0, ds1);
           }
         }
