@@ -36,10 +36,52 @@
 
 namespace hk {
 
-constexpr int kBwdThreads = 384;
-constexpr int kBwdRegsAtLaunch = 168;  // see the setmaxnreg calls; same budget as the forward kernel
+// Element-wise warps: kBwdParts threads share one TMEM lane (one score row), each owning 128 / kBwdParts columns.
+// 4 parts = 16 element-wise warps (4 per scheduler) in a 640-thread CTA without register re-allocation; 2 parts =
+// 8 warps in a 384-thread CTA that re-balances registers like the forward kernel. Both were measured at the same
+// throughput (the kernels run against the power cap, not against their cycle count); 4 is the default because it
+// needs no setmaxnreg bookkeeping.
+#ifndef HK_BWD_PARTS
+#define HK_BWD_PARTS 4
+#endif
+constexpr int kBwdParts = HK_BWD_PARTS;
+static_assert(kBwdParts == 2 || kBwdParts == 4, "2 or 4 threads per TMEM lane");
+constexpr int kBwdCW = 4 * kBwdParts;              // element-wise warps
+constexpr int kBwdPC = 128 / kBwdParts;            // score columns per element-wise thread
+constexpr int kBwdThreads = 32 * (kBwdCW + 4);     // + TMA producer, two UMMA issuers, one idle warp
+// Register budget: all warps start with kBwdRegsAtLaunch; the element-wise warps then grow by exactly what the
+// other four warps give up (setmaxnreg only moves registers inside the CTA's own allocation: asking for more than
+// was released would block forever): 8 x (208 - 168) = 4 x (168 - 88). With 4 parts (640 threads) every thread keeps
+// its 96 registers: the element-wise code fits, and no re-allocation is done.
+constexpr int kBwdRegsAtLaunch = kBwdParts == 2 ? 168 : 96;
+constexpr int kBwdRegsGrown = kBwdParts == 2 ? 208 : 96;
+constexpr int kBwdRegsShrunk = kBwdParts == 2 ? 88 : 96;
+static_assert(kBwdCW * (kBwdRegsGrown - kBwdRegsAtLaunch) == 4 * (kBwdRegsAtLaunch - kBwdRegsShrunk),
+              "registers taken by the element-wise warps must equal the registers released by the other warps");
 
 enum : int { kStatusSmemAlign = 3 };  // dynamic shared memory did not start on a 1024-byte boundary
+
+// kBwdPC fp32 columns of this thread's lane -> registers / kBwdPC/2 packed bf16 columns -> TMEM
+__device__ __forceinline__ void bwd_ld_part(uint32_t taddr, uint32_t* r) {
+#pragma unroll
+  for (int c = 0; c < kBwdPC / 32; ++c) ptx::tmem_ld32(taddr + c * 32, r + c * 32);
+}
+__device__ __forceinline__ void bwd_st_packed(uint32_t taddr, const uint32_t* r) {
+  if constexpr (kBwdPC == 64) ptx::tmem_st32(taddr, r);
+  else ptx::tmem_st16(taddr, r);
+}
+__device__ __forceinline__ void bwd_grow_registers() {
+  if constexpr (kBwdParts == 2) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    static_assert(kBwdParts != 2 || kBwdRegsGrown == 208, "keep the immediate above in step");
+  }
+}
+__device__ __forceinline__ void bwd_shrink_registers() {
+  if constexpr (kBwdParts == 2) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+    static_assert(kBwdParts != 2 || kBwdRegsShrunk == 88, "keep the immediate above in step");
+  }
+}
 
 struct BwdParams {
   const float* lse;     // [B,H,1,N] from the forward pass (natural log)
@@ -150,8 +192,8 @@ __device__ __forceinline__ void bwd_issue_ss(uint32_t d_tmem, uint32_t a_lo, uin
     ptx::umma_ss_lohi(d_tmem, a_lo + off, b_lo + off, desc_hi, idesc, k > 0 ? 1u : 0u);
   }
 }
-// Gradient-shaped product: d[128 x D] (+)= a * b, a = bf16 [128 x 128] in TMEM (written by the two half-row
-// thread groups: 16-element steps 0-3 start at column 0, steps 4-7 at column 64 of the score buffer),
+// Gradient-shaped product: d[128 x D] (+)= a * b, a = bf16 [128 x 128] in TMEM (each of the kBwdParts thread
+// groups of a row keeps its packed columns inside the kBwdPC columns it owns, starting at `a_tmem`),
 // b = a 128 x D tile in shared memory read MN-major (its rows are the contraction index).
 template <int D>
 __device__ __forceinline__ void bwd_issue_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo_mn, bool acc) {
@@ -159,21 +201,24 @@ __device__ __forceinline__ void bwd_issue_ts(uint32_t d_tmem, uint32_t a_tmem, u
   constexpr uint32_t desc_hi = ptx::smem_desc_hi(1024);
 #pragma unroll
   for (int k = 0; k < kBlockN / 16; ++k)
-    ptx::umma_ts_lohi(d_tmem, a_tmem + (k / 4) * 64 + (k % 4) * 8, b_lo_mn + k * 128, desc_hi, idesc,
-                      (acc || k > 0) ? 1u : 0u);
+    ptx::umma_ts_lohi(d_tmem, a_tmem + ((16 * k) / kBwdPC) * kBwdPC + ((16 * k) % kBwdPC) / 2, b_lo_mn + k * 128,
+                      desc_hi, idesc, (acc || k > 0) ? 1u : 0u);
 }
 
-// Accumulator rows (this thread's TMEM lane, D/2 columns from `taddr`) -> bf16 -> global, scaled.
+// Accumulator rows (this thread's TMEM lane, D / kBwdParts columns from `taddr`) -> bf16 -> global, scaled.
 template <int D>
-__device__ __forceinline__ void bwd_store_half_row(uint32_t taddr, __nv_bfloat16* dst, float mul) {
+__device__ __forceinline__ void bwd_store_part_row(uint32_t taddr, __nv_bfloat16* dst, float mul) {
+  constexpr int kCols = D / kBwdParts;  // 64, 32 or 16
+  constexpr int kChunk = kCols >= 32 ? 32 : 16;
 #pragma unroll
-  for (int cc = 0; cc < D / 64; ++cc) {
-    uint32_t o[32];
-    ptx::tmem_ld32(taddr + cc * 32, o);
+  for (int cc = 0; cc < kCols / kChunk; ++cc) {
+    uint32_t o[kChunk];
+    if constexpr (kChunk == 32) ptx::tmem_ld32(taddr + cc * 32, o);
+    else ptx::tmem_ld16(taddr, o);
     ptx::tmem_wait_ld();
-    uint4* out = reinterpret_cast<uint4*>(dst + cc * 32);
+    uint4* out = reinterpret_cast<uint4*>(dst + cc * kChunk);
 #pragma unroll
-    for (int v4 = 0; v4 < 4; ++v4) {
+    for (int v4 = 0; v4 < kChunk / 8; ++v4) {
       uint4 val;
       val.x = ptx::pack_bf16x2(__uint_as_float(o[v4 * 8 + 0]) * mul, __uint_as_float(o[v4 * 8 + 1]) * mul);
       val.y = ptx::pack_bf16x2(__uint_as_float(o[v4 * 8 + 2]) * mul, __uint_as_float(o[v4 * 8 + 3]) * mul);
@@ -257,9 +302,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     mbar_init(bars + KV_EMPTY, 2);  // one arrival per issuing thread (K feeds S^T, V feeds dP^T)
     mbar_init(bars + ST_FULL, 1);
     mbar_init(bars + DP_FULL, 1);
-    mbar_init(bars + P_FULL, 8);    // one arrival per element-wise warp
-    mbar_init(bars + DS_FULL, 8);
-    mbar_init(bars + S_FREE, 8);
+    mbar_init(bars + P_FULL, kBwdCW);    // one arrival per element-wise warp
+    mbar_init(bars + DS_FULL, kBwdCW);
+    mbar_init(bars + S_FREE, kBwdCW);
     mbar_init(bars + ACC_FULL, 1);
     for (int s = 0; s < RA; ++s) {
       mbar_init(bars + QA_FULL + s, 1);
@@ -271,11 +316,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bars + STAT_FULL + s, 1);
-      mbar_init(bars + STAT_EMPTY + s, 8);
+      mbar_init(bars + STAT_EMPTY + s, kBwdCW);
     }
     fence_mbar_init();
   }
-  if (warp == 8) {
+  if (warp == kBwdCW) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -290,14 +335,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   // dK [256,256+D); dV [256+D,256+2D).
   constexpr uint32_t cST = 0, cY = 128, cDK = 256, cDV = 256 + D;
 
-  if (warp < 8) {
+  if (warp < kBwdCW) {
     // ------------------------------------------------------------------ element-wise warps
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
-    const int hf = warp >> 2;                          // which 64 query columns of the tile
+    bwd_grow_registers();
+    const int part = warp >> 2;                        // which kBwdPC query columns of the tile
     const int row = (warp & 3) * 32 + lane;            // key row inside the block == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tS = tmem + lane_addr + cST + hf * 64;
-    const uint32_t tY = tmem + lane_addr + cY + hf * 64;
+    const uint32_t tS = tmem + lane_addr + cST + part * kBwdPC;
+    const uint32_t tY = tmem + lane_addr + cY + part * kBwdPC;
     const float c = p.scale_log2;
     constexpr float kNegLog2e = -1.4426950408889634f;
     uint32_t it = 0, acc_cnt = 0;
@@ -316,7 +361,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
         HK_STAMP(0, 0);
         const bool diag = CAUSAL && (n % w.cnt_i == 0);  // the query tile at the key block's own position
-        const float* sL = sStat + (it & 1) * 256 + hf * 64;
+        const float* sL = sStat + (it & 1) * 256 + part * kBwdPC;
         const float* sDl = sL + 128;
         // ---- S^T into registers; X is free for S^T of the next iteration right away
         ok = mbar_wait(bars + ST_FULL, it & 1, abortp, kWaitLimitCycles) &&
@@ -325,9 +370,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         if (!ok) break;
         tc_fence_after();
         HK_STAMP(0, 1);
-        uint32_t su[64];
-        tmem_ld32(tS, su);
-        tmem_ld32(tS + 32, su + 32);
+        uint32_t su[kBwdPC];
+        bwd_ld_part(tS, su);
         tmem_wait_ld();
         tc_fence_before();
         __syncwarp();
@@ -337,7 +381,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           const uint64_t c2 = pack2(c, c);
           const uint64_t k2 = pack2(kNegLog2e, kNegLog2e);
 #pragma unroll
-          for (int q4 = 0; q4 < 16; ++q4) {
+          for (int q4 = 0; q4 < kBwdPC / 4; ++q4) {
             const float4 l4 = *reinterpret_cast<const float4*>(sL + q4 * 4);
             const uint64_t xa = fma2(pack2(__uint_as_float(su[q4 * 4 + 0]), __uint_as_float(su[q4 * 4 + 1])), c2,
                                      mul2(pack2(l4.x, l4.y), k2));
@@ -354,7 +398,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           if (diag) {
             // the query tile at the key block's own position: queries earlier than the key see nothing
 #pragma unroll
-            for (int col = 0; col < 64; ++col) su[col] = (hf * 64 + col) < row ? 0u : su[col];
+            for (int col = 0; col < kBwdPC; ++col) su[col] = (part * kBwdPC + col) < row ? 0u : su[col];
           }
         }
         HK_STAMP(0, 2);
@@ -364,15 +408,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         if (!ok) break;
         tc_fence_after();
         HK_STAMP(0, 3);
-        uint32_t du[64];
-        tmem_ld32(tY, du);
-        tmem_ld32(tY + 32, du + 32);
+        uint32_t du[kBwdPC];
+        bwd_ld_part(tY, du);
         tmem_wait_ld();
         {
-          uint32_t pk[32];
+          uint32_t pk[kBwdPC / 2];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) pk[i] = pack_bf16x2(__uint_as_float(su[2 * i]), __uint_as_float(su[2 * i + 1]));
-          tmem_st32(tY, pk);  // P^T: first 32 of this thread's 64 columns
+          for (int i = 0; i < kBwdPC / 2; ++i)
+            pk[i] = pack_bf16x2(__uint_as_float(su[2 * i]), __uint_as_float(su[2 * i + 1]));
+          bwd_st_packed(tY, pk);  // P^T: first half of this thread's columns
         }
         tmem_wait_st();
         tc_fence_before();
@@ -381,9 +425,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         HK_STAMP(0, 4);
         // ---- dS^T = P^T * (dP^T - delta)
         {
-          uint32_t pk[32];
+          uint32_t pk[kBwdPC / 2];
 #pragma unroll
-          for (int q4 = 0; q4 < 16; ++q4) {
+          for (int q4 = 0; q4 < kBwdPC / 4; ++q4) {
             const float4 d4 = *reinterpret_cast<const float4*>(sDl + q4 * 4);
             const uint64_t m1 = pack2(-1.0f, -1.0f);
             const uint64_t ta = fma2(pack2(d4.x, d4.y), m1,
@@ -396,7 +440,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             pk[q4 * 2] = pack_bf16x2(ds0, ds1);
             pk[q4 * 2 + 1] = pack_bf16x2(ds2, ds3);
           }
-          tmem_st32(tY + 32, pk);  // dS^T: last 32 of this thread's 64 columns
+          bwd_st_packed(tY + kBwdPC / 2, pk);  // dS^T: second half of this thread's columns
         }
         tmem_wait_st();
         tc_fence_before();
@@ -414,14 +458,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       if (!ok) break;
       ++acc_cnt;
       tc_fence_after();
-      const size_t off = ((static_cast<size_t>(w.b) * p.N + w.j * kBlockN + row) * p.H_KV + w.kvh) * D + hf * (D / 2);
-      bwd_store_half_row<D>(tmem + lane_addr + cDK + hf * (D / 2), p.dk + off, p.scale);
-      bwd_store_half_row<D>(tmem + lane_addr + cDV + hf * (D / 2), p.dv + off, 1.0f);
+      const size_t off = ((static_cast<size_t>(w.b) * p.N + w.j * kBlockN + row) * p.H_KV + w.kvh) * D + part * (D / kBwdParts);
+      bwd_store_part_row<D>(tmem + lane_addr + cDK + part * (D / kBwdParts), p.dk + off, p.scale);
+      bwd_store_part_row<D>(tmem + lane_addr + cDV + part * (D / kBwdParts), p.dv + off, 1.0f);
       tc_fence_before();  // orders these reads before the next item's first dV product (published through P_FULL)
     }
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
-    if (warp == 8 && lane == 0) {
+    bwd_shrink_registers();
+    if (warp == kBwdCW && lane == 0) {
       // ---------------- TMA producer
       prefetch_tmap(&tmap_q);
       prefetch_tmap(&tmap_k);
@@ -479,7 +523,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           }
         }
       }
-    } else if (warp == 9 && lane == 0) {
+    } else if (warp == kBwdCW + 1 && lane == 0) {
       // ---------------- UMMA issuer A: S^T = K Q^T, as soon as the previous S^T has been read
       // Two threads issue. This one runs ahead with the S^T products, which only wait for the Q tile and for the
       // element-wise warps' word that X is free; issuer B follows the dependent chain dV, dK, dP^T. A thread that
@@ -524,7 +568,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         if (!ok) break;
         umma_commit(bars + KV_EMPTY);  // K has fed its last product (issuer B arrives for V)
       }
-    } else if (warp == 10 && lane == 0) {
+    } else if (warp == kBwdCW + 2 && lane == 0) {
       // ---------------- UMMA issuer B: dV += P^T dO, dK += dS^T Q, then dP^T of the next iteration into Y
       constexpr uint32_t tile16 = kTile >> 4;
       const uint32_t v_lo = smem_desc_lo(smem_u32(sV), 16);
@@ -576,7 +620,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           if (!ok) break;
           tc_fence_after();
           HK_STAMP(3, 14);
-          bwd_issue_ts<D>(tmem + cDK, tmem + cY + 32, q_mn0 + cur_q * tile16, n > 0);
+          bwd_issue_ts<D>(tmem + cDK, tmem + cY + kBwdPC / 2, q_mn0 + cur_q * tile16, n > 0);
           // S^T of this stage (issuer A) completed before dS^T could be computed, so this one arrival frees Q
           umma_commit(bars + QA_EMPTY + cur_q);
           HK_STAMP(3, 15);
@@ -607,7 +651,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     if (tid == 0) atomicCAS(p.status, kStatusOk, kStatusTimeout);
     __syncthreads();
   }
-  if (warp == 8) {
+  if (warp == kBwdCW) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
@@ -688,10 +732,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     mbar_init(bars + QDO_FULL, 1);
     mbar_init(bars + QDO_EMPTY, 2);  // Q released by issuer A, dO by issuer B
     mbar_init(bars + S_FULL, 1);
-    mbar_init(bars + S_FREE, 8);     // one arrival per element-wise warp once its part is in registers
+    mbar_init(bars + S_FREE, kBwdCW);     // one arrival per element-wise warp once its part is in registers
     mbar_init(bars + DP_FULL, 1);
-    mbar_init(bars + DP_FREE, 8);
-    mbar_init(bars + DS_FULL, 8);
+    mbar_init(bars + DP_FREE, kBwdCW);
+    mbar_init(bars + DS_FULL, kBwdCW);
     mbar_init(bars + DS_FREE, 1);
     mbar_init(bars + DQ_FULL, 1);
     for (int s = 0; s < RA; ++s) {
@@ -704,7 +748,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     }
     fence_mbar_init();
   }
-  if (warp == 8) {
+  if (warp == kBwdCW) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -717,15 +761,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   // Nothing aliases: S and dP are free for the next tile as soon as they are in registers.
   constexpr uint32_t cS = 0, cDP = 128, cDQ = 256, cDS = 384;
 
-  if (warp < 8) {
+  if (warp < kBwdCW) {
     // ------------------------------------------------------------------ element-wise warps
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
-    const int hf = warp >> 2;                          // which 64 key columns of the tile
+    bwd_grow_registers();
+    const int part = warp >> 2;                        // which kBwdPC key columns of the tile
     const int row = (warp & 3) * 32 + lane;            // query row inside the tile == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tS = tmem + lane_addr + cS + hf * 64;
-    const uint32_t tP = tmem + lane_addr + cDP + hf * 64;
-    const uint32_t tDS = tmem + lane_addr + cDS + hf * 32;
+    const uint32_t tS = tmem + lane_addr + cS + part * kBwdPC;
+    const uint32_t tP = tmem + lane_addr + cDP + part * kBwdPC;
+    const uint32_t tDS = tmem + lane_addr + cDS + part * (kBwdPC / 2);
     const float c = p.scale_log2;
     uint32_t it = 0, dq_cnt = 0;
     bool ok = true;
@@ -751,9 +795,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         if (!ok) break;
         tc_fence_after();
         HK_STAMP(0, 1);
-        uint32_t su[64];
-        tmem_ld32(tS, su);
-        tmem_ld32(tS + 32, su + 32);
+        uint32_t su[kBwdPC];
+        bwd_ld_part(tS, su);
         tmem_wait_ld();
         tc_fence_before();
         __syncwarp();
@@ -761,7 +804,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         {
           const uint64_t c2 = pack2(c, c), nl2 = pack2(nl, nl);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < kBwdPC / 2; ++i) {
             float x0, x1;
             unpack2(fma2(pack2(__uint_as_float(su[2 * i]), __uint_as_float(su[2 * i + 1])), c2, nl2), x0, x1);
             su[2 * i] = __float_as_uint(ex2_approx(x0));
@@ -770,7 +813,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           if (diag) {
             // diagonal tile: keys later than the query see nothing
 #pragma unroll
-            for (int col = 0; col < 64; ++col) su[col] = (hf * 64 + col) > row ? 0u : su[col];
+            for (int col = 0; col < kBwdPC; ++col) su[col] = (part * kBwdPC + col) > row ? 0u : su[col];
           }
         }
         HK_STAMP(0, 2);
@@ -779,18 +822,17 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         if (!ok) break;
         tc_fence_after();
         HK_STAMP(0, 3);
-        uint32_t pk[32];
+        uint32_t pk[kBwdPC / 2];
         {
-          uint32_t du[64];
-          tmem_ld32(tP, du);
-          tmem_ld32(tP + 32, du + 32);
+          uint32_t du[kBwdPC];
+          bwd_ld_part(tP, du);
           tmem_wait_ld();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bars + DP_FREE);  // issuer B may overwrite dP with the next tile's
           const uint64_t ndl2 = pack2(-dl, -dl);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < kBwdPC / 2; ++i) {
             float ds0, ds1;
             unpack2(mul2(pack2(__uint_as_float(su[2 * i]), __uint_as_float(su[2 * i + 1])),
                          add2(pack2(__uint_as_float(du[2 * i]), __uint_as_float(du[2 * i + 1])), ndl2)),
@@ -803,7 +845,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        tmem_st32(tDS, pk);
+        bwd_st_packed(tDS, pk);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
@@ -818,13 +860,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       ++dq_cnt;
       tc_fence_after();
       __nv_bfloat16* dst = p.dq + w.b * p.dq_stride_b + (static_cast<long long>(w.i) * kBlockM + row) * p.dq_stride_n +
-                           w.h * p.dq_stride_h + hf * (D / 2);
-      bwd_store_half_row<D>(tmem + lane_addr + cDQ + hf * (D / 2), dst, p.scale);
+                           w.h * p.dq_stride_h + part * (D / kBwdParts);
+      bwd_store_part_row<D>(tmem + lane_addr + cDQ + part * (D / kBwdParts), dst, p.scale);
       tc_fence_before();  // orders these reads before the next item's first dQ product (published through DS_FULL)
     }
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
-    if (warp == 8 && lane == 0) {
+    bwd_shrink_registers();
+    if (warp == kBwdCW && lane == 0) {
       // ---------------- TMA producer
       prefetch_tmap(&tmap_q);
       prefetch_tmap(&tmap_k);
@@ -873,7 +915,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           }
         }
       }
-    } else if (warp == 9 && lane == 0) {
+    } else if (warp == kBwdCW + 1 && lane == 0) {
       // ---------------- UMMA issuer A: S = Q K^T, as soon as the previous S has been read
       // Two issuing threads, as in the dK/dV kernel: this one runs ahead with the S products, issuer B follows
       // with dP (as soon as the previous dP has been read) and dQ += dS K.
@@ -915,7 +957,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         if (!ok) break;
         umma_commit(bars + QDO_EMPTY);  // Q has fed its last product (issuer B arrives for dO)
       }
-    } else if (warp == 10 && lane == 0) {
+    } else if (warp == kBwdCW + 2 && lane == 0) {
       // ---------------- UMMA issuer B: dP = dO V^T, dQ += dS K
       constexpr uint32_t tile16 = kTile >> 4;
       const uint32_t do_lo = smem_desc_lo(smem_u32(sDO), 16);
@@ -1002,7 +1044,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     if (tid == 0) atomicCAS(p.status, kStatusOk, kStatusTimeout);
     __syncthreads();
   }
-  if (warp == 8) {
+  if (warp == kBwdCW) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
