@@ -58,6 +58,8 @@ NCU_TRAFFIC_BYTES = {
     # metric captures of the full workloads (profiles/attn_fwd_kernel_causal_d128_and_mha_d64.md)
     "gqa_causal_fwd_b4_n8192_h64_kv8_d128": 1.109e9 + 0.520e9,
     "mha_fwd_b16_n4096_h16_d64": 0.404e9 + 0.118e9,
+    # backward, 4 x the B=4 capture of the two main kernels (profiles/attn_bwd_kernels_gqa_bwd_d128.md) + the prep kernel
+    "gqa_bwd_b16_n2048_h64_kv8_d128": 4 * (358.2e6 + 413.1e6) + 1.082e9,
     # 14-sequence capture (280.26 MB for sum ctx 66 608) scaled by sum ctx to 275 479; split + combine
     "paged_decode_s64_ctx512_8192_h64_kv8_d128": (273.46e6 + 4.73e6 + 2.47e6) * 275479 / 66608,
 }
