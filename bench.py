@@ -41,6 +41,10 @@ WORKLOADS = {
     "gqa_bwd_b16_n2048_h64_kv8_d128": ("bwd", 16, 2048, 64, 8, 128, False),
     "gqa_causal_bwd_b4_n8192_h64_kv8_d128": ("bwd", 4, 8192, 64, 8, 128, True),
     "mha_bwd_b16_n4096_h16_d64": ("bwd", 16, 4096, 16, 16, 64, False),
+    # the two byte-moving neighbours of the path: rotary pre-pass (the reference harness's shape, kernels/rotary/test_python.py:10-13)
+    # and the KV-cache append of one prefill chunk (16 sequences x 2048 new tokens)
+    "rotary_b16_h16_n2048_d128": ("rotary", 16, 2048, 16, 16, 128, False),
+    "paged_kv_append_s16_t2048_kv8_d128": ("append", 16, 2048, 64, 8, 128, False),
     # reduced copies of the above for ncu captures (same kernels and tile shapes, inputs still beyond L2)
     "profile_gqa_fwd_b4_n2048_h64_kv8_d128": ("fwd", 4, 2048, 64, 8, 128, False),
     "profile_paged_decode_s14_ctx512_8192_h64_kv8_d128": ("decode", 14, 0, 64, 8, 128, False),
@@ -240,6 +244,8 @@ def main() -> int:
     kind, b, n, h, hkv, d, causal = WORKLOADS[args.workload]
     peaks, peaks_src = load_peaks()
 
+    if kind in ("rotary", "append"):
+        return run_stream_workload(args, rank, world, local_rank, kind, b, n, h, hkv, d, peaks, peaks_src)
     if args.impl == "reference":
         return run_reference_arm(args, rank, world, kind, b, n, h, hkv, d, causal)
 
@@ -414,6 +420,147 @@ def main() -> int:
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    return 0
+
+
+def run_stream_workload(args, rank, world, local_rank, kind, b, n, h, hkv, d, peaks, peaks_src) -> int:
+    """The HBM-bound byte movers next to the attention path: rotary pre-pass and paged KV-cache append. Single GPU
+    (under torchrun every rank runs its own copy; rank 0 reports its own figure times the number of ranks)."""
+    from oracle.attn_oracle import rotary_cos_sin
+
+    cores = os.cpu_count() or 1
+    if kind == "rotary":
+        gen = torch.Generator().manual_seed(rank)
+        x_h = torch.randn((b, h, n, d), generator=gen).to(torch.bfloat16)
+        cos_h, sin_h = rotary_cos_sin(n, d)
+        alg_bytes = 2 * x_h.numel() * 2
+    else:
+        gen = torch.Generator().manual_seed(rank)
+        s_n, t_n = b, n
+        k_h = torch.randn((s_n, t_n, hkv, d), generator=gen).to(torch.bfloat16)
+        v_h = torch.randn((s_n, t_n, hkv, d), generator=gen).to(torch.bfloat16)
+        pages_per_seq = t_n // 16
+        pool = s_n * pages_per_seq
+        bt_h = torch.randperm(pool, generator=gen).to(torch.int32).view(s_n, pages_per_seq)
+        sp_h = torch.zeros(s_n, dtype=torch.int32)
+        alg_bytes = 2 * 2 * k_h.numel() * 2
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        torch.set_num_threads(cores)
+        from oracle.attn_oracle import paged_kv_append_oracle, rotary_oracle
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < 10.0:
+            if kind == "rotary":
+                rotary_oracle(x_h[:2], cos_h, sin_h)
+                frac = 2 / b
+            else:
+                kp = torch.zeros((16 * 8, 16, hkv, d), dtype=torch.bfloat16)
+                paged_kv_append_oracle(k_h[:1, :128], v_h[:1, :128], kp, kp.clone(), torch.arange(8, dtype=torch.int32).view(1, 8),
+                                       sp_h[:1])
+                frac = 128 / (b * n)
+            reps += 1
+        dt = time.perf_counter() - t0
+        value = alg_bytes * frac * reps / dt / 1e9
+        line = {"impl": "reference", "metric": f"{kind} GB/s (bytes read + written)", "value": value, "unit": "GB/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / reps * 1e3,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": args.workload},
+                "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port",
+                                 "sample": f"{reps} passes over {frac:.4f} of the workload in {dt:.1f} s, oracle"},
+                "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+        print(json.dumps(line), flush=True)
+        return 0
+
+    import hipkittens_b200 as hk
+    from hipkittens_b200 import _native
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    stream = torch.cuda.current_stream(dev)
+    sampler = ClockSampler(local_rank)
+    if kind == "rotary":
+        x, cos, sin = x_h.to(dev), cos_h.to(dev), sin_h.to(dev)
+        out = torch.empty_like(x)
+        tk = hk.load_tk_kernel_rotary()
+
+        def step():
+            hk.rotary(x, cos, sin, out=out, stream=stream)
+
+        host_in, dev_in = [x_h.pin_memory()], [x]
+        host_out, dev_out = [torch.empty(x_h.shape, dtype=x_h.dtype).pin_memory()], [out]
+
+        def api_step():
+            tk.dispatch_rotary(x, out, sin, cos, stream=stream.cuda_stream)
+
+        path = "pinned host x -> H2D -> tk_kernel.dispatch_rotary -> D2H o"
+    else:
+        k_new, v_new, bt, sp = k_h.to(dev), v_h.to(dev), bt_h.to(dev), sp_h.to(dev)
+        kp = torch.zeros((pool, 16, hkv, d), dtype=torch.bfloat16, device=dev)
+        vp = torch.zeros_like(kp)
+
+        def step():
+            hk.paged_kv_append(k_new, v_new, kp, vp, bt, sp, stream=stream)
+
+        host_in, dev_in = [k_h.pin_memory(), v_h.pin_memory()], [k_new, v_new]
+        host_out, dev_out = [], []
+        api_step = step
+        path = "pinned host k_new, v_new -> H2D -> hipkittens_b200.paged_kv_append (the cache stays on the device)"
+    sampler.start()
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    l0 = hk.kernel_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.timed = True
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    sampler.timed = False
+    launches = hk.kernel_launch_count() - l0
+    ms = e0.elapsed_time(e1) / args.steps
+    if _native.device_status(local_rank) != 0:
+        raise SystemExit("device status non-zero after the timed region")
+    e2e = None
+    if not args.no_e2e:
+        def e2e_step():
+            for src, dst in zip(host_in, dev_in):
+                dst.copy_(src, non_blocking=True)
+            api_step()
+            for src, dst in zip(dev_out, host_out):
+                dst.copy_(src, non_blocking=True)
+        for _ in range(2):
+            e2e_step()
+        torch.cuda.synchronize()
+        steps = max(1, min(args.steps, 10))
+        e0.record(stream)
+        for _ in range(steps):
+            e2e_step()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        e2e = {"value": alg_bytes * world / (e0.elapsed_time(e1) / steps * 1e-3) / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host_in),
+               "d2h_bytes_per_step": sum(t.numel() * t.element_size() for t in host_out), "steps": steps, "path": path}
+    sampler.stop()
+    if rank == 0:
+        ach = alg_bytes / (ms * 1e-3) / 1e9
+        line = {"n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "data": "synthetic", "gpu_launches": int(launches),
+                "clocks": sampler.summary(), "peaks_source": peaks_src,
+                "metric": f"{kind} GB/s (bytes read + written)", "value": ach * world, "unit": "GB/s", "dtype": "bf16",
+                "config": {"workload": args.workload, "B_or_S": b, "N_or_T": n, "H": h, "H_KV": hkv, "D": d,
+                           "cache": "inputs_exceed_l2" if alg_bytes > 126e6 else "inputs_fit_l2"},
+                "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": ach / peaks["hbm_gbs"], "peak_kind": f"of {peaks_src} (copy)", "traffic": None,
+                             "bytes_per_launch": alg_bytes}}
+        if e2e:
+            line["e2e"] = e2e
+        print(json.dumps(line), flush=True)
     return 0
 
 

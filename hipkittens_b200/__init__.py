@@ -30,9 +30,11 @@ from ._native import (  # noqa: F401
     load_tk_kernel_bkwd,
     load_tk_kernel_bkwd_prep,
     load_tk_kernel_fwd,
+    load_tk_kernel_rotary,
     paged_decode,
     paged_decode_workspace_bytes,
     paged_kv_append,
+    rotary,
 )
 
 __all__ = [
@@ -50,7 +52,9 @@ __all__ = [
     "load_tk_kernel_bkwd",
     "load_tk_kernel_bkwd_prep",
     "load_tk_kernel_fwd",
+    "load_tk_kernel_rotary",
     "paged_decode",
     "paged_kv_append",
     "paged_decode_workspace_bytes",
+    "rotary",
 ]

@@ -11,6 +11,7 @@ into directories that mirror the reference's:
     kernels/attn/gqa_causal_backwards/tk_kernel_fwd  dispatch_fwd (blocking), causal default
     kernels/attn/gqa{,_causal}_backwards/tk_kernel_bkwd       dispatch_bwd_combined
     kernels/attn/gqa{,_causal}_backwards/tk_kernel_bkwd_prep  dispatch_prep, dispatch_dq_shuffle
+    kernels/rotary/tk_kernel                       dispatch_rotary
 
 Run as ``python -m hipkittens_b200._build``. nvcc cross-compiles without a GPU.
 """
@@ -118,6 +119,18 @@ def build_shims(force: bool = False):
             f"-DHK_BKWD_PREP={prep}", f"-DHK_DEFAULT_CAUSAL={causal}",
             "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
             bsrc, "-o", target,
+            "-L", LIB_DIR, "-lhk_attn", f"-Wl,-rpath,$ORIGIN/{rel}",
+        ])
+    rsrc = os.path.join(CSRC, "tk_kernel_rotary_shim.cpp")
+    target = shim_path("kernels/rotary", "tk_kernel")
+    out.append(target)
+    if force or not _newer(target, [rsrc, common, os.path.join(INCLUDE, "hk_attn.h"), LIB_PATH]):
+        os.makedirs(os.path.dirname(target), exist_ok=True)
+        rel = os.path.relpath(LIB_DIR, os.path.dirname(target))
+        _run([
+            "g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden",
+            "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
+            rsrc, "-o", target,
             "-L", LIB_DIR, "-lhk_attn", f"-Wl,-rpath,$ORIGIN/{rel}",
         ])
     return out

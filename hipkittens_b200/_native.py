@@ -27,6 +27,7 @@ EXPORTED_SYMBOLS = (
     "hk_attn_bwd_prep",
     "hk_attn_bwd",
     "hk_attn_dq_shuffle",
+    "hk_rotary",
     "hk_attn_paged_decode_workspace_bytes",
     "hk_attn_paged_decode",
     "hk_attn_paged_decode_static",
@@ -82,6 +83,8 @@ def capi() -> ctypes.CDLL:
     lib.hk_attn_bwd.restype = ci
     lib.hk_attn_dq_shuffle.argtypes = [vp, vp, ci, ci, ci, ci, ci, vp]
     lib.hk_attn_dq_shuffle.restype = ci
+    lib.hk_rotary.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]
+    lib.hk_rotary.restype = ci
     lib.hk_attn_paged_decode_workspace_bytes.argtypes = [ci, ci, ci, ci, ci]
     lib.hk_attn_paged_decode_workspace_bytes.restype = ctypes.c_size_t
     lib.hk_attn_paged_decode.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cf, vp,
@@ -285,6 +288,32 @@ def dq_shuffle(dq_bhnd: torch.Tensor, dq_bnhd: Optional[torch.Tensor] = None,
     return dq_bnhd
 
 
+def rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, out: Optional[torch.Tensor] = None,
+           stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """Rotary embedding of x [B,H,N,D] bf16 with cos, sin [N, R/2] bf16 (R <= D, the rest passes through): the
+    reference's ``tk_kernel.dispatch_rotary`` (kernels/rotary/kernel.cpp:44-98). `out` may be `x` itself."""
+    for name, t in (("x", x), ("cos", cos), ("sin", sin)):
+        if not isinstance(t, torch.Tensor):
+            raise RuntimeError("Expected a torch.Tensor")
+        if not t.is_contiguous():
+            raise RuntimeError("Tensor must be contiguous")
+        if t.device.type != "cuda":
+            raise RuntimeError("Tensor must be on CUDA device")
+        if t.dtype != torch.bfloat16:
+            raise RuntimeError(f"{name} must be torch.bfloat16")
+    if x.dim() != 4 or cos.dim() != 2 or cos.shape != sin.shape or cos.shape[0] != x.shape[2]:
+        raise RuntimeError("x must be [B,H,N,D] and cos/sin [N, R/2]")
+    b, h, n, d = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    if out.shape != x.shape or out.dtype != x.dtype or not out.is_contiguous():
+        raise RuntimeError("out must be a contiguous bf16 tensor of x's shape")
+    s = stream if stream is not None else torch.cuda.current_stream(x.device)
+    _check(capi().hk_rotary(x.data_ptr(), out.data_ptr(), sin.data_ptr(), cos.data_ptr(), b, h, n, d,
+                            2 * cos.shape[1], x.device.index, s.cuda_stream), "hk_rotary")
+    return out
+
+
 def paged_decode_workspace_bytes(s: int, h: int, d: int, max_pages: int, page_size: int = 16) -> int:
     return int(capi().hk_attn_paged_decode_workspace_bytes(s, h, d, max_pages, page_size))
 
@@ -411,3 +440,8 @@ def load_tk_kernel_bkwd_prep(causal: bool = True):
     ``dispatch_dq_shuffle(dQ_in, dQ)``. (Both builds are identical; `causal` only picks the directory.)"""
     return _load_ext("kernels/attn/gqa_causal_backwards" if causal else "kernels/attn/gqa_backwards",
                      "tk_kernel_bkwd_prep")
+
+
+def load_tk_kernel_rotary():
+    """The ``tk_kernel`` module of kernels/rotary: ``dispatch_rotary(x, o, sin, cos)``."""
+    return _load_ext("kernels/rotary", "tk_kernel")

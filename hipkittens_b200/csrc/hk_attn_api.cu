@@ -13,6 +13,7 @@
 #include "attn_fwd_sm100.cuh"
 #include "paged_decode_sm100.cuh"
 #include "paged_kv_append_sm100.cuh"
+#include "rotary_sm100.cuh"
 
 namespace {
 
@@ -396,6 +397,34 @@ int hk_attn_dq_shuffle(const void* dq_bhnd, void* dq_bnhd, int B, int N, int H, 
   if (blocks > 0x7fffffffll) return HK_EINVAL;
   hk::attn_dq_shuffle_kernel<<<unsigned(blocks), 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
       static_cast<const uint4*>(dq_bhnd), static_cast<uint4*>(dq_bnhd), B, N, H, vec);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  HK_CUDA(cudaGetLastError());
+  return HK_OK;
+}
+
+int hk_rotary(const void* x, void* o, const void* sin, const void* cos, int B, int H, int N, int D, int rotary_dim,
+              int device, void* cuda_stream) {
+  if (!x || !o || !sin || !cos) return HK_EINVAL;
+  if (B <= 0 || H <= 0 || N <= 0 || D <= 0) return HK_EINVAL;
+  if (rotary_dim <= 0) rotary_dim = D;
+  if (D % 8 != 0 || rotary_dim % 16 != 0 || rotary_dim > D) return HK_EUNSUPPORTED;
+  if (!aligned16(x) || !aligned16(o) || !aligned16(sin) || !aligned16(cos)) return HK_EINVAL;
+  DeviceState* st = nullptr;
+  int rc = use_device(device, &st);
+  if (rc != HK_OK) return rc;
+  hk::RotaryParams p;
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.o = static_cast<__nv_bfloat16*>(o);
+  p.cos = static_cast<const __nv_bfloat16*>(cos);
+  p.sin = static_cast<const __nv_bfloat16*>(sin);
+  p.rows = static_cast<long long>(B) * H * N;
+  p.N = N;
+  p.D = D;
+  p.R = rotary_dim;
+  const long long units = p.rows * (rotary_dim / 16 + (D - rotary_dim) / 8);
+  const long long blocks = (units + 255) / 256;
+  if (blocks > 0x7fffffffll) return HK_EINVAL;
+  hk::rotary_kernel<<<unsigned(blocks), 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   HK_CUDA(cudaGetLastError());
   return HK_OK;

@@ -108,6 +108,17 @@ int hk_attn_bwd(const void* q, const void* k, const void* v, const void* d_o, co
 int hk_attn_dq_shuffle(const void* dq_bhnd, void* dq_bnhd, int B, int N, int H, int D, int device,
                        void* cuda_stream);
 
+/* Rotary position embedding of q or k, the step before attention (training/llama/llama/models/mha.py:217-220).
+ * Replaces tk_kernel.dispatch_rotary(x, o, sin, cos) (kernels/rotary/kernel.cpp:44-98):
+ *   x, o : bf16 [B, H, N, D] contiguous        sin, cos : bf16 [N, rotary_dim / 2]
+ *   o[.., i] = x[.., i] cos[n,i] - x[.., i+R/2] sin[n,i],  o[.., i+R/2] = x[.., i+R/2] cos[n,i] + x[.., i] sin[n,i]
+ *   for i < R/2 (R = rotary_dim; <= 0 selects D), o[.., R:] = x[.., R:]. Products and sums are rounded to bf16 one
+ *   by one, as in the reference kernel, so results are bit-identical to the harness's bf16 PyTorch expression.
+ *   D a multiple of 8, rotary_dim a multiple of 16 and <= D (the reference is built for D = rotary_dim = 128);
+ *   x and o may be the same buffer. Asynchronous on `cuda_stream`. */
+int hk_rotary(const void* x, void* o, const void* sin, const void* cos, int B, int H, int N, int D, int rotary_dim,
+              int device, void* cuda_stream);
+
 /* Appends T new tokens per sequence to the paged KV cache read by hk_attn_paged_decode.
  * Paged counterpart of the reference's contiguous cache update, kv_cache[b, offset : offset + T] = kv
  * (training/llama/llama/models/mha.py:16-42, _update_kv_cache).

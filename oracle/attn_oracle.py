@@ -51,6 +51,8 @@ from hipkittens_b200.synthetic import make_paged_inputs, make_prefill_inputs  # 
 __all__ = [
     "attn_fwd_oracle",
     "attn_bwd_oracle",
+    "rotary_oracle",
+    "rotary_cos_sin",
     "paged_decode_oracle",
     "paged_kv_append_oracle",
     "make_prefill_inputs",
@@ -230,3 +232,29 @@ def paged_kv_append_oracle(k_new, v_new, k_pages, v_pages, block_table, start_po
             kp[pid, pos % page] = k_new[s, t]
             vp[pid, pos % page] = v_new[s, t]
     return kp, vp
+
+
+def rotary_cos_sin(n: int, rotary_dim: int, base: float = 10000.0):
+    """cos, sin [N, rotary_dim / 2] bf16 as the reference harness builds them, in bf16 throughout
+    (``kernels/rotary/test_python.py:36-45``: positions, inverse frequencies and their outer product are bf16)."""
+    dt = torch.bfloat16
+    t = torch.arange(n, dtype=dt)
+    inv_freq = 1.0 / (base ** (torch.arange(0, rotary_dim, 2, dtype=dt) / rotary_dim))
+    freqs = torch.outer(t, inv_freq).to(dtype=dt)
+    return torch.cos(freqs).to(dtype=dt), torch.sin(freqs).to(dtype=dt)
+
+
+def rotary_oracle(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotary embedding of x [B,H,N,D] bf16 with cos, sin [N, R/2] bf16, restating ``get_output`` of the reference
+    harness (``kernels/rotary/test_python.py:48-58``) on bf16 tensors: x * cos + rotate_half(x) * sin over the first R
+    dimensions, every product and the sum rounded to bf16 (what the kernel's __hmul2 / __hsub2 / __hadd2 do,
+    ``kernels/rotary/kernel.cpp:62-71``); the remaining dimensions pass through. Bit-exact target."""
+    assert x.dtype == torch.bfloat16 and cos.dtype == torch.bfloat16 and sin.dtype == torch.bfloat16
+    ro_dim = cos.shape[-1] * 2
+    assert ro_dim <= x.shape[-1] and cos.shape[0] == x.shape[2]
+    x_ro, x_end = x[..., :ro_dim], x[..., ro_dim:]
+    x1, x2 = x_ro.chunk(2, dim=-1)
+    rotated = torch.cat((-x2, x1), dim=-1)
+    c = torch.cat((cos, cos), dim=-1).view(1, 1, cos.shape[0], ro_dim)
+    s_ = torch.cat((sin, sin), dim=-1).view(1, 1, sin.shape[0], ro_dim)
+    return torch.cat([x_ro * c + rotated * s_, x_end], dim=-1)

@@ -101,5 +101,32 @@ def main() -> None:
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def rotary_main() -> None:
+    """Rotary fixture from the reference harness's own ``get_cos_sin`` / ``get_output``
+    (kernels/rotary/test_python.py:36-58). The harness imports its compiled module at the top, so the two functions
+    are taken out of its source with ``ast`` and executed on CPU tensors."""
+    import ast
+
+    from einops import repeat
+
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    src = open(os.path.join(ref_root, "kernels", "rotary", "test_python.py")).read()
+    tree = ast.parse(src)
+    wanted = [n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name in ("get_cos_sin", "get_output")]
+    assert len(wanted) == 2
+    b, h, n, d = 2, 3, 160, 128
+    ns = {"torch": torch, "repeat": repeat, "N": n, "D": d}
+    exec(compile(ast.Module(body=wanted, type_ignores=[]), "rotary_harness_functions", "exec"), ns)
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn((b, h, n, d), generator=gen).to(torch.bfloat16)
+    cos_in, sin_in, ro_dim = ns["get_cos_sin"](x, rotary_emb_dim=d)
+    out = ns["get_output"](x, cos_in, sin_in, ro_dim)
+    path = os.path.join(HERE, "rotary_b2_h3_n160_d128.npz")
+    np.savez_compressed(path, x=bf16_bits(x), cos=bf16_bits(cos_in), sin=bf16_bits(sin_in), o_ref=bf16_bits(out),
+                        shape=np.array([b, h, n, d, ro_dim], dtype=np.int64))
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
     main()
+    rotary_main()
