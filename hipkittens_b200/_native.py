@@ -240,7 +240,7 @@ def attn_bwd(
     """dQ, dK, dV of the attention forward (the reference's ``dispatch_bwd_combined``,
     kernels/attn/gqa_backwards/attn_bkwd_non_causal.cpp:37-49). q, d_o [B,N,H,D], k, v [B,N,H_KV,D] bf16;
     lse, delta [B,H,1,N] fp32. dQ comes back as [B,N,H,D], or [B,H,N,D] with ``dq_layout=HK_DQ_BHND``
-    (the reference's pre-shuffle layout). N must be a multiple of 128."""
+    (the reference's pre-shuffle layout). Any N >= 1."""
     for name, t in (("q", q), ("k", k), ("v", v), ("d_o", d_o)):
         _require_cuda_bf16(name, t, 4)
         if t.dtype != torch.bfloat16:

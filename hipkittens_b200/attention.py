@@ -8,8 +8,7 @@ input dtype and (q, k, v, O, L) are saved for the backward pass, which runs the 
 (hipkittens.py:64-119): ``dispatch_prep(O, dO, delta)``, ``dispatch_bwd_combined(q, k, v, dO, dQ_in, dK, dV,
 L, delta)`` and ``dispatch_dq_shuffle(dQ_in, dQ)``.
 
-Differences: the backward needs N to be a multiple of 128; dQ_in is not zero-filled (nothing is accumulated
-into it); and causality and the softmax scale are honoured here (they are baked into the reference's compiled module, and its modules
+Differences: dQ_in is not zero-filled (nothing is accumulated into it); and causality and the softmax scale are honoured here (they are baked into the reference's compiled module, and its modules
 ignore the ``causal`` and ``softmax_scale`` they are constructed with, hipkittens.py:147-162).
 """
 from __future__ import annotations

@@ -23,7 +23,8 @@
 // TMEM is laid out so that a score-shaped accumulator is free for the next tile as soon as the element-wise
 // warps hold it in registers (its bf16 successor goes elsewhere: see the column maps in the kernels).
 //
-// Sequence lengths must be a multiple of 128 (the reference's kernels need a multiple of 256).
+// Any sequence length works (the reference's kernels need a multiple of 256): TMA zero-fills the rows of a partial
+// last tile, their statistics are read as zero, and their gradient rows are not stored.
 #pragma once
 
 #include <cuda.h>
@@ -207,7 +208,7 @@ __device__ __forceinline__ void bwd_issue_ts(uint32_t d_tmem, uint32_t a_tmem, u
 
 // Accumulator rows (this thread's TMEM lane, D / kBwdParts columns from `taddr`) -> bf16 -> global, scaled.
 template <int D>
-__device__ __forceinline__ void bwd_store_part_row(uint32_t taddr, __nv_bfloat16* dst, float mul) {
+__device__ __forceinline__ void bwd_store_part_row(uint32_t taddr, __nv_bfloat16* dst, float mul, bool row_exists) {
   constexpr int kCols = D / kBwdParts;  // 64, 32 or 16
   constexpr int kChunk = kCols >= 32 ? 32 : 16;
 #pragma unroll
@@ -217,6 +218,7 @@ __device__ __forceinline__ void bwd_store_part_row(uint32_t taddr, __nv_bfloat16
     else ptx::tmem_ld16(taddr, o);
     ptx::tmem_wait_ld();
     uint4* out = reinterpret_cast<uint4*>(dst + cc * kChunk);
+    if (!row_exists) continue;  // the TMEM load above is warp-collective, the store is per row
 #pragma unroll
     for (int v4 = 0; v4 < kChunk / 8; ++v4) {
       uint4 val;
@@ -242,7 +244,7 @@ struct DkdvItem {
 template <bool CAUSAL>
 __device__ __forceinline__ DkdvItem decode_dkdv_item(const BwdParams& p, int idx) {
   DkdvItem w;
-  const int NB = p.N / kBlockN;
+  const int NB = (p.N + kBlockN - 1) / kBlockN;  // the last block may be partial
   const int units = p.B * p.H_KV;
   int unit;
   if (CAUSAL) {
@@ -315,7 +317,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       mbar_init(bars + RB_EMPTY + s, 1);
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(bars + STAT_FULL + s, 1);
+      mbar_init(bars + STAT_FULL + s, 1);   // one arrival by the statistics loader warp
       mbar_init(bars + STAT_EMPTY + s, kBwdCW);
     }
     fence_mbar_init();
@@ -330,8 +332,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const uint32_t tmem = *tmem_slot;
   volatile uint32_t* abortp = abort_word;
   const int G = p.H / p.H_KV;
-  // TMEM columns: X = S^T [0,128); Y = dP^T [128,256), later overwritten by the two bf16 operands: each half-row
-  // thread group keeps to the 64 columns it read, P^T in their first 32, dS^T in their last 32;
+  // TMEM columns: X = S^T [0,128); Y = dP^T [128,256), later overwritten by the two bf16 operands: each thread
+  // keeps to the kBwdPC columns it read, P^T in their first half, dS^T in their second half;
   // dK [256,256+D); dV [256+D,256+2D).
   constexpr uint32_t cST = 0, cY = 128, cDK = 256, cDV = 256 + D;
 
@@ -459,8 +461,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       ++acc_cnt;
       tc_fence_after();
       const size_t off = ((static_cast<size_t>(w.b) * p.N + w.j * kBlockN + row) * p.H_KV + w.kvh) * D + part * (D / kBwdParts);
-      bwd_store_part_row<D>(tmem + lane_addr + cDK + part * (D / kBwdParts), p.dk + off, p.scale);
-      bwd_store_part_row<D>(tmem + lane_addr + cDV + part * (D / kBwdParts), p.dv + off, 1.0f);
+      const bool row_exists = w.j * kBlockN + row < p.N;  // keys of a partial last block beyond N are computed, not stored
+      bwd_store_part_row<D>(tmem + lane_addr + cDK + part * (D / kBwdParts), p.dk + off, p.scale, row_exists);
+      bwd_store_part_row<D>(tmem + lane_addr + cDV + part * (D / kBwdParts), p.dv + off, 1.0f, row_exists);
       tc_fence_before();  // orders these reads before the next item's first dV product (published through P_FULL)
     }
   } else {
@@ -504,13 +507,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             qa = 0;
             qa_par ^= 1;
           }
-          const int ss = it & 1;
-          ok = mbar_wait(bars + STAT_EMPTY + ss, ((it >> 1) & 1) ^ 1, abortp, kWaitLimitCycles);
-          if (!ok) break;
-          mbar_expect_tx(bars + STAT_FULL + ss, 2 * kBlockM * 4);
-          const size_t soff = (static_cast<size_t>(w.b) * p.H + head) * p.N + static_cast<size_t>(i) * kBlockM;
-          bulk_load_1d(sStat + ss * 256, p.lse + soff, kBlockM * 4, bars + STAT_FULL + ss);
-          bulk_load_1d(sStat + ss * 256 + 128, p.delta + soff, kBlockM * 4, bars + STAT_FULL + ss);
           ok = mbar_wait(bars + RB_EMPTY + rb, rb_par ^ 1, abortp, kWaitLimitCycles);
           if (!ok) break;
           mbar_expect_tx(bars + RB_FULL + rb, kTile);
@@ -637,6 +633,51 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         umma_commit(bars + ACC_FULL);
         umma_commit(bars + KV_EMPTY);
       }
+    } else if (warp == kBwdCW + 3) {
+      // ---------------- statistics loader: L and delta of each query tile -> shared memory (indexed by column in
+      // this kernel), zeros beyond N. Plain guarded loads, so any N and any alignment of the two arrays work; with
+      // zeros there a padded query column gives p = 1, dP = 0, dS = 0 and meets zero-filled rows of dO and Q in the
+      // products, so nothing has to be masked.
+      // The values of a tile are fetched into registers one iteration before the stage that takes them is free, so the
+      // global-memory latency never sits between STAT_EMPTY and STAT_FULL.
+      uint32_t it = 0;
+      bool ok = true;
+      float lv[kBlockM / 32], dv_[kBlockM / 32];
+      auto fetch = [&](const DkdvItem& w, int n) {
+        const int head = w.kvh * G + n / w.cnt_i;
+        const int i = (CAUSAL ? w.j : 0) + n % w.cnt_i;
+        const size_t base = (static_cast<size_t>(w.b) * p.H + head) * p.N;
+#pragma unroll
+        for (int t = 0; t < kBlockM / 32; ++t) {
+          const int pos = i * kBlockM + t * 32 + lane;
+          const bool in = pos < p.N;
+          lv[t] = in ? __ldg(p.lse + base + pos) : 0.f;
+          dv_[t] = in ? __ldg(p.delta + base + pos) : 0.f;
+        }
+      };
+      for (int round = 0; ok; ++round) {
+        const int idx = item_for_round(round, blockIdx.x, gridDim.x);
+        if (idx >= p.n_items) {
+          if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
+          continue;
+        }
+        const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
+        fetch(w, 0);
+        for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
+          const int ss = it & 1;
+          ok = mbar_wait(bars + STAT_EMPTY + ss, ((it >> 1) & 1) ^ 1, abortp, kWaitLimitCycles);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+#pragma unroll
+          for (int t = 0; t < kBlockM / 32; ++t) {
+            sStat[ss * 256 + t * 32 + lane] = lv[t];
+            sStat[ss * 256 + 128 + t * 32 + lane] = dv_[t];
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bars + STAT_FULL + ss);
+          if (n + 1 < w.n_iter) fetch(w, n + 1);
+        }
+      }
     }
   }
 
@@ -668,7 +709,7 @@ struct DqItem {
 template <bool CAUSAL>
 __device__ __forceinline__ DqItem decode_dq_item(const BwdParams& p, int idx) {
   DqItem w;
-  const int NB = p.N / kBlockM;
+  const int NB = (p.N + kBlockM - 1) / kBlockM;  // the last tile may be partial
   const int G = p.H / p.H_KV;
   const int units = p.B * p.H_KV;
   int unit, g;
@@ -785,8 +826,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       }
       const DqItem w = decode_dq_item<CAUSAL>(p, idx);
       const size_t srow = (static_cast<size_t>(w.b) * p.H + w.h) * p.N + static_cast<size_t>(w.i) * kBlockM + row;
-      const float nl = p.lse[srow] * -1.4426950408889634f;
-      const float dl = p.delta[srow];
+      const bool row_exists = w.i * kBlockM + row < p.N;  // rows of a partial last tile beyond N: zero statistics
+      const float nl = row_exists ? p.lse[srow] * -1.4426950408889634f : 0.f;
+      const float dl = row_exists ? p.delta[srow] : 0.f;
       for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
         const bool diag = CAUSAL && (n == w.n_iter - 1);
         HK_STAMP(0, 0);
@@ -861,7 +903,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       tc_fence_after();
       __nv_bfloat16* dst = p.dq + w.b * p.dq_stride_b + (static_cast<long long>(w.i) * kBlockM + row) * p.dq_stride_n +
                            w.h * p.dq_stride_h + part * (D / kBwdParts);
-      bwd_store_part_row<D>(tmem + lane_addr + cDQ + part * (D / kBwdParts), dst, p.scale);
+      bwd_store_part_row<D>(tmem + lane_addr + cDQ + part * (D / kBwdParts), dst, p.scale, row_exists);
       tc_fence_before();  // orders these reads before the next item's first dQ product (published through DS_FULL)
     }
   } else {

@@ -197,7 +197,7 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
 template <int D, bool CAUSAL>
 int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                hk::BwdParams p, int B, int N, int H, int H_KV, int sm_count, cudaStream_t stream) {
-  const int nb = N / hk::kBlockM;
+  const int nb = (N + hk::kBlockM - 1) / hk::kBlockM;
   p.n_items = B * H_KV * nb;
   int grid = p.n_items < sm_count ? p.n_items : sm_count;
 #ifdef HK_TRACE
@@ -332,10 +332,9 @@ int hk_attn_bwd(const void* q, const void* k, const void* v, const void* d_o, co
   if (B <= 0 || N <= 0 || H <= 0 || H_KV <= 0) return HK_EINVAL;
   if (D != 64 && D != 128) return HK_EUNSUPPORTED;
   if (H % H_KV != 0) return HK_EINVAL;
-  if (N % hk::kBlockM != 0) return HK_EUNSUPPORTED;
   if (dq_layout != HK_DQ_BNHD && dq_layout != HK_DQ_BHND) return HK_EINVAL;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(d_o) || !aligned16(dq) || !aligned16(dk) ||
-      !aligned16(dv) || !aligned16(lse) || !aligned16(delta))
+      !aligned16(dv) || (reinterpret_cast<uintptr_t>(lse) & 3) || (reinterpret_cast<uintptr_t>(delta) & 3))
     return HK_EINVAL;
   DeviceState* st = nullptr;
   int rc = use_device(device, &st);

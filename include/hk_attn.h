@@ -96,8 +96,8 @@ int hk_attn_bwd_prep(const void* o, const void* d_o, float* delta, int B, int N,
  * written once, in the layout `dq_layout` names, and does not need to be zero-filled.
  *   q, d_o, dq : bf16 [B,N,H,D] (dq as dq_layout says)    k, v, dk, dv : bf16 [B,N,H_KV,D]
  *   lse, delta : fp32 [B,H,1,N]
- *   D in {64, 128}; N a multiple of 128 (HK_EUNSUPPORTED otherwise; the reference needs a multiple of 256);
- *   all pointers 16-byte aligned; softmax_scale <= 0 selects 1/sqrt(D).
+ *   D in {64, 128}; any N >= 1 (the reference needs a multiple of 256); tensor pointers 16-byte aligned, lse and
+ *   delta 4-byte aligned; softmax_scale <= 0 selects 1/sqrt(D).
  * Results are bit-identical from run to run (no atomics). */
 int hk_attn_bwd(const void* q, const void* k, const void* v, const void* d_o, const float* lse, const float* delta,
                 void* dq, void* dk, void* dv, int B, int N, int H, int H_KV, int D, int causal, float softmax_scale,

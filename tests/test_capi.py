@@ -111,11 +111,11 @@ def test_bwd_rejects_bad_arguments_before_cuda(native_built):
     assert bwd(q=None) == _native.HK_EINVAL
     assert bwd(lse=None) == _native.HK_EINVAL
     assert bwd(dq=72) == _native.HK_EINVAL      # not 16-byte aligned
-    assert bwd(lse=68) == _native.HK_EINVAL     # L feeds 16-byte bulk copies
+    assert bwd(lse=66) == _native.HK_EINVAL     # fp32 arrays need 4-byte alignment
     assert bwd(H=3, HKV=2) == _native.HK_EINVAL
     assert bwd(layout=2) == _native.HK_EINVAL
     assert bwd(D=96) == _native.HK_EUNSUPPORTED
-    assert bwd(N=200) == _native.HK_EUNSUPPORTED  # the backward needs whole 128-row tiles
+    assert bwd(N=0) == _native.HK_EINVAL
     assert lib.hk_attn_bwd_prep(None, 64, 64, 1, 128, 2, 128, 0, None) == _native.HK_EINVAL
     assert lib.hk_attn_bwd_prep(64, 64, 64, 1, 128, 2, 96, 0, None) == _native.HK_EUNSUPPORTED
     assert lib.hk_attn_bwd_prep(64, 64, 64, 1, 0, 2, 128, 0, None) == _native.HK_EINVAL
