@@ -64,6 +64,9 @@ NCU_TRAFFIC_BYTES = {
     "mha_fwd_b16_n4096_h16_d64": 0.404e9 + 0.118e9,
     # backward, 4 x the B=4 capture of the two main kernels (profiles/attn_bwd_kernels_gqa_bwd_d128.md) + the prep kernel
     "gqa_bwd_b16_n2048_h64_kv8_d128": 4 * (358.2e6 + 413.1e6) + 1.082e9,
+    # rate x duration of the section capture (profiles/rotary_kernel_and_paged_kv_append_kernel.md)
+    "rotary_b16_h16_n2048_d128": 216.6e6,
+    "paged_kv_append_s16_t2048_kv8_d128": 222.6e6,
     # 14-sequence capture (280.26 MB for sum ctx 66 608) scaled by sum ctx to 275 479; split + combine
     "paged_decode_s64_ctx512_8192_h64_kv8_d128": (273.46e6 + 4.73e6 + 2.47e6) * 275479 / 66608,
 }
@@ -556,8 +559,8 @@ def run_stream_workload(args, rank, world, local_rank, kind, b, n, h, hkv, d, pe
                 "config": {"workload": args.workload, "B_or_S": b, "N_or_T": n, "H": h, "H_KV": hkv, "D": d,
                            "cache": "inputs_exceed_l2" if alg_bytes > 126e6 else "inputs_fit_l2"},
                 "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                             "frac": ach / peaks["hbm_gbs"], "peak_kind": f"of {peaks_src} (copy)", "traffic": None,
-                             "bytes_per_launch": alg_bytes}}
+                             "frac": ach / peaks["hbm_gbs"], "peak_kind": f"of {peaks_src} (copy)",
+                             "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "bytes_per_launch": alg_bytes}}
         if e2e:
             line["e2e"] = e2e
         print(json.dumps(line), flush=True)
