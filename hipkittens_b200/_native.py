@@ -26,6 +26,7 @@ EXPORTED_SYMBOLS = (
     "hk_attn_fwd_varlen",
     "hk_attn_bwd_prep",
     "hk_attn_bwd",
+    "hk_attn_bwd_varlen",
     "hk_attn_dq_shuffle",
     "hk_rotary",
     "hk_attn_paged_decode_workspace_bytes",
@@ -81,6 +82,8 @@ def capi() -> ctypes.CDLL:
     lib.hk_attn_bwd_prep.restype = ci
     lib.hk_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, cf, ci, ci, vp]
     lib.hk_attn_bwd.restype = ci
+    lib.hk_attn_bwd_varlen.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, ci, cf, ci, ci, vp]
+    lib.hk_attn_bwd_varlen.restype = ci
     lib.hk_attn_dq_shuffle.argtypes = [vp, vp, ci, ci, ci, ci, ci, vp]
     lib.hk_attn_dq_shuffle.restype = ci
     lib.hk_rotary.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]
@@ -236,11 +239,13 @@ def attn_bwd(
     dv: Optional[torch.Tensor] = None,
     dq_layout: int = HK_DQ_BNHD,
     stream: Optional[torch.cuda.Stream] = None,
+    kv_lens: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """dQ, dK, dV of the attention forward (the reference's ``dispatch_bwd_combined``,
     kernels/attn/gqa_backwards/attn_bkwd_non_causal.cpp:37-49). q, d_o [B,N,H,D], k, v [B,N,H_KV,D] bf16;
     lse, delta [B,H,1,N] fp32. dQ comes back as [B,N,H,D], or [B,H,N,D] with ``dq_layout=HK_DQ_BHND``
-    (the reference's pre-shuffle layout). Any N >= 1."""
+    (the reference's pre-shuffle layout). Any N >= 1. `kv_lens` (int32 [B], non-causal only) is the padding of
+    ``attn_fwd(..., kv_lens=)``: dK and dV rows of padded keys come back as zeros."""
     for name, t in (("q", q), ("k", k), ("v", v), ("d_o", d_o)):
         _require_cuda_bf16(name, t, 4)
         if t.dtype != torch.bfloat16:
@@ -263,10 +268,13 @@ def attn_bwd(
         if tuple(t.shape) != tuple(shp) or t.dtype != torch.bfloat16 or not t.is_contiguous():
             raise RuntimeError(f"{name} must be a contiguous bf16 tensor of shape {tuple(shp)}")
     s = stream if stream is not None else torch.cuda.current_stream(q.device)
-    rc = capi().hk_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), d_o.data_ptr(), lse.data_ptr(),
-                            delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), b, n, h, hkv, d,
-                            int(bool(causal)), float(softmax_scale or 0.0), int(dq_layout), q.device.index,
-                            s.cuda_stream)
+    if kv_lens is not None and (kv_lens.dtype != torch.int32 or kv_lens.shape != (b,) or kv_lens.device != q.device):
+        raise RuntimeError("kv_lens must be an int32 tensor [B] on q's device")
+    rc = capi().hk_attn_bwd_varlen(q.data_ptr(), k.data_ptr(), v.data_ptr(), d_o.data_ptr(), lse.data_ptr(),
+                                   delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), b, n, h, hkv, d,
+                                   kv_lens.data_ptr() if kv_lens is not None else None,
+                                   int(bool(causal)), float(softmax_scale or 0.0), int(dq_layout), q.device.index,
+                                   s.cuda_stream)
     _check(rc, "hk_attn_bwd")
     return dq, dk, dv
 

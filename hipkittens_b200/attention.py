@@ -8,7 +8,9 @@ input dtype and (q, k, v, O, L) are saved for the backward pass, which runs the 
 (hipkittens.py:64-119): ``dispatch_prep(O, dO, delta)``, ``dispatch_bwd_combined(q, k, v, dO, dQ_in, dK, dV,
 L, delta)`` and ``dispatch_dq_shuffle(dQ_in, dQ)``.
 
-Differences: dQ_in is not zero-filled (nothing is accumulated into it); and causality and the softmax scale are honoured here (they are baked into the reference's compiled module, and its modules
+Differences: dQ_in is not zero-filled (nothing is accumulated into it); a right-padded ``key_padding_mask``
+(True = keep, as in ``base.py:88-103``) is honoured through per-batch key lengths, where the reference's modules
+accept the argument and ignore it (hipkittens.py:147-162); and causality and the softmax scale are honoured here (they are baked into the reference's compiled module, and its modules
 ignore the ``causal`` and ``softmax_scale`` they are constructed with, hipkittens.py:147-162).
 """
 from __future__ import annotations
@@ -17,7 +19,15 @@ import torch
 import torch.nn as nn
 from torch.autograd import Function
 
-from ._native import attn_fwd, device_status, load_tk_kernel_bkwd, load_tk_kernel_bkwd_prep, load_tk_kernel_fwd
+from ._native import (
+    attn_bwd,
+    attn_bwd_prep,
+    attn_fwd,
+    device_status,
+    load_tk_kernel_bkwd,
+    load_tk_kernel_bkwd_prep,
+    load_tk_kernel_fwd,
+)
 
 _fwd_modules = {}
 _bkwd_modules = {}
@@ -44,7 +54,7 @@ def _tma_viewable(t: torch.Tensor) -> bool:
 class HipAttnFunction(Function):
     @staticmethod
     def forward(ctx, q_bnhd: torch.Tensor, k_bnhd: torch.Tensor, v_bnhd: torch.Tensor, causal: bool = True,
-                softmax_scale=None):
+                softmax_scale=None, kv_lens=None):
         B, N, H, D = q_bnhd.shape
         HKV = k_bnhd.shape[2]
         dev = q_bnhd.device
@@ -57,12 +67,16 @@ class HipAttnFunction(Function):
 
         O = torch.empty((B, N, H, D), dtype=torch.bfloat16, device=dev)
         L = torch.empty((B, H, 1, N), dtype=torch.float32, device=dev)
-        if all(_tma_viewable(t) for t in (q_bnhd, k_bnhd, v_bnhd)) and not all(
-                t.is_contiguous() for t in (q_bnhd, k_bnhd, v_bnhd)):
+        if kv_lens is not None or (all(_tma_viewable(t) for t in (q_bnhd, k_bnhd, v_bnhd)) and not all(
+                t.is_contiguous() for t in (q_bnhd, k_bnhd, v_bnhd))):
             # bf16 views of a packed projection (what qkv.unbind(2) gives): the kernel reads them through
             # strided TMA descriptors, so the reference's three .contiguous() copies (hipkittens.py:37-39) go
-            q, k, v = q_bnhd, k_bnhd, v_bnhd
-            attn_fwd(q, k, v, causal=bool(causal), softmax_scale=softmax_scale, out=O, lse=L)
+            # (key lengths go the same way: the reference's dispatch_fwd has no argument for them)
+            if all(_tma_viewable(t) for t in (q_bnhd, k_bnhd, v_bnhd)):
+                q, k, v = q_bnhd, k_bnhd, v_bnhd
+            else:
+                q, k, v = (t.to(torch.bfloat16).contiguous() for t in (q_bnhd, k_bnhd, v_bnhd))
+            attn_fwd(q, k, v, causal=bool(causal), softmax_scale=softmax_scale, out=O, lse=L, kv_lens=kv_lens)
             status = device_status(dev.index)  # blocks on the device like dispatch_fwd does
             if status != 0:
                 raise RuntimeError(f"attention forward failed on the device (status {status})")
@@ -75,6 +89,7 @@ class HipAttnFunction(Function):
         ctx.save_for_backward(q, k, v, O, L)
         ctx.causal = bool(causal)
         ctx.softmax_scale = softmax_scale
+        ctx.kv_lens = kv_lens
         return O.to(out_dtype)
 
     @staticmethod
@@ -96,13 +111,36 @@ class HipAttnFunction(Function):
         dV = torch.empty((B, N, HKV, D), dtype=torch.bfloat16, device=dev)
         delta = torch.empty((B, H, 1, N), dtype=torch.float32, device=dev)
 
+        if ctx.kv_lens is not None:
+            # padded batch: the C ABI's varlen entry (no counterpart among the reference's three calls); dQ is written
+            # in its final layout, so no shuffle pass
+            attn_bwd_prep(O, dO, delta)
+            attn_bwd(q, k, v, dO, L, delta, causal=False, softmax_scale=ctx.softmax_scale, dq=dQ, dk=dK, dv=dV,
+                     kv_lens=ctx.kv_lens)
+            status = device_status(dev.index)
+            if status != 0:
+                raise RuntimeError(f"attention backward failed on the device (status {status})")
+            return dQ.to(dO_bnhd.dtype), dK.to(dO_bnhd.dtype), dV.to(dO_bnhd.dtype), None, None, None
+
         tk_kernel_bkwd, tk_kernel_bkwd_prep = _tk_kernel_bkwd(ctx.causal)
         tk_kernel_bkwd_prep.dispatch_prep(O, dO, delta)
         tk_kernel_bkwd.dispatch_bwd_combined(q, k, v, dO, dQ_in, dK, dV, L, delta, causal=ctx.causal,
                                              softmax_scale=ctx.softmax_scale)
         tk_kernel_bkwd_prep.dispatch_dq_shuffle(dQ_in, dQ)
 
-        return dQ.to(dO_bnhd.dtype), dK.to(dO_bnhd.dtype), dV.to(dO_bnhd.dtype), None, None
+        return dQ.to(dO_bnhd.dtype), dK.to(dO_bnhd.dtype), dV.to(dO_bnhd.dtype), None, None, None
+
+
+def _lens_from_key_padding_mask(mask: torch.Tensor, seqlen: int):
+    """(B, S) bool, True = keep (base.py:88-89) -> int32 key lengths, for masks that keep a prefix of each row
+    (right padding, what padded batches have). Anything else cannot be expressed as lengths and is refused."""
+    if mask.dim() != 2 or mask.shape[1] != seqlen or mask.dtype != torch.bool:
+        raise ValueError("key_padding_mask must be a bool tensor (batch, seqlen), True = keep")
+    lens = mask.sum(dim=1).to(torch.int32)
+    prefix = torch.arange(seqlen, device=mask.device).unsqueeze(0) < lens.unsqueeze(1)
+    if not bool((mask == prefix).all()) or bool((lens < 1).any()):
+        raise ValueError("only right-padded key_padding_mask (a kept prefix of at least one key per row) is supported")
+    return lens.contiguous()
 
 
 class HipSelfAttention(nn.Module):
@@ -120,11 +158,14 @@ class HipSelfAttention(nn.Module):
     def forward(self, qkv, causal=None, key_padding_mask=None):
         assert qkv.dtype in [torch.float16, torch.bfloat16]
         assert qkv.is_cuda
-        if key_padding_mask is not None:
-            raise ValueError("key_padding_mask is not supported by the kernels")
         causal = self.causal if causal is None else causal
+        kv_lens = None
+        if key_padding_mask is not None:
+            if causal:
+                raise ValueError("key_padding_mask together with causal is not supported by the kernels")
+            kv_lens = _lens_from_key_padding_mask(key_padding_mask, qkv.shape[1])
         q, k, v = qkv.unbind(dim=2)
-        out_bnhd = HipAttnFunction.apply(q, k, v, causal, self.softmax_scale)
+        out_bnhd = HipAttnFunction.apply(q, k, v, causal, self.softmax_scale, kv_lens)
         return out_bnhd.to(q.dtype).contiguous()
 
 
@@ -139,11 +180,14 @@ class HipCrossAttention(nn.Module):
         self.deterministic = deterministic
 
     def forward(self, q, kv, causal=None, key_padding_mask=None):
-        if key_padding_mask is not None:
-            raise ValueError("key_padding_mask is not supported by the kernels")
         batch_size = q.shape[0]
         causal = self.causal if causal is None else causal
         assert kv.shape[0] == batch_size and kv.shape[4] == q.shape[3]
+        kv_lens = None
+        if key_padding_mask is not None:
+            if causal:
+                raise ValueError("key_padding_mask together with causal is not supported by the kernels")
+            kv_lens = _lens_from_key_padding_mask(key_padding_mask, kv.shape[1])
         k, v = kv.unbind(dim=2)
-        out_bnhd = HipAttnFunction.apply(q, k, v, causal, self.softmax_scale)
+        out_bnhd = HipAttnFunction.apply(q, k, v, causal, self.softmax_scale, kv_lens)
         return out_bnhd.to(q.dtype).contiguous()

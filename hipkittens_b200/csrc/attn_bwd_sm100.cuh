@@ -96,6 +96,7 @@ struct BwdParams {
   int group_units;      // causal order: (batch, kv-head) units swept together (L2 residency)
   float scale;
   float scale_log2;
+  const int* kv_lens;   // optional device [B]: batch b attends to keys [0, kv_lens[b]) only (non-causal); null = N
   int* status;
 #ifdef HK_TRACE
   long long* trace;     // [4 roles][4096] clock stamps of CTA 0 (debug builds only)
@@ -234,8 +235,9 @@ __device__ __forceinline__ void bwd_store_part_row(uint32_t taddr, __nv_bfloat16
 // ------------------------------------------------------------------------------------ dK, dV
 struct DkdvItem {
   int b, kvh, j;   // batch, kv head, key block
+  int kv_len;      // keys this batch element attends to
   int cnt_i;       // query tiles per head this key block meets
-  int n_iter;      // heads of the group x query tiles
+  int n_iter;      // heads of the group x query tiles; 0 for a key block that lies wholly beyond kv_len
 };
 
 // Work order: one (batch, kv head) unit's key blocks are adjacent so that the CTAs running at the same
@@ -260,8 +262,9 @@ __device__ __forceinline__ DkdvItem decode_dkdv_item(const BwdParams& p, int idx
   }
   w.b = unit / p.H_KV;
   w.kvh = unit % p.H_KV;
+  w.kv_len = (!CAUSAL && p.kv_lens) ? min(max(p.kv_lens[w.b], 1), p.N) : p.N;
   w.cnt_i = CAUSAL ? NB - w.j : NB;
-  w.n_iter = (p.H / p.H_KV) * w.cnt_i;
+  w.n_iter = (w.j * kBlockN >= w.kv_len) ? 0 : (p.H / p.H_KV) * w.cnt_i;
   return w;
 }
 
@@ -360,6 +363,20 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         continue;
       }
       const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
+      const bool pad_row = w.j * kBlockN + row >= w.kv_len;  // this key is padding (or lies beyond N)
+      if (w.n_iter == 0) {
+        // the whole key block is padding: its gradients are zero and no product was issued for it
+        if (w.j * kBlockN + row < p.N) {
+          const size_t off =
+              ((static_cast<size_t>(w.b) * p.N + w.j * kBlockN + row) * p.H_KV + w.kvh) * D + part * (D / kBwdParts);
+#pragma unroll
+          for (int v = 0; v < D / kBwdParts / 8; ++v) {
+            reinterpret_cast<uint4*>(p.dk + off)[v] = make_uint4(0, 0, 0, 0);
+            reinterpret_cast<uint4*>(p.dv + off)[v] = make_uint4(0, 0, 0, 0);
+          }
+        }
+        continue;
+      }
       for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
         HK_STAMP(0, 0);
         const bool diag = CAUSAL && (n % w.cnt_i == 0);  // the query tile at the key block's own position
@@ -401,6 +418,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             // the query tile at the key block's own position: queries earlier than the key see nothing
 #pragma unroll
             for (int col = 0; col < kBwdPC; ++col) su[col] = (part * kBwdPC + col) < row ? 0u : su[col];
+          }
+          if (pad_row) {
+            // a padded key is seen by nobody: P^T and dS^T rows are zero, so are its dK and dV rows
+#pragma unroll
+            for (int col = 0; col < kBwdPC; ++col) su[col] = 0u;
           }
         }
         HK_STAMP(0, 2);
@@ -485,6 +507,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           continue;
         }
         const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
+        if (w.n_iter == 0) continue;  // key block wholly beyond this batch element's length: nothing to do
         ok = mbar_wait(bars + KV_EMPTY, (item_cnt & 1) ^ 1, abortp, kWaitLimitCycles);
         if (!ok) break;
         ++item_cnt;
@@ -543,6 +566,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           continue;
         }
         const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
+        if (w.n_iter == 0) continue;  // key block wholly beyond this batch element's length: nothing to do
         ok = mbar_wait(bars + KV_FULL, item_cnt & 1, abortp, kWaitLimitCycles);
         if (!ok) break;
         ++item_cnt;
@@ -586,6 +610,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           continue;
         }
         const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
+        if (w.n_iter == 0) continue;  // key block wholly beyond this batch element's length: nothing to do
         ok = mbar_wait(bars + KV_FULL, item_cnt & 1, abortp, kWaitLimitCycles) &&
              mbar_wait(bars + RB_FULL + rb, rb_par, abortp, kWaitLimitCycles);
         if (!ok) break;
@@ -662,6 +687,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           continue;
         }
         const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
+        if (w.n_iter == 0) continue;  // key block wholly beyond this batch element's length: nothing to do
         fetch(w, 0);
         for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
           const int ss = it & 1;
@@ -701,6 +727,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 // ------------------------------------------------------------------------------------ dQ
 struct DqItem {
   int b, h, kvh, i;  // batch, query head, its kv head, query tile
+  int kv_len;        // keys this batch element attends to
   int n_iter;        // key tiles this query tile meets
 };
 
@@ -732,7 +759,8 @@ __device__ __forceinline__ DqItem decode_dq_item(const BwdParams& p, int idx) {
   w.b = unit / p.H_KV;
   w.kvh = unit % p.H_KV;
   w.h = w.kvh * G + g;
-  w.n_iter = CAUSAL ? w.i + 1 : NB;
+  w.kv_len = (!CAUSAL && p.kv_lens) ? min(max(p.kv_lens[w.b], 1), p.N) : p.N;
+  w.n_iter = CAUSAL ? w.i + 1 : (w.kv_len + kBlockN - 1) / kBlockN;
   return w;
 }
 
@@ -856,6 +884,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             // diagonal tile: keys later than the query see nothing
 #pragma unroll
             for (int col = 0; col < kBwdPC; ++col) su[col] = (part * kBwdPC + col) > row ? 0u : su[col];
+          }
+          if (!CAUSAL && n == w.n_iter - 1 && (w.kv_len & (kBlockN - 1)) != 0) {
+            // partial last tile: keys at or beyond the length are padding
+            const int rem = w.kv_len - n * kBlockN;
+#pragma unroll
+            for (int col = 0; col < kBwdPC; ++col) su[col] = (part * kBwdPC + col) >= rem ? 0u : su[col];
           }
         }
         HK_STAMP(0, 2);

@@ -328,6 +328,15 @@ int hk_attn_bwd_prep(const void* o, const void* d_o, float* delta, int B, int N,
 int hk_attn_bwd(const void* q, const void* k, const void* v, const void* d_o, const float* lse, const float* delta,
                 void* dq, void* dk, void* dv, int B, int N, int H, int H_KV, int D, int causal, float softmax_scale,
                 int dq_layout, int device, void* cuda_stream) {
+  return hk_attn_bwd_varlen(q, k, v, d_o, lse, delta, dq, dk, dv, B, N, H, H_KV, D, nullptr, causal, softmax_scale,
+                            dq_layout, device, cuda_stream);
+}
+
+int hk_attn_bwd_varlen(const void* q, const void* k, const void* v, const void* d_o, const float* lse,
+                       const float* delta, void* dq, void* dk, void* dv, int B, int N, int H, int H_KV, int D,
+                       const int32_t* kv_lens, int causal, float softmax_scale, int dq_layout, int device,
+                       void* cuda_stream) {
+  if (kv_lens && causal) return HK_EUNSUPPORTED;
   if (!q || !k || !v || !d_o || !lse || !delta || !dq || !dk || !dv) return HK_EINVAL;
   if (B <= 0 || N <= 0 || H <= 0 || H_KV <= 0) return HK_EINVAL;
   if (D != 64 && D != 128) return HK_EUNSUPPORTED;
@@ -371,6 +380,7 @@ int hk_attn_bwd(const void* q, const void* k, const void* v, const void* d_o, co
   }
   p.scale = softmax_scale > 0.f ? softmax_scale : 1.0f / std::sqrt(float(D));
   p.scale_log2 = p.scale * 1.4426950408889634f;
+  p.kv_lens = kv_lens;
   p.status = st->status;
 #ifdef HK_TRACE
   p.trace = g_trace_buf;

@@ -103,6 +103,15 @@ int hk_attn_bwd(const void* q, const void* k, const void* v, const void* d_o, co
                 void* dq, void* dk, void* dv, int B, int N, int H, int H_KV, int D, int causal, float softmax_scale,
                 int dq_layout, int device, void* cuda_stream);
 
+/* hk_attn_bwd for right-padded batches: batch element b attends to its first kv_lens[b] keys only, the backward of
+ * hk_attn_fwd_varlen (the reference's key_padding_mask, training/llama/llama/models/attentions/base.py:97-103; its
+ * kernels have no counterpart). kv_lens: device int32 [B], values clamped to [1, N]; null = no padding. dK and dV
+ * rows of padded keys come back as zeros. Non-causal only (HK_EUNSUPPORTED with causal != 0). */
+int hk_attn_bwd_varlen(const void* q, const void* k, const void* v, const void* d_o, const float* lse,
+                       const float* delta, void* dq, void* dk, void* dv, int B, int N, int H, int H_KV, int D,
+                       const int32_t* kv_lens, int causal, float softmax_scale, int dq_layout, int device,
+                       void* cuda_stream);
+
 /* dq_bnhd[b,n,h,:] = dq_bhnd[b,h,n,:]. Replaces dispatch_dq_shuffle (attn_bkwd_prep.cpp:199-223,236-239); only
  * needed after hk_attn_bwd with HK_DQ_BHND. D a multiple of 8; the two buffers must not alias. */
 int hk_attn_dq_shuffle(const void* dq_bhnd, void* dq_bnhd, int B, int N, int H, int D, int device,

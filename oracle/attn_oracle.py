@@ -121,6 +121,7 @@ def attn_bwd_oracle(
     causal: bool = False,
     softmax_scale: Optional[float] = None,
     dtype: torch.dtype = torch.float32,
+    kv_lens: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """Gradients of O = softmax(scale q k^T) v with respect to q, k, v for the upstream gradient d_o.
 
@@ -128,7 +129,8 @@ def attn_bwd_oracle(
     dk, dv [B,N,H_KV,D] and delta [B,H,1,N] = rowsum(d_o * O), all in `dtype` (no bf16 rounding: the
     tolerance of the comparison covers the kernels' bf16 outputs). O here is the unrounded attention
     output; the kernels compute delta from the bf16-rounded O of the forward pass
-    (kernels/attn/gqa_backwards/attn_bkwd_prep.cpp:176-185).
+    (kernels/attn/gqa_backwards/attn_bkwd_prep.cpp:176-185). ``kv_lens`` [B] masks keys at or beyond a batch
+    element's length (the reference's ``key_padding_mask``, ``base.py:97-103``); their dk and dv are zero.
     """
     b, n, h, d = q.shape
     hkv = k.shape[2]
@@ -150,6 +152,9 @@ def attn_bwd_oracle(
             scores = torch.einsum("tgd,sd->gts", qg, ku * scale)
             if causal:
                 scores = scores.masked_fill((col > row).unsqueeze(0), float("-inf"))
+            if kv_lens is not None:
+                assert not causal
+                scores = scores.masked_fill((col >= int(kv_lens[bi])).unsqueeze(0), float("-inf"))
             p = torch.softmax(scores, dim=-1)                    # [G, N, N]
             o = torch.einsum("gts,sd->tgd", p, vu)
             dl = (dog * o).sum(-1)                               # [N, G]

@@ -87,7 +87,11 @@ def main() -> None:
     q = torch.randn((b, n, h, d), generator=gen).to(torch.bfloat16)
     k = torch.randn((b, n, hkv, d), generator=gen).to(torch.bfloat16)
     v = torch.randn((b, n, hkv, d), generator=gen).to(torch.bfloat16)
+    d_o = torch.randn((b, n, h, d), generator=gen).to(torch.bfloat16)  # drawn last: q, k, v keep their values
     keep = torch.arange(n).view(1, n) < torch.tensor(lens).view(b, 1)  # True = keep (base.py:88-89)
+    qf = q.float().requires_grad_(True)
+    kvf = torch.stack([k.float(), v.float()], dim=2).requires_grad_(True)
+    CrossAttention(causal=False)(qf, kvf, key_padding_mask=keep).backward(d_o.float())
     with torch.no_grad():
         o32 = CrossAttention(causal=False)(q.float(), torch.stack([k.float(), v.float()], dim=2), key_padding_mask=keep)
         kk = k.double().repeat_interleave(h // hkv, dim=2)
@@ -96,7 +100,10 @@ def main() -> None:
         lse = torch.logsumexp(scores, dim=-1).numpy()
     path = os.path.join(HERE, f"case_{name}.npz")
     np.savez_compressed(path, q=bf16_bits(q), k=bf16_bits(k), v=bf16_bits(v), o_ref_fp32=o32.numpy().astype(np.float32),
-                        lse_def_fp64=lse, kv_lens=np.array(lens, dtype=np.int32),
+                        lse_def_fp64=lse, kv_lens=np.array(lens, dtype=np.int32), d_o=bf16_bits(d_o),
+                        dq_ref_fp32=qf.grad.numpy().astype(np.float32),
+                        dk_ref_fp32=kvf.grad[:, :, 0].contiguous().numpy().astype(np.float32),
+                        dv_ref_fp32=kvf.grad[:, :, 1].contiguous().numpy().astype(np.float32),
                         shape=np.array([b, n, h, hkv, d, 0, seed], dtype=np.int64))
     print("wrote", path, os.path.getsize(path), "bytes")
 

@@ -2,9 +2,10 @@
 oracle and against gradients of the reference's own PyTorch module, through the C ABI, the reference's
 Python entry points and the autograd function.
 
-Tolerance (written here, floating point): every gradient element within 2e-2 + 1e-2 * |ref| of the fp32
-oracle (outputs are bf16: half an ulp is 2^-9 relative; P and dS are rounded to bf16 before the last
-products), and a relative L2 error of at most 5e-3 per tensor."""
+Tolerance (written here, floating point): every gradient element within max(2e-2, 1e-2 * max|ref|) + 1e-2 * |ref|
+of the fp32 oracle (outputs are bf16: half an ulp is 2^-9 relative; P and dS are rounded to bf16 before the last
+products, and a dK or dV element sums thousands of such terms, so its absolute error scales with the size of the
+tensor, not of the element), and a relative L2 error of at most 5e-3 per tensor."""
 import glob
 import os
 
@@ -33,10 +34,10 @@ def make_do(shape, seed):
     return torch.randn(shape, generator=torch.Generator().manual_seed(seed)).to(torch.bfloat16)
 
 
-def run_bwd(q, k, v, d_o, causal, dev, scale=None, dq_layout=hk.HK_DQ_BNHD):
+def run_bwd(q, k, v, d_o, causal, dev, scale=None, dq_layout=hk.HK_DQ_BNHD, kv_lens=None):
     """Forward + prep + backward on the GPU; gradient buffers are poisoned with NaN first."""
     qd, kd, vd, dod = (t.to(dev) for t in (q, k, v, d_o))
-    o, lse = hk.attn_fwd(qd, kd, vd, causal=causal, softmax_scale=scale)
+    o, lse = hk.attn_fwd(qd, kd, vd, causal=causal, softmax_scale=scale, kv_lens=kv_lens)
     delta = hk.attn_bwd_prep(o, dod)
     b, n, h, d = q.shape
     dq_shape = (b, n, h, d) if dq_layout == hk.HK_DQ_BNHD else (b, h, n, d)
@@ -44,7 +45,7 @@ def run_bwd(q, k, v, d_o, causal, dev, scale=None, dq_layout=hk.HK_DQ_BNHD):
     dk = torch.full(k.shape, float("nan"), dtype=torch.bfloat16, device=dev)
     dv = torch.full(v.shape, float("nan"), dtype=torch.bfloat16, device=dev)
     hk.attn_bwd(qd, kd, vd, dod, lse, delta, causal=causal, softmax_scale=scale, dq=dq, dk=dk, dv=dv,
-                dq_layout=dq_layout)
+                dq_layout=dq_layout, kv_lens=kv_lens)
     assert _native.device_status(0) == 0
     return dq.cpu(), dk.cpu(), dv.cpu(), delta.cpu(), o.cpu()
 
@@ -53,7 +54,7 @@ def assert_grad_parity(got, ref, name):
     got = got.float()
     assert not torch.isnan(got).any(), f"{name} has unwritten elements"
     diff = (got - ref).abs()
-    bad = diff > (ATOL + RTOL * ref.abs())
+    bad = diff > (max(ATOL, RTOL * float(ref.abs().max())) + RTOL * ref.abs())
     assert not bool(bad.any()), f"{name}: {int(bad.sum())} elements out of tolerance, max|diff| = {float(diff.max())}"
     if float(ref.abs().max()) > 1e-3:  # a single key gives P = 1 and dq = dk = 0 up to rounding: no relative figure then
         l2 = float(diff.pow(2).sum().sqrt() / ref.pow(2).sum().sqrt())
@@ -103,7 +104,8 @@ def test_parity_against_reference_module_gradients(dev, path):
     b, n, h, hkv, d, causal, _ = [int(x) for x in z["shape"]]
     bits = lambda a: torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16)  # noqa: E731
     q, k, v, d_o = bits(z["q"]), bits(z["k"]), bits(z["v"]), bits(z["d_o"])
-    dq, dk, dv, _delta, _o = run_bwd(q, k, v, d_o, bool(causal), dev)
+    kv_lens = torch.from_numpy(z["kv_lens"]).to(dev) if "kv_lens" in z.files else None
+    dq, dk, dv, _delta, _o = run_bwd(q, k, v, d_o, bool(causal), dev, kv_lens=kv_lens)
     assert_grad_parity(dq, torch.from_numpy(z["dq_ref_fp32"]), "dq")
     assert_grad_parity(dk, torch.from_numpy(z["dk_ref_fp32"]), "dk")
     assert_grad_parity(dv, torch.from_numpy(z["dv_ref_fp32"]), "dv")
@@ -198,6 +200,32 @@ def test_autograd_function_backward(dev):
     assert_grad_parity(qkv.grad[:, :, 2].cpu(), rv, "dv")
 
 
+def test_modules_with_key_padding_mask(dev):
+    """A right-padded key_padding_mask through the module, forward and backward, against the oracle (the reference's
+    PyTorch modules implement the mask, base.py:97-103; its kernel-backed modules ignore it)."""
+    from hipkittens_b200.attention import HipCrossAttention
+    from oracle.attn_oracle import attn_fwd_oracle
+
+    q, k, v = make_prefill_inputs(3, 256, 4, 2, 64, seed=58)
+    d_o = make_do((3, 256, 4, 64), seed=59)
+    lens = torch.tensor([256, 100, 129], dtype=torch.int32)
+    mask = (torch.arange(256).view(1, 256) < lens.view(3, 1)).to(dev)
+    qd = q.to(dev).requires_grad_(True)
+    kvd = torch.stack([k, v], dim=2).to(dev).requires_grad_(True)
+    out = HipCrossAttention(causal=False)(qd, kvd, key_padding_mask=mask)
+    o_ref, _ = attn_fwd_oracle(q, k, v, False, kv_lens=lens)
+    assert float((out.detach().float().cpu() - o_ref.float()).abs().max()) <= 2e-2
+    out.backward(d_o.to(dev))
+    rq, rk, rv, _ = attn_bwd_oracle(q, k, v, d_o, causal=False, kv_lens=lens)
+    assert_grad_parity(qd.grad.cpu(), rq, "dq")
+    assert_grad_parity(kvd.grad[:, :, 0].cpu(), rk, "dk")
+    assert_grad_parity(kvd.grad[:, :, 1].cpu(), rv, "dv")
+    holes = mask.clone()
+    holes[1, 3] = False
+    with pytest.raises(ValueError):
+        HipCrossAttention(causal=False)(qd, kvd, key_padding_mask=holes)
+
+
 def test_custom_softmax_scale(dev):
     q, k, v = make_prefill_inputs(1, 256, 2, 1, 128, seed=49)
     d_o = make_do((1, 256, 2, 128), seed=50)
@@ -217,6 +245,31 @@ def test_bad_arguments(dev):
     with pytest.raises(RuntimeError):
         hk.attn_bwd(q.to(dev), k.to(dev), v.to(dev), q.to(dev), torch.zeros(1, 2, 1, 64, device=dev),
                     torch.zeros(1, 2, 1, 128, device=dev))  # L of the wrong length
+
+
+def test_key_padding_lengths(dev):
+    """Per-batch key lengths (the reference's key_padding_mask): a length inside the first block, one on a block
+    boundary, the full length, and one inside a later block; key blocks wholly beyond a length are skipped by both
+    kernels and their dK / dV rows come back as exact zeros, whatever the padded keys contain."""
+    q, k, v = make_prefill_inputs(4, 512, 8, 2, 128, seed=56)
+    d_o = make_do((4, 512, 8, 128), seed=57)
+    lens = torch.tensor([512, 5, 256, 300], dtype=torch.int32)
+    dq, dk, dv, _, _ = run_bwd(q, k, v, d_o, False, dev, kv_lens=lens.to(dev))
+    rq, rk, rv, _ = attn_bwd_oracle(q, k, v, d_o, causal=False, kv_lens=lens)
+    assert_grad_parity(dq, rq, "dq")
+    assert_grad_parity(dk, rk, "dk")
+    assert_grad_parity(dv, rv, "dv")
+    k2, v2 = k.clone(), v.clone()
+    for b in range(4):
+        assert float(dk[b, int(lens[b]):].abs().max() if int(lens[b]) < 512 else 0) == 0.0
+        assert float(dv[b, int(lens[b]):].abs().max() if int(lens[b]) < 512 else 0) == 0.0
+        k2[b, int(lens[b]):] = 1e4
+        v2[b, int(lens[b]):] = -3e4  # finite: a padded key inside a loaded tile still meets p = 0 in the products
+    dq2, dk2, dv2, _, _ = run_bwd(q, k2, v2, d_o, False, dev, kv_lens=lens.to(dev))
+    assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)
+    with pytest.raises(hk.HkError):
+        hk.attn_bwd(q.to(dev), k.to(dev), v.to(dev), d_o.to(dev), torch.zeros(4, 8, 1, 512, device=dev),
+                    torch.zeros(4, 8, 1, 512, device=dev), causal=True, kv_lens=lens.to(dev))
 
 
 def test_padded_rows_do_not_leak(dev):

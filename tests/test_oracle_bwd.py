@@ -20,7 +20,7 @@ def _bf16(bits: np.ndarray) -> torch.Tensor:
 
 
 def test_golden_gradient_cases_present():
-    assert len(GOLDEN) >= 4
+    assert len(GOLDEN) >= 5
 
 
 @pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
@@ -29,7 +29,8 @@ def test_oracle_matches_reference_module_gradients(path):
     b, n, h, hkv, d, causal, _seed = [int(x) for x in z["shape"]]
     q, k, v, d_o = _bf16(z["q"]), _bf16(z["k"]), _bf16(z["v"]), _bf16(z["d_o"])
     assert d_o.shape == (b, n, h, d)
-    dq, dk, dv, _delta = attn_bwd_oracle(q, k, v, d_o, causal=bool(causal))
+    kv_lens = torch.from_numpy(z["kv_lens"]) if "kv_lens" in z.files else None  # the reference's key_padding_mask
+    dq, dk, dv, _delta = attn_bwd_oracle(q, k, v, d_o, causal=bool(causal), kv_lens=kv_lens)
     for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
         ref = torch.from_numpy(z[name + "_ref_fp32"])
         assert got.shape == ref.shape
