@@ -71,3 +71,30 @@ def scatter_outputs(o_full, l_full, o_s, l_s, members: List[UnitSlice], h_kv: in
     for i, s in enumerate(members):
         o_full[s.batch, :, s.kvh_lo * g:s.kvh_hi * g] = o_s[i]
         l_full[s.batch, s.kvh_lo * g:s.kvh_hi * g] = l_s[i]
+
+
+def shard_like_q(t, h_kv: int, members: List[UnitSlice]):
+    """This rank's part of another [B,N,H,D] tensor that follows q's heads (dO, O), for one group returned by
+    `shard_tensors`."""
+    import torch
+
+    g = t.shape[2] // h_kv
+    return torch.stack([t[s.batch, :, s.kvh_lo * g:s.kvh_hi * g] for s in members]).contiguous()
+
+
+def shard_stats(t, h_kv: int, members: List[UnitSlice]):
+    """This rank's part of a per-row statistic [B,H,1,N] (L, delta) for one group returned by `shard_tensors`."""
+    import torch
+
+    g = t.shape[1] // h_kv
+    return torch.stack([t[s.batch, s.kvh_lo * g:s.kvh_hi * g] for s in members]).contiguous()
+
+
+def scatter_grads(dq_full, dk_full, dv_full, dq_s, dk_s, dv_s, members: List[UnitSlice], h_kv: int) -> None:
+    """Write a shard's dQ [n,N,H',D], dK and dV [n,N,H_KV',D] back into the full-size gradient tensors. The backward
+    shards exactly like the forward: dK and dV of a kv head only need the query heads of its own group."""
+    g = dq_full.shape[2] // h_kv
+    for i, s in enumerate(members):
+        dq_full[s.batch, :, s.kvh_lo * g:s.kvh_hi * g] = dq_s[i]
+        dk_full[s.batch, :, s.kvh_lo:s.kvh_hi] = dk_s[i]
+        dv_full[s.batch, :, s.kvh_lo:s.kvh_hi] = dv_s[i]

@@ -74,3 +74,37 @@ def test_two_rank_sharded_forward_matches_unsharded(b, hkv):
     ret = mgr.dict()
     mp.spawn(_worker, args=(2, _free_port(), b, 128, 2 * hkv, hkv, 64, True, ret), nprocs=2, join=True)
     assert ret["o"] == 0.0 and ret["l"] == 0.0
+
+
+def _bwd_worker(rank, world, port, b, n, h, hkv, d, causal, ret):
+    from hipkittens_b200.shard import scatter_grads, shard_like_q
+    from oracle.attn_oracle import attn_bwd_oracle
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    q, k, v = make_prefill_inputs(b, n, h, hkv, d, seed=0)
+    d_o = make_prefill_inputs(b, n, h, hkv, d, seed=1)[0]
+    dq_full, dk_full, dv_full = torch.zeros(q.shape), torch.zeros(k.shape), torch.zeros(v.shape)
+    for qs, ks, vs, members in shard_tensors(q, k, v, hkv, partition_units(b, hkv, world, rank)):
+        dos = shard_like_q(d_o, hkv, members)
+        dq_s, dk_s, dv_s, _ = attn_bwd_oracle(qs, ks, vs, dos, causal)  # stands in for the kernels on this rank
+        scatter_grads(dq_full, dk_full, dv_full, dq_s, dk_s, dv_s, members, hkv)
+    for t in (dq_full, dk_full, dv_full):
+        dist.all_reduce(t)  # verification only: shards are disjoint
+    if rank == 0:
+        rq, rk, rv, _ = attn_bwd_oracle(q, k, v, d_o, causal)
+        ret["err"] = max(float((dq_full - rq).abs().max()), float((dk_full - rk).abs().max()),
+                         float((dv_full - rv).abs().max()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("b,hkv", [(4, 2), (1, 4)])
+def test_two_rank_sharded_backward_matches_unsharded(b, hkv):
+    """dK and dV of a kv head need only the query heads of its own group, so the backward shards over the same
+    (batch, kv-head) units as the forward, again without a collective on the data path."""
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_bwd_worker, args=(2, _free_port(), b, 128, 2 * hkv, hkv, 64, True, ret), nprocs=2, join=True)
+    assert ret["err"] == 0.0
