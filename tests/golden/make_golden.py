@@ -1,8 +1,8 @@
 """Generate the golden fixtures in this folder by running the reference's own PyTorch attention.
 
-Run once in a container that has the reference checkout (default location below, or pass its path):
+Run once in a container that has the reference checkout, giving its path:
 
-    python tests/golden/make_golden.py [/path/to/HipKittens]
+    python tests/golden/make_golden.py /path/to/HipKittens
 
 It imports ``llama.models.attentions.base.CrossAttention`` / ``SelfAttention`` from the reference's
 ``training/llama`` tree and evaluates them on seeded bf16-valued inputs, once on fp32 copies (then the
@@ -34,12 +34,18 @@ CASES = [
 PADDED = ("b3_n256_h4_kv2_d64_keypad", 3, 256, 4, 2, 64, 4, [256, 100, 129])
 
 
+def reference_root() -> str:
+    if len(sys.argv) < 2 or not os.path.isdir(os.path.join(sys.argv[1], "training", "llama")):
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/HipKittens")
+    return sys.argv[1]
+
+
 def bf16_bits(t: torch.Tensor) -> np.ndarray:
     return t.contiguous().view(torch.int16).numpy().view(np.uint16)
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = reference_root()
     sys.path.insert(0, os.path.join(ref_root, "training", "llama"))
     from llama.models.attentions.base import CrossAttention, SelfAttention  # noqa: E402
 
@@ -116,7 +122,7 @@ def rotary_main() -> None:
 
     from einops import repeat
 
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = reference_root()
     src = open(os.path.join(ref_root, "kernels", "rotary", "test_python.py")).read()
     tree = ast.parse(src)
     wanted = [n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name in ("get_cos_sin", "get_output")]
