@@ -280,7 +280,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   constexpr int kChunks = D / 64;
   constexpr int RA = SM::kRingA, RB = SM::kRingB;
   enum { KV_FULL = 0, KV_EMPTY, ST_FULL, DP_FULL, P_FULL, DS_FULL, ACC_FULL, S_FREE, QA_FULL = 8, QA_EMPTY = 14,
-         RB_FULL = 20, RB_EMPTY = 24, STAT_FULL = 28, STAT_EMPTY = 30, CTRL = 32 };
+         RB_FULL = 20, RB_EMPTY = 24, STAT_FULL = 28, STAT_EMPTY = 30, DP_FREE = 32, Y_FREE = 33, CTRL = 34 };
   static_assert(RA <= 6 && RB <= 4, "barrier slots");
 
   extern __shared__ __align__(1024) uint8_t bwd_smem[];
@@ -304,12 +304,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   if (tid == 0) {
     *abort_word = 0;
     mbar_init(bars + KV_FULL, 1);
-    mbar_init(bars + KV_EMPTY, 2);  // one arrival per issuing thread (K feeds S^T, V feeds dP^T)
+    mbar_init(bars + KV_EMPTY, 1);  // K and V only feed issuer A's products
     mbar_init(bars + ST_FULL, 1);
     mbar_init(bars + DP_FULL, 1);
     mbar_init(bars + P_FULL, kBwdCW);    // one arrival per element-wise warp
     mbar_init(bars + DS_FULL, kBwdCW);
     mbar_init(bars + S_FREE, kBwdCW);
+    mbar_init(bars + DP_FREE, kBwdCW);
+    mbar_init(bars + Y_FREE, 1);
     mbar_init(bars + ACC_FULL, 1);
     for (int s = 0; s < RA; ++s) {
       mbar_init(bars + QA_FULL + s, 1);
@@ -317,7 +319,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     }
     for (int s = 0; s < RB; ++s) {
       mbar_init(bars + RB_FULL + s, 1);
-      mbar_init(bars + RB_EMPTY + s, 1);
+      mbar_init(bars + RB_EMPTY + s, 2);  // dO feeds dP^T (issuer A) and dV (issuer B)
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bars + STAT_FULL + s, 1);   // one arrival by the statistics loader warp
@@ -335,10 +337,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const uint32_t tmem = *tmem_slot;
   volatile uint32_t* abortp = abort_word;
   const int G = p.H / p.H_KV;
-  // TMEM columns: X = S^T [0,128); Y = dP^T [128,256), later overwritten by the two bf16 operands: each thread
-  // keeps to the kBwdPC columns it read, P^T in their first half, dS^T in their second half;
-  // dK [256,256+D); dV [256+D,256+2D).
-  constexpr uint32_t cST = 0, cY = 128, cDK = 256, cDV = 256 + D;
+  // TMEM columns: X [0,128) takes the two score-shaped products in turn, S^T(n) then dP^T(n), each free again as soon
+  // as the element-wise warps hold it in registers; Y [128,256) holds the two bf16 operands, P^T in [128,192) and dS^T
+  // in [192,256), free again when dV(n) and dK(n) have consumed them; dK [256,256+D); dV [256+D,256+2D). Nothing
+  // fp32 aliases anything bf16, so no product has to wait behind another one's operands.
+  constexpr uint32_t cX = 0, cY = 128, cDK = 256, cDV = 256 + D;
 
   if (warp < kBwdCW) {
     // ------------------------------------------------------------------ element-wise warps
@@ -346,8 +349,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const int part = warp >> 2;                        // which kBwdPC query columns of the tile
     const int row = (warp & 3) * 32 + lane;            // key row inside the block == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tS = tmem + lane_addr + cST + part * kBwdPC;
-    const uint32_t tY = tmem + lane_addr + cY + part * kBwdPC;
+    const uint32_t tX = tmem + lane_addr + cX + part * kBwdPC;
+    const uint32_t tPt = tmem + lane_addr + cY + part * (kBwdPC / 2);        // this thread's packed columns of P^T
+    const uint32_t tDSt = tmem + lane_addr + cY + 64 + part * (kBwdPC / 2);  // ... and of dS^T
     const float c = p.scale_log2;
     constexpr float kNegLog2e = -1.4426950408889634f;
     uint32_t it = 0, acc_cnt = 0;
@@ -382,7 +386,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const bool diag = CAUSAL && (n % w.cnt_i == 0);  // the query tile at the key block's own position
         const float* sL = sStat + (it & 1) * 256 + part * kBwdPC;
         const float* sDl = sL + 128;
-        // ---- S^T into registers; X is free for S^T of the next iteration right away
+        // ---- S^T into registers; X is free for dP^T of this pair right away
         ok = mbar_wait(bars + ST_FULL, it & 1, abortp, kWaitLimitCycles) &&
              mbar_wait(bars + STAT_FULL + (it & 1), (it >> 1) & 1, abortp, kWaitLimitCycles);
         ok = __all_sync(0xffffffffu, ok);
@@ -390,7 +394,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         tc_fence_after();
         HK_STAMP(0, 1);
         uint32_t su[kBwdPC];
-        bwd_ld_part(tS, su);
+        bwd_ld_part(tX, su);
         tmem_wait_ld();
         tc_fence_before();
         __syncwarp();
@@ -426,21 +430,29 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           }
         }
         HK_STAMP(0, 2);
-        // ---- dP^T into registers; only then may the bf16 operands overwrite Y
+        // ---- dP^T into registers; X is free for S^T of the next pair
         ok = mbar_wait(bars + DP_FULL, it & 1, abortp, kWaitLimitCycles);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
         HK_STAMP(0, 3);
         uint32_t du[kBwdPC];
-        bwd_ld_part(tY, du);
+        bwd_ld_part(tX, du);
         tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + DP_FREE);
+        // ---- Y is free once dV and dK of the previous pair have consumed their operands (first pair ever: at once)
+        ok = mbar_wait(bars + Y_FREE, (it & 1) ^ 1, abortp, kWaitLimitCycles);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
         {
           uint32_t pk[kBwdPC / 2];
 #pragma unroll
           for (int i = 0; i < kBwdPC / 2; ++i)
             pk[i] = pack_bf16x2(__uint_as_float(su[2 * i]), __uint_as_float(su[2 * i + 1]));
-          bwd_st_packed(tY, pk);  // P^T: first half of this thread's columns
+          bwd_st_packed(tPt, pk);
         }
         tmem_wait_st();
         tc_fence_before();
@@ -464,7 +476,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             pk[q4 * 2] = pack_bf16x2(ds0, ds1);
             pk[q4 * 2 + 1] = pack_bf16x2(ds2, ds3);
           }
-          bwd_st_packed(tY + kBwdPC / 2, pk);  // dS^T: second half of this thread's columns
+          bwd_st_packed(tDSt, pk);
         }
         tmem_wait_st();
         tc_fence_before();
@@ -543,58 +555,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
       }
     } else if (warp == kBwdCW + 1 && lane == 0) {
-      // ---------------- UMMA issuer A: S^T = K Q^T, as soon as the previous S^T has been read
-      // Two threads issue. This one runs ahead with the S^T products, which only wait for the Q tile and for the
-      // element-wise warps' word that X is free; issuer B follows the dependent chain dV, dK, dP^T. A thread that
-      // issues returns only a few MMAs ahead of the pipe, so its commits and mbarrier waits (~180 clocks per product)
-      // would otherwise let the pipe run dry between products.
+      // ---------------- UMMA issuer A: the two score-shaped products, S^T = K Q^T and dP^T = V dO^T, which take
+      // turns in X: each is issued as soon as the element-wise warps have read its predecessor.
+      // Two threads issue because a thread that issues returns only a few MMAs ahead of the pipe: with one issuer
+      // every commit and mbarrier wait between two products (~180 clocks) let the pipe run dry.
       constexpr uint32_t tile16 = kTile >> 4;
       const uint32_t k_lo = smem_desc_lo(smem_u32(sK), 16);
-      const uint32_t q_lo0 = smem_desc_lo(smem_u32(sQ), 16);       // K-major view (B of S^T)
-      uint32_t item_cnt = 0, sf_cnt = 0;
-      int qa = 0;
-      uint32_t qa_par = 0;
-      bool ok = true;
-#ifdef HK_TRACE
-      const bool trace_on = p.trace != nullptr;
-      int trace_n = 0;
-#endif
-      for (int round = 0; ok; ++round) {
-        const int idx = item_for_round(round, blockIdx.x, gridDim.x);
-        if (idx >= p.n_items) {
-          if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
-          continue;
-        }
-        const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
-        if (w.n_iter == 0) continue;  // key block wholly beyond this batch element's length: nothing to do
-        ok = mbar_wait(bars + KV_FULL, item_cnt & 1, abortp, kWaitLimitCycles);
-        if (!ok) break;
-        ++item_cnt;
-        for (int n = 0; n < w.n_iter && ok; ++n, ++sf_cnt) {
-          // X has been read (first S^T ever: passes at once)
-          ok = mbar_wait(bars + S_FREE, (sf_cnt & 1) ^ 1, abortp, kWaitLimitCycles) &&
-               mbar_wait(bars + QA_FULL + qa, qa_par, abortp, kWaitLimitCycles);
-          if (!ok) break;
-          tc_fence_after();
-          HK_STAMP(2, 12);
-          bwd_issue_ss<D>(tmem + cST, k_lo, q_lo0 + qa * tile16);
-          umma_commit(bars + ST_FULL);
-          HK_STAMP(2, 13);
-          if (++qa == RA) {
-            qa = 0;
-            qa_par ^= 1;
-          }
-        }
-        if (!ok) break;
-        umma_commit(bars + KV_EMPTY);  // K has fed its last product (issuer B arrives for V)
-      }
-    } else if (warp == kBwdCW + 2 && lane == 0) {
-      // ---------------- UMMA issuer B: dV += P^T dO, dK += dS^T Q, then dP^T of the next iteration into Y
-      constexpr uint32_t tile16 = kTile >> 4;
       const uint32_t v_lo = smem_desc_lo(smem_u32(sV), 16);
-      const uint32_t q_mn0 = smem_desc_lo(smem_u32(sQ), kSub);     // MN-major view (B of dK)
+      const uint32_t q_lo0 = smem_desc_lo(smem_u32(sQ), 16);       // K-major view (B of S^T)
       const uint32_t do_lo0 = smem_desc_lo(smem_u32(sDO), 16);     // K-major view (B of dP^T)
-      const uint32_t do_mn0 = smem_desc_lo(smem_u32(sDO), kSub);   // MN-major view (B of dV)
       uint32_t item_cnt = 0, it = 0;
       int qa = 0, rb = 0;
       uint32_t qa_par = 0, rb_par = 0;
@@ -611,52 +580,103 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
         const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
         if (w.n_iter == 0) continue;  // key block wholly beyond this batch element's length: nothing to do
-        ok = mbar_wait(bars + KV_FULL, item_cnt & 1, abortp, kWaitLimitCycles) &&
-             mbar_wait(bars + RB_FULL + rb, rb_par, abortp, kWaitLimitCycles);
+        ok = mbar_wait(bars + KV_FULL, item_cnt & 1, abortp, kWaitLimitCycles);
         if (!ok) break;
         ++item_cnt;
-        tc_fence_after();
-        bwd_issue_ss<D>(tmem + cY, v_lo, do_lo0 + rb * tile16);  // ordered behind the previous item's dV / dK
-        umma_commit(bars + DP_FULL);
         for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
-          const int cur_q = qa, cur_do = rb;
-          const uint32_t cur_q_par = qa_par;
+          // S^T(n): dP^T of the previous pair has been read out of X (first pair ever: passes at once)
+          ok = mbar_wait(bars + DP_FREE, (it & 1) ^ 1, abortp, kWaitLimitCycles) &&
+               mbar_wait(bars + QA_FULL + qa, qa_par, abortp, kWaitLimitCycles);
+          if (!ok) break;
+          tc_fence_after();
+          HK_STAMP(2, 12);
+          bwd_issue_ss<D>(tmem + cX, k_lo, q_lo0 + qa * tile16);
+          umma_commit(bars + ST_FULL);
+          HK_STAMP(2, 13);
           if (++qa == RA) {
             qa = 0;
             qa_par ^= 1;
           }
+          // dP^T(n): S^T(n) has been read out of X
+          ok = mbar_wait(bars + S_FREE, it & 1, abortp, kWaitLimitCycles) &&
+               mbar_wait(bars + RB_FULL + rb, rb_par, abortp, kWaitLimitCycles);
+          if (!ok) break;
+          tc_fence_after();
+          bwd_issue_ss<D>(tmem + cX, v_lo, do_lo0 + rb * tile16);
+          umma_commit(bars + DP_FULL);
+          umma_commit(bars + RB_EMPTY + rb);  // first of two arrivals (issuer B: after dV of this stage)
+          HK_STAMP(2, 17);
           if (++rb == RB) {
             rb = 0;
             rb_par ^= 1;
           }
-          ok = mbar_wait(bars + P_FULL, it & 1, abortp, kWaitLimitCycles);
+        }
+        if (!ok) break;
+        umma_commit(bars + KV_EMPTY);
+      }
+    } else if (warp == kBwdCW + 2 && lane == 0) {
+      // ---------------- UMMA issuer B: the two gradient-shaped products, dV += P^T dO and dK += dS^T Q
+      constexpr uint32_t tile16 = kTile >> 4;
+      constexpr uint32_t idesc = make_idesc_bf16(kBlockM, D, true);
+      constexpr uint32_t desc_hi = smem_desc_hi(1024);
+      const uint32_t q_mn0 = smem_desc_lo(smem_u32(sQ), kSub);     // MN-major view (B of dK)
+      const uint32_t do_mn0 = smem_desc_lo(smem_u32(sDO), kSub);   // MN-major view (B of dV)
+      uint32_t it = 0;
+      int qa = 0, rb = 0;
+      uint32_t qa_par = 0, rb_par = 0;
+      bool ok = true;
+#ifdef HK_TRACE
+      const bool trace_on = p.trace != nullptr;
+      int trace_n = 0;
+#endif
+      for (int round = 0; ok; ++round) {
+        const int idx = item_for_round(round, blockIdx.x, gridDim.x);
+        if (idx >= p.n_items) {
+          if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
+          continue;
+        }
+        const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
+        if (w.n_iter == 0) continue;  // key block wholly beyond this batch element's length: nothing to do
+        for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
+          ok = mbar_wait(bars + P_FULL, it & 1, abortp, kWaitLimitCycles) &&
+               mbar_wait(bars + RB_FULL + rb, rb_par, abortp, kWaitLimitCycles);
           if (!ok) break;
           tc_fence_after();
           HK_STAMP(3, 10);
-          bwd_issue_ts<D>(tmem + cDV, tmem + cY, do_mn0 + cur_do * tile16, n > 0);
-          umma_commit(bars + RB_EMPTY + cur_do);  // dO fed dP^T earlier and dV now
+          {
+            const uint32_t b_lo = do_mn0 + rb * tile16;
+#pragma unroll
+            for (int k = 0; k < kBlockN / 16; ++k)
+              umma_ts_lohi(tmem + cDV, tmem + cY + k * 8, b_lo + k * 128, desc_hi, idesc, (n > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(bars + RB_EMPTY + rb);  // second of two arrivals
           HK_STAMP(3, 11);
+          if (++rb == RB) {
+            rb = 0;
+            rb_par ^= 1;
+          }
           ok = mbar_wait(bars + DS_FULL, it & 1, abortp, kWaitLimitCycles) &&
-               mbar_wait(bars + QA_FULL + cur_q, cur_q_par, abortp, kWaitLimitCycles);
+               mbar_wait(bars + QA_FULL + qa, qa_par, abortp, kWaitLimitCycles);
           if (!ok) break;
           tc_fence_after();
           HK_STAMP(3, 14);
-          bwd_issue_ts<D>(tmem + cDK, tmem + cY + kBwdPC / 2, q_mn0 + cur_q * tile16, n > 0);
+          {
+            const uint32_t b_lo = q_mn0 + qa * tile16;
+#pragma unroll
+            for (int k = 0; k < kBlockN / 16; ++k)
+              umma_ts_lohi(tmem + cDK, tmem + cY + 64 + k * 8, b_lo + k * 128, desc_hi, idesc, (n > 0 || k > 0) ? 1u : 0u);
+          }
           // S^T of this stage (issuer A) completed before dS^T could be computed, so this one arrival frees Q
-          umma_commit(bars + QA_EMPTY + cur_q);
+          umma_commit(bars + QA_EMPTY + qa);
+          umma_commit(bars + Y_FREE);
           HK_STAMP(3, 15);
-          if (n + 1 < w.n_iter) {
-            ok = mbar_wait(bars + RB_FULL + rb, rb_par, abortp, kWaitLimitCycles);
-            if (!ok) break;
-            tc_fence_after();
-            bwd_issue_ss<D>(tmem + cY, v_lo, do_lo0 + rb * tile16);  // overwrites P^T(n), dS^T(n): behind dV(n), dK(n)
-            umma_commit(bars + DP_FULL);
-            HK_STAMP(3, 17);
+          if (++qa == RA) {
+            qa = 0;
+            qa_par ^= 1;
           }
         }
         if (!ok) break;
         umma_commit(bars + ACC_FULL);
-        umma_commit(bars + KV_EMPTY);
       }
     } else if (warp == kBwdCW + 3) {
       // ---------------- statistics loader: L and delta of each query tile -> shared memory (indexed by column in
