@@ -582,45 +582,87 @@ def measure_e2e(hk, kind, args, dev, stream, causal, b, n, h, hkv, d, shards, de
         h2d = sum(t.numel() * t.element_size() for hs in host_in for t in hs)
         d2h = sum(t.numel() * t.element_size() for ho in host_out for t in ho)
 
-        def step():
-            for hs, ds, do, ho in zip(host_in, dev_in, dev_out, host_out):
-                for src, dst in zip(hs, ds):
-                    dst.copy_(src, non_blocking=True)
-                tk.dispatch_micro(ds[0], ds[1], ds[2], do[0], do[1], causal=causal, stream=stream.cuda_stream)
-                ho[0].copy_(do[0], non_blocking=True)
-                ho[1].copy_(do[1], non_blocking=True)
+        # The (batch, kv-head) units are independent, so a step is cut into batch chunks that flow through three
+        # streams: chunk c+1 is copied in while chunk c is computed and chunk c-1 is copied out (PCIe is full duplex).
+        s_in, s_cmp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
 
-        path = "pinned host -> H2D -> tk_kernel.dispatch_micro -> D2H (O and L)"
+        def step():
+            start = torch.cuda.Event()
+            start.record(stream)
+            for st in (s_in, s_cmp, s_out):
+                st.wait_event(start)
+            for hs, ds, do, ho in zip(host_in, dev_in, dev_out, host_out):
+                nb = ds[0].shape[0]
+                n_chunks = min(nb, 8)
+                bounds = [nb * c // n_chunks for c in range(n_chunks + 1)]
+                for lo, hi in zip(bounds[:-1], bounds[1:]):
+                    with torch.cuda.stream(s_in):
+                        for src, dst in zip(hs, ds):
+                            dst[lo:hi].copy_(src[lo:hi], non_blocking=True)
+                        ready = torch.cuda.Event()
+                        ready.record(s_in)
+                    s_cmp.wait_event(ready)
+                    tk.dispatch_micro(ds[0][lo:hi], ds[1][lo:hi], ds[2][lo:hi], do[0][lo:hi], do[1][lo:hi], causal=causal,
+                                      stream=s_cmp.cuda_stream)
+                    done = torch.cuda.Event()
+                    done.record(s_cmp)
+                    s_out.wait_event(done)
+                    with torch.cuda.stream(s_out):
+                        ho[0][lo:hi].copy_(do[0][lo:hi], non_blocking=True)
+                        ho[1][lo:hi].copy_(do[1][lo:hi], non_blocking=True)
+            for st in (s_in, s_cmp, s_out):
+                stream.wait_stream(st)
+
+        path = ("pinned host -> H2D -> tk_kernel.dispatch_micro -> D2H (O and L), in up to 8 batch chunks pipelined over "
+                "three streams")
     elif kind == "bwd":
-        # one training-step backward as the reference's autograd function runs it (hipkittens.py:96-112):
-        # q, k, v, O, L (saved by the forward) and dO arrive from pinned host memory, the three reference
-        # calls run, dQ, dK, dV go back to pinned host memory
+        # one training-step backward (hipkittens.py:96-112): q, k, v, O, L (saved by the forward) and dO arrive from
+        # pinned host memory, delta prep and the backward run, dQ, dK, dV go back to pinned host memory
         outs, bwd_in = bwd
-        bk, prep = hk.load_tk_kernel_bkwd(causal), hk.load_tk_kernel_bkwd_prep(causal)
         sets = []
         for (qs, ks, vs), (o, l), (d_o, delta, dq, dk, dv) in zip(shards, outs, bwd_in):
             dev_in = [qs, ks, vs, o, l, d_o]
             hin = [t.cpu().pin_memory() for t in dev_in]
-            dq_in = torch.empty((qs.shape[0], qs.shape[2], qs.shape[1], qs.shape[3]), dtype=torch.bfloat16, device=dev)
             hout = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (dq, dk, dv)]
-            sets.append((hin, dev_in, delta, dq_in, (dq, dk, dv), hout))
+            sets.append((hin, dev_in, delta, (dq, dk, dv), hout))
         h2d = sum(t.numel() * t.element_size() for st in sets for t in st[0])
-        d2h = sum(t.numel() * t.element_size() for st in sets for t in st[5])
+        d2h = sum(t.numel() * t.element_size() for st in sets for t in st[4])
+
+        # batch chunks pipelined over three streams, as in the forward; the C ABI's asynchronous entries are used
+        # (the reference's three dispatchers block on the device after every call, which would serialise the chunks)
+        s_in, s_cmp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
 
         def step():
-            for hin, dev_in, delta, dq_in, (dq, dk, dv), hout in sets:
-                for src, dst in zip(hin, dev_in):
-                    dst.copy_(src, non_blocking=True)
+            start = torch.cuda.Event()
+            start.record(stream)
+            for st in (s_in, s_cmp, s_out):
+                st.wait_event(start)
+            for hin, dev_in, delta, (dq, dk, dv), hout in sets:
                 qs, ks, vs, o, l, d_o = dev_in
-                prep.dispatch_prep(o, d_o, delta, stream=stream.cuda_stream)
-                bk.dispatch_bwd_combined(qs, ks, vs, d_o, dq_in, dk, dv, l, delta, causal=causal,
-                                         stream=stream.cuda_stream)
-                prep.dispatch_dq_shuffle(dq_in, dq, stream=stream.cuda_stream)
-                for src, dst in zip((dq, dk, dv), hout):
-                    dst.copy_(src, non_blocking=True)
+                nb = qs.shape[0]
+                n_chunks = min(nb, 8)
+                bounds = [nb * c // n_chunks for c in range(n_chunks + 1)]
+                for lo, hi in zip(bounds[:-1], bounds[1:]):
+                    with torch.cuda.stream(s_in):
+                        for src, dst in zip(hin, dev_in):
+                            dst[lo:hi].copy_(src[lo:hi], non_blocking=True)
+                        ready = torch.cuda.Event()
+                        ready.record(s_in)
+                    s_cmp.wait_event(ready)
+                    hk.attn_bwd_prep(o[lo:hi], d_o[lo:hi], delta[lo:hi], stream=s_cmp)
+                    hk.attn_bwd(qs[lo:hi], ks[lo:hi], vs[lo:hi], d_o[lo:hi], l[lo:hi], delta[lo:hi], causal=causal,
+                                dq=dq[lo:hi], dk=dk[lo:hi], dv=dv[lo:hi], stream=s_cmp)
+                    done = torch.cuda.Event()
+                    done.record(s_cmp)
+                    s_out.wait_event(done)
+                    with torch.cuda.stream(s_out):
+                        for src, dst in zip((dq, dk, dv), hout):
+                            dst[lo:hi].copy_(src[lo:hi], non_blocking=True)
+            for st in (s_in, s_cmp, s_out):
+                stream.wait_stream(st)
 
-        path = ("pinned host (q, k, v, O, L, dO) -> H2D -> dispatch_prep, dispatch_bwd_combined, dispatch_dq_shuffle "
-                "(each blocking, as in the reference) -> D2H (dQ, dK, dV)")
+        path = ("pinned host (q, k, v, O, L, dO) -> H2D -> hk_attn_bwd_prep, hk_attn_bwd (dQ written as [B,N,H,D]) -> D2H "
+                "(dQ, dK, dV), in up to 8 batch chunks pipelined over three streams")
     else:
         q, kp, vp, bt, cl, ws = dec
         # decode step inputs: the new query token, block table and lengths; the KV pool is state that
