@@ -507,7 +507,10 @@ int hk_paged_kv_append(const void* k_new, const void* v_new, void* k_pages, void
   p.max_pages = max_pages_per_seq;
   p.num_pages = num_pages;
   p.status = st->status;
-  hk::paged_kv_append_kernel<<<dim3(T, S), 128, 0, static_cast<cudaStream_t>(cuda_stream)>>>(p);
+  const long long groups = (static_cast<long long>(S) * T + hk::kAppendUnroll - 1) / hk::kAppendUnroll;
+  const long long max_blocks = static_cast<long long>(st->sm_count) * 16;  // 16 x 128 threads fill an SM
+  const unsigned blocks = static_cast<unsigned>(groups < max_blocks ? groups : max_blocks);
+  hk::paged_kv_append_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(cuda_stream)>>>(p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   HK_CUDA(cudaGetLastError());
   return HK_OK;
