@@ -1,0 +1,55 @@
+"""Seeded random shapes through the forward and the backward on the GPU against the oracle: odd head counts, group sizes,
+lengths that are and are not multiples of the tile, both head dimensions, causal or not, with and without key lengths.
+The persistent kernels deal work items to CTAs in rounds, so shapes with few, many and uneven numbers of items all
+exercise different paths of the item schedule and of the ring and barrier bookkeeping."""
+import random
+
+import pytest
+import torch
+
+import hipkittens_b200 as hk
+from hipkittens_b200 import _native
+from hipkittens_b200.synthetic import make_prefill_inputs
+from oracle.attn_oracle import attn_bwd_oracle, attn_fwd_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _cases(n_cases=28, seed=2024):
+    rng = random.Random(seed)
+    out = []
+    for i in range(n_cases):
+        d = rng.choice([64, 128])
+        hkv = rng.choice([1, 2, 3, 4])
+        g = rng.choice([1, 2, 3, 4, 8])
+        b = rng.randint(1, 4)
+        n = rng.choice([rng.randint(1, 1100), 128 * rng.randint(1, 9)])
+        causal = rng.random() < 0.5
+        lens = None
+        if not causal and rng.random() < 0.4:
+            lens = [rng.randint(1, n) for _ in range(b)]
+        out.append((i, b, n, hkv * g, hkv, d, causal, lens))
+    return out
+
+
+@pytest.mark.parametrize("i,b,n,h,hkv,d,causal,lens", _cases(), ids=lambda v: str(v) if not isinstance(v, list) else "lens")
+def test_random_shape(i, b, n, h, hkv, d, causal, lens):
+    dev = torch.device("cuda:0")
+    q, k, v = make_prefill_inputs(b, n, h, hkv, d, seed=500 + i)
+    d_o = make_prefill_inputs(b, n, h, hkv, d, seed=900 + i)[0]
+    kv_lens = torch.tensor(lens, dtype=torch.int32) if lens is not None else None
+    kv_dev = kv_lens.to(dev) if kv_lens is not None else None
+    qd, kd, vd, dod = (t.to(dev) for t in (q, k, v, d_o))
+    o, lse = hk.attn_fwd(qd, kd, vd, causal=causal, kv_lens=kv_dev)
+    delta = hk.attn_bwd_prep(o, dod)
+    dq, dk, dv = hk.attn_bwd(qd, kd, vd, dod, lse, delta, causal=causal, kv_lens=kv_dev)
+    assert _native.device_status(0) == 0
+    o_ref, l_ref = attn_fwd_oracle(q, k, v, causal, kv_lens=kv_lens)
+    assert float((o.float().cpu() - o_ref.float()).abs().max()) <= 2e-2
+    assert float((lse.cpu() - l_ref).abs().max()) <= 1e-3
+    rq, rk, rv, _ = attn_bwd_oracle(q, k, v, d_o, causal=causal, kv_lens=kv_lens)
+    for name, got, ref in (("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rv)):
+        diff = (got.float().cpu() - ref).abs()
+        assert not torch.isnan(diff).any(), name
+        tol = max(2e-2, 1e-2 * float(ref.abs().max())) + 1e-2 * ref.abs()
+        assert bool((diff <= tol).all()), f"{name}: max|diff| = {float(diff.max())}"
