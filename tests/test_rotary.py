@@ -87,3 +87,21 @@ def test_kernel_against_reference_harness_fixture():
     x, cos, sin, ref = _bf16(z["x"]), _bf16(z["cos"]), _bf16(z["sin"]), _bf16(z["o_ref"])
     out = hk.rotary(x.to(dev), cos.to(dev), sin.to(dev))
     assert torch.equal(out.cpu().view(torch.int16), ref.view(torch.int16))
+
+
+@pytest.mark.gpu
+def test_opposite_angle_undoes_the_rotation():
+    """The backward of the pre-pass is the rotation by the opposite angle (-sin): applying both gives x back up to bf16
+    rounding of the two passes (cos^2 + sin^2 = 1 only to bf16 precision)."""
+    dev = torch.device("cuda:0")
+    x = torch.randn((2, 4, 256, 128), generator=torch.Generator().manual_seed(9)).to(torch.bfloat16).to(dev)
+    cos, sin = rotary_cos_sin(256, 128)
+    cos, sin = cos.to(dev), sin.to(dev)
+    y = hk.rotary(x, cos, sin)
+    back = hk.rotary(y, cos, (-sin.float()).to(torch.bfloat16))
+    assert float((back.float() - x.float()).abs().max()) <= 0.06 * float(x.float().abs().max())
+    # and it is the transpose: <rot(x), g> == <x, rot^T(g)>
+    g = torch.randn(x.shape, generator=torch.Generator().manual_seed(10)).to(torch.bfloat16).to(dev)
+    lhs = float((y.float() * g.float()).sum())
+    rhs = float((x.float() * hk.rotary(g, cos, (-sin.float()).to(torch.bfloat16)).float()).sum())
+    assert abs(lhs - rhs) <= 2e-3 * float((x.float().abs() * g.float().abs()).sum())
