@@ -114,3 +114,30 @@ def test_full_size_configuration(dev):
     # size-independent property: doubling V doubles O exactly and leaves L unchanged
     o3, l3 = hk.paged_decode(qd, kp, (vp.float() * 2).to(torch.bfloat16), btd, cld)
     assert torch.equal(o3.float(), o.float() * 2) and torch.equal(l3, l)
+
+
+def test_decode_replays_from_a_cuda_graph(dev):
+    """A serving loop captures the decode step once and replays it: the split and combine launches of
+    hk_attn_paged_decode (workspace owned by the caller) go onto the capturing stream, and a replay after the inputs
+    changed in place gives the same bits as an eager call."""
+    q, kp, vp, bt, cl = make_paged_inputs(3, 16, 2, 128, 16, 400, 100, 1500, seed=12)
+    q, kp, vp, bt, cl = (t.to(dev) for t in (q, kp, vp, bt, cl))
+    ws = torch.empty(hk.paged_decode_workspace_bytes(3, 16, 128, bt.shape[1]), dtype=torch.uint8, device=dev)
+    o = torch.empty_like(q)
+    l = torch.empty((3, 16, 1, 1), dtype=torch.float32, device=dev)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        hk.paged_decode(q, kp, vp, bt, cl, out=o, lse=l, workspace=ws, stream=side)  # warm-up outside the capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        hk.paged_decode(q, kp, vp, bt, cl, out=o, lse=l, workspace=ws, stream=side)
+    q.copy_(torch.randn(q.shape, generator=torch.Generator().manual_seed(13)).to(torch.bfloat16))  # a new query token
+    graph.replay()
+    torch.cuda.synchronize()
+    o_replay, l_replay = o.clone(), l.clone()
+    o_eager, l_eager = hk.paged_decode(q, kp, vp, bt, cl)
+    assert _native.device_status(0) == 0
+    assert torch.equal(o_replay, o_eager) and torch.equal(l_replay, l_eager)
+    o_ref, l_ref = paged_decode_oracle(q.cpu(), kp.cpu(), vp.cpu(), bt.cpu(), cl.cpu())
+    assert float((o_replay.float().cpu() - o_ref.float()).abs().max()) <= 2e-2
