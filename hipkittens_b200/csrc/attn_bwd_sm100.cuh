@@ -17,10 +17,10 @@
 //                         already in the A-operand position of dV += P^T dO and dK += dS^T Q.
 //   attn_bwd_dq_kernel    one query tile of 128 rows stays in shared memory; the K/V tiles stream past it:
 //                         S = Q K^T, dP = dO V^T, dQ += dS K.
-// Both kernels are persistent (one CTA per SM, 384 threads): warps 0-7 do the element-wise work (two
-// threads per TMEM lane, 64 columns each), warp 8 is the TMA producer, warps 9 and 10 each hold one UMMA
-// issuing thread (one per dependency chain).
-// TMEM is laid out so that a score-shaped accumulator is free for the next tile as soon as the element-wise
+// Both kernels are persistent (one CTA per SM, 640 threads by default): warps 0-15 do the element-wise work
+// (four threads per TMEM lane, 32 columns each), then one warp each for the TMA producer, two UMMA issuing threads
+// (one per dependency chain) and, in the dK/dV kernel, the loader of the per-row statistics.
+// TMEM is laid out so that a score-shaped accumulator is free for the next product as soon as the element-wise
 // warps hold it in registers (its bf16 successor goes elsewhere: see the column maps in the kernels).
 //
 // Any sequence length works (the reference's kernels need a multiple of 256): TMA zero-fills the rows of a partial
@@ -49,7 +49,7 @@ constexpr int kBwdParts = HK_BWD_PARTS;
 static_assert(kBwdParts == 2 || kBwdParts == 4, "2 or 4 threads per TMEM lane");
 constexpr int kBwdCW = 4 * kBwdParts;              // element-wise warps
 constexpr int kBwdPC = 128 / kBwdParts;            // score columns per element-wise thread
-constexpr int kBwdThreads = 32 * (kBwdCW + 4);     // + TMA producer, two UMMA issuers, one idle warp
+constexpr int kBwdThreads = 32 * (kBwdCW + 4);     // + TMA producer, two UMMA issuers, statistics loader (idle in dQ)
 // Register budget: all warps start with kBwdRegsAtLaunch; the element-wise warps then grow by exactly what the
 // other four warps give up (setmaxnreg only moves registers inside the CTA's own allocation: asking for more than
 // was released would block forever): 8 x (208 - 168) = 4 x (168 - 88). With 4 parts (640 threads) every thread keeps
@@ -508,7 +508,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       prefetch_tmap(&tmap_k);
       prefetch_tmap(&tmap_v);
       prefetch_tmap(&tmap_do);
-      uint32_t item_cnt = 0, it = 0;
+      uint32_t item_cnt = 0;
       int qa = 0, rb = 0;
       uint32_t qa_par = 0, rb_par = 0;
       bool ok = true;
@@ -529,7 +529,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           tma_load_4d(sK + ch * kSub, &tmap_k, bars + KV_FULL, ch * 64, w.kvh, w.j * kBlockN, w.b);
           tma_load_4d(sV + ch * kSub, &tmap_v, bars + KV_FULL, ch * 64, w.kvh, w.j * kBlockN, w.b);
         }
-        for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
+        for (int n = 0; n < w.n_iter && ok; ++n) {
           const int head = w.kvh * G + n / w.cnt_i;
           const int i = (CAUSAL ? w.j : 0) + n % w.cnt_i;
           ok = mbar_wait(bars + QA_EMPTY + qa, qa_par ^ 1, abortp, kWaitLimitCycles);
