@@ -319,3 +319,35 @@ def test_full_size_identities_config2(dev):
         diff = (got.float().cpu() - ref).abs()
         assert float(diff.max()) <= 2e-2 * float(ref.abs().max()) + 1e-2 * float(ref.abs().max()), name
         assert float(diff.pow(2).sum().sqrt() / ref.pow(2).sum().sqrt()) <= L2TOL, name
+
+
+def test_full_size_identities_config3_causal(dev):
+    """BASELINE config 3 shape (B4 N8192 H64 H_KV8 D128, causal): the same two size-independent identities over every
+    (batch, kv head) unit, plus the first rows of one unit against the oracle restricted to the keys they can see."""
+    b, n, h, hkv, d = 4, 8192, 64, 8, 128
+    g = h // hkv
+    gen = torch.Generator(device=dev).manual_seed(61)
+    q = torch.randn((b, n, h, d), generator=gen, device=dev).to(torch.bfloat16)
+    k = torch.randn((b, n, hkv, d), generator=gen, device=dev).to(torch.bfloat16)
+    v = torch.randn((b, n, hkv, d), generator=gen, device=dev).to(torch.bfloat16)
+    d_o = torch.randn((b, n, h, d), generator=gen, device=dev).to(torch.bfloat16)
+    o, lse = hk.attn_fwd(q, k, v, causal=True)
+    delta = hk.attn_bwd_prep(o, d_o)
+    dq, dk, dv = hk.attn_bwd(q, k, v, d_o, lse, delta, causal=True)
+    assert _native.device_status(0) == 0
+    for t in (dq, dk, dv):
+        assert not torch.isnan(t.float()).any()
+    qdq = (q.float() * dq.float()).view(b, n, hkv, g * d).sum((1, 3))
+    kdk = (k.float() * dk.float()).sum((1, 3))
+    scale_ref = (q.float() * dq.float()).abs().view(b, n, hkv, g * d).sum((1, 3))
+    assert float(((qdq - kdk).abs() / scale_ref).max()) <= 1e-3
+    dv_sum = dv.float().sum(1)
+    do_sum = d_o.float().view(b, n, hkv, g, d).sum((1, 3))
+    assert float((dv_sum - do_sum).abs().max()) <= 2e-2 * float(do_sum.abs().max())
+    # causality makes the first 256 query rows independent of everything behind them: dq of those rows equals the dq of
+    # the 256-token problem (dk and dv of the first keys also collect from later queries, so only dq is compared)
+    bi, kh, m = 2, 5, 256
+    hs = slice(kh * g, (kh + 1) * g)
+    rq, _, _, _ = attn_bwd_oracle(q[bi:bi + 1, :m, hs].cpu(), k[bi:bi + 1, :m, kh:kh + 1].cpu(),
+                                  v[bi:bi + 1, :m, kh:kh + 1].cpu(), d_o[bi:bi + 1, :m, hs].cpu(), causal=True)
+    assert_grad_parity(dq[bi:bi + 1, :m, hs].cpu(), rq, "dq (first 256 rows)")
