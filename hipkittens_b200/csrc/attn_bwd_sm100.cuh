@@ -288,7 +288,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   uint8_t* sV = bwd_smem + kTile;
   uint8_t* sQ = bwd_smem + 2 * kTile;          // RA stages
   uint8_t* sDO = sQ + RA * kTile;              // RB stages
-  float* sStat = reinterpret_cast<float*>(bwd_smem + SM::kTiles * kTile);  // [2 stages][L 128 | delta 128]
+  float* sStat = reinterpret_cast<float*>(bwd_smem + SM::kTiles * kTile);  // [2 stages][-L log2e 128 | -delta 128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(bwd_smem + SM::kTiles * kTile + SM::kStatBytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + CTRL);
   uint32_t* abort_word = tmem_slot + 1;
@@ -353,7 +353,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const uint32_t tPt = tmem + lane_addr + cY + part * (kBwdPC / 2);        // this thread's packed columns of P^T
     const uint32_t tDSt = tmem + lane_addr + cY + 64 + part * (kBwdPC / 2);  // ... and of dS^T
     const float c = p.scale_log2;
-    constexpr float kNegLog2e = -1.4426950408889634f;
     uint32_t it = 0, acc_cnt = 0;
     bool ok = true;
 #ifdef HK_TRACE
@@ -402,14 +401,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         // ---- p = exp2(s * c - L * log2(e)), kept in fp32 for dS (two columns per packed fp32x2 instruction)
         {
           const uint64_t c2 = pack2(c, c);
-          const uint64_t k2 = pack2(kNegLog2e, kNegLog2e);
 #pragma unroll
           for (int q4 = 0; q4 < kBwdPC / 4; ++q4) {
-            const float4 l4 = *reinterpret_cast<const float4*>(sL + q4 * 4);
+            const float4 l4 = *reinterpret_cast<const float4*>(sL + q4 * 4);  // -L * log2(e) of four query columns
             const uint64_t xa = fma2(pack2(__uint_as_float(su[q4 * 4 + 0]), __uint_as_float(su[q4 * 4 + 1])), c2,
-                                     mul2(pack2(l4.x, l4.y), k2));
+                                     pack2(l4.x, l4.y));
             const uint64_t xb = fma2(pack2(__uint_as_float(su[q4 * 4 + 2]), __uint_as_float(su[q4 * 4 + 3])), c2,
-                                     mul2(pack2(l4.z, l4.w), k2));
+                                     pack2(l4.z, l4.w));
             float x0, x1, x2, x3;
             unpack2(xa, x0, x1);
             unpack2(xb, x2, x3);
@@ -464,12 +462,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           uint32_t pk[kBwdPC / 2];
 #pragma unroll
           for (int q4 = 0; q4 < kBwdPC / 4; ++q4) {
-            const float4 d4 = *reinterpret_cast<const float4*>(sDl + q4 * 4);
-            const uint64_t m1 = pack2(-1.0f, -1.0f);
-            const uint64_t ta = fma2(pack2(d4.x, d4.y), m1,
-                                     pack2(__uint_as_float(du[q4 * 4 + 0]), __uint_as_float(du[q4 * 4 + 1])));
-            const uint64_t tb = fma2(pack2(d4.z, d4.w), m1,
-                                     pack2(__uint_as_float(du[q4 * 4 + 2]), __uint_as_float(du[q4 * 4 + 3])));
+            const float4 d4 = *reinterpret_cast<const float4*>(sDl + q4 * 4);  // -delta of four query columns
+            const uint64_t ta = add2(pack2(__uint_as_float(du[q4 * 4 + 0]), __uint_as_float(du[q4 * 4 + 1])),
+                                     pack2(d4.x, d4.y));
+            const uint64_t tb = add2(pack2(__uint_as_float(du[q4 * 4 + 2]), __uint_as_float(du[q4 * 4 + 3])),
+                                     pack2(d4.z, d4.w));
             float ds0, ds1, ds2, ds3;
             unpack2(mul2(pack2(__uint_as_float(su[q4 * 4 + 0]), __uint_as_float(su[q4 * 4 + 1])), ta), ds0, ds1);
             unpack2(mul2(pack2(__uint_as_float(su[q4 * 4 + 2]), __uint_as_float(su[q4 * 4 + 3])), tb), ds2, ds3);
@@ -696,8 +693,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         for (int t = 0; t < kBlockM / 32; ++t) {
           const int pos = i * kBlockM + t * 32 + lane;
           const bool in = pos < p.N;
-          lv[t] = in ? __ldg(p.lse + base + pos) : 0.f;
-          dv_[t] = in ? __ldg(p.delta + base + pos) : 0.f;
+          // stored ready for use: -L * log2(e) is the addend of the exponent, -delta the addend of dP
+          lv[t] = in ? __ldg(p.lse + base + pos) * -1.4426950408889634f : 0.f;
+          dv_[t] = in ? -__ldg(p.delta + base + pos) : 0.f;
         }
       };
       for (int round = 0; ok; ++round) {
