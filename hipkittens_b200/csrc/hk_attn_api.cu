@@ -198,6 +198,7 @@ template <int D, bool CAUSAL>
 int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                hk::BwdParams p, int B, int N, int H, int H_KV, int sm_count, cudaStream_t stream) {
   const int nb = (N + hk::kBlockM - 1) / hk::kBlockM;
+  if (static_cast<long long>(B) * H * nb > 0x3fffffffll) return HK_EINVAL;  // work items are indexed with int
   p.n_items = B * H_KV * nb;
   int grid = p.n_items < sm_count ? p.n_items : sm_count;
 #ifdef HK_TRACE
@@ -286,6 +287,7 @@ int hk_attn_fwd_varlen(const void* q, const void* k, const void* v, void* o, flo
     long long u = (static_cast<long long>(HK_GROUP_MB) << 20) / kv_bytes;
     p.group_units = int(u < 1 ? 1 : (u > B * H_KV ? B * H_KV : u));
   }
+  if (static_cast<long long>(B) * H * nqb > 0x3fffffffll) return HK_EINVAL;  // work items are indexed with int
   p.n_items = p.pair_heads ? B * H_KV * (G / 2) * nqb : B * H_KV * G * ((nqb + 1) / 2);
   p.scale = softmax_scale > 0.f ? softmax_scale : 1.0f / std::sqrt(float(D));
   p.scale_log2 = p.scale * 1.4426950408889634f;
