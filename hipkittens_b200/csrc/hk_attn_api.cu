@@ -454,7 +454,7 @@ int hk_attn_paged_decode(const void* q, const void* k_pages, const void* v_pages
   if (D != 128 || page_size != 16) return HK_EUNSUPPORTED;
   if (H % H_KV != 0) return HK_EINVAL;
   const int G = H / H_KV;
-  if (G != 1 && G != 2 && G != 4 && G != 8) return HK_EUNSUPPORTED;
+  if (G < 1 || G > 8) return HK_EUNSUPPORTED;  // the heads of a group sit in the 8 usable rows of one MMA tile
   if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(o)) return HK_EINVAL;
   const size_t need = hk::decode_workspace_bytes(S, H, D, max_pages_per_seq, page_size);
   if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)) return HK_EWORKSPACE;
@@ -612,7 +612,7 @@ extern "C" int hk_attn_paged_decode_static(const void* q, const void* k_pages, c
   if (D != 128 || page_size != 16) return HK_EUNSUPPORTED;
   if (H % H_KV != 0) return HK_EINVAL;
   const int G = H / H_KV;
-  if (G != 1 && G != 2 && G != 4 && G != 8) return HK_EUNSUPPORTED;
+  if (G < 1 || G > 8) return HK_EUNSUPPORTED;  // the heads of a group sit in the 8 usable rows of one MMA tile
   if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(o)) return HK_EINVAL;
   const size_t need = hk::decode_workspace_bytes(S, H, D, max_pages_per_seq, page_size);
   if (need == 0 || need > HK_DECODE_STATIC_SCRATCH_BYTES) {

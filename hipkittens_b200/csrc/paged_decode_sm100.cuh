@@ -355,7 +355,7 @@ inline int prepare_decode_kernels(char* err, size_t err_len) {
     snprintf(err, err_len, "decode kernel attribute: %s", cudaGetErrorString(e));                       \
     return -3;                                                                                          \
   }
-  HK_PREP(1) HK_PREP(2) HK_PREP(4) HK_PREP(8)
+  HK_PREP(1) HK_PREP(2) HK_PREP(3) HK_PREP(4) HK_PREP(5) HK_PREP(6) HK_PREP(7) HK_PREP(8)
 #undef HK_PREP
   return 0;
 }
@@ -367,10 +367,11 @@ inline cudaError_t launch_paged_decode(DecodeParams p, int sm_count, cudaStream_
   const dim3 grid(splits, p.H_KV, p.S);
   const int G = p.H / p.H_KV;
   switch (G) {
-    case 1: paged_decode_split_kernel<1><<<grid, kDecodeThreads, kDecodeSmemBytes, stream>>>(p); break;
-    case 2: paged_decode_split_kernel<2><<<grid, kDecodeThreads, kDecodeSmemBytes, stream>>>(p); break;
-    case 4: paged_decode_split_kernel<4><<<grid, kDecodeThreads, kDecodeSmemBytes, stream>>>(p); break;
-    default: paged_decode_split_kernel<8><<<grid, kDecodeThreads, kDecodeSmemBytes, stream>>>(p); break;
+#define HK_CASE(g) \
+  case g: paged_decode_split_kernel<g><<<grid, kDecodeThreads, kDecodeSmemBytes, stream>>>(p); break;
+    HK_CASE(1) HK_CASE(2) HK_CASE(3) HK_CASE(4) HK_CASE(5) HK_CASE(6) HK_CASE(7) HK_CASE(8)
+#undef HK_CASE
+    default: return cudaErrorInvalidValue;
   }
   *launched += 1;
   cudaError_t e = cudaGetLastError();

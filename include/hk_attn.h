@@ -63,7 +63,7 @@ int hk_attn_fwd_varlen(const void* q, const void* k, const void* v, void* o, flo
  *   block_table : int32 [S, max_pages_per_seq]; token j of sequence s is row j % page_size of page
  *                 block_table[s, j / page_size]; entries must lie in [0, num_pages)
  *   ctx_lens    : int32 [S], 1 <= ctx_lens[s] <= max_pages_per_seq * page_size
- *   D = 128, page_size = 16, H / H_KV in {1, 2, 4, 8}.
+ *   D = 128, page_size = 16, H / H_KV from 1 to 8.
  *   workspace   : device scratch of at least hk_attn_paged_decode_workspace_bytes(...) bytes, 256-byte
  *                 aligned; holds the per-split partial results between the two kernels. */
 size_t hk_attn_paged_decode_workspace_bytes(int S, int H, int D, int max_pages_per_seq, int page_size);

@@ -77,7 +77,7 @@ def test_decode_rejects_bad_arguments_before_cuda(native_built):
     assert call(q=None) == _native.HK_EINVAL
     assert call(D=64) == _native.HK_EUNSUPPORTED
     assert call(page=32) == _native.HK_EUNSUPPORTED
-    assert call(H=3, HKV=1) == _native.HK_EUNSUPPORTED  # group size 3
+    assert call(H=9, HKV=1) == _native.HK_EUNSUPPORTED  # group size 9: more heads than rows of the MMA tile
     assert call(H=8, HKV=3) == _native.HK_EINVAL
     assert call(ws=None) == _native.HK_EWORKSPACE
     assert call(ws_bytes=16) == _native.HK_EWORKSPACE

@@ -40,6 +40,11 @@ CASES = [
     (5, 4, 1, 64, 1, 16, 4),          # everything inside the first page
     (2, 64, 8, 1200, 8000, 8192, 5),  # the configuration's head counts at maximum context
     (10, 16, 8, 5300, 6000, 8192, 6),  # enough CTAs for the launcher to pick 1024-token chunks
+    # group sizes that are not powers of two (28 / 4 = 7, 40 / 8 = 5, 12 / 2 = 6, 3 / 1 = 3 query heads per kv head)
+    (3, 28, 4, 600, 50, 2100, 7),
+    (2, 40, 8, 700, 900, 3000, 8),
+    (4, 12, 2, 300, 1, 700, 9),
+    (2, 3, 1, 200, 200, 1300, 10),
 ]
 
 
