@@ -181,6 +181,21 @@ __global__ void __launch_bounds__(256) attn_dq_shuffle_kernel(const uint4* __res
 // then the (L, delta) stages, then the mbarriers and two control words.
 
 // ------------------------------------------------------------------------------------ shared helpers
+// The two UMMA-issuing roles run either as one thread (lane 0 of their warp) or as a whole warp that keeps
+// its control flow and descriptor arithmetic warp-uniform and elects one lane per group of tcgen05 instructions
+// (measured 1.5 to 4 % faster on every backward shape tried; the same change to the forward kernel's single
+// issuer measured equal at D = 128 and 8 % slower at D = 64, so the forward kernel keeps its one thread).
+#ifndef HK_BWD_WARP_ISSUE
+#define HK_BWD_WARP_ISSUE 1
+#endif
+constexpr bool kBwdWarpIssue = HK_BWD_WARP_ISSUE != 0;
+__device__ __forceinline__ bool iss_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                         uint64_t limit_cycles) {
+  bool ok = ptx::mbar_wait(bar, parity, abort_flag, limit_cycles);
+  if (kBwdWarpIssue) ok = __all_sync(0xffffffffu, ok);
+  return ok;
+}
+__device__ __forceinline__ bool iss_elect() { return !kBwdWarpIssue || ptx::elect_one(); }
 // S-shaped product with both operands in shared memory, K-major, 128 B swizzle: d[128 x 128] = a * b^T
 // over D. `a_lo` / `b_lo` are descriptor low words of the two 128 x D tiles.
 template <int D>
@@ -341,7 +356,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   // as the element-wise warps hold it in registers; Y [128,256) holds the two bf16 operands, P^T in [128,192) and dS^T
   // in [192,256), free again when dV(n) and dK(n) have consumed them; dK [256,256+D); dV [256+D,256+2D). Nothing
   // fp32 aliases anything bf16, so no product has to wait behind another one's operands.
+  // With D = 64 the accumulators leave 128 columns over: dP^T then gets a region of its own, [384,512), so that
+  // S^T(n+1) only waits for S^T(n) to be read and dP^T(n+1) for dP^T(n), and both products are in flight long before
+  // the element-wise warps need them (kSplitX).
+  constexpr bool kSplitX = (D == 64);
   constexpr uint32_t cX = 0, cY = 128, cDK = 256, cDV = 256 + D;
+  constexpr uint32_t cXdP = kSplitX ? 384 : cX;
 
   if (warp < kBwdCW) {
     // ------------------------------------------------------------------ element-wise warps
@@ -350,6 +370,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const int row = (warp & 3) * 32 + lane;            // key row inside the block == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tX = tmem + lane_addr + cX + part * kBwdPC;
+    const uint32_t tXdP = tmem + lane_addr + cXdP + part * kBwdPC;
     const uint32_t tPt = tmem + lane_addr + cY + part * (kBwdPC / 2);        // this thread's packed columns of P^T
     const uint32_t tDSt = tmem + lane_addr + cY + 64 + part * (kBwdPC / 2);  // ... and of dS^T
     const float c = p.scale_log2;
@@ -435,7 +456,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         tc_fence_after();
         HK_STAMP(0, 3);
         uint32_t du[kBwdPC];
-        bwd_ld_part(tX, du);
+        bwd_ld_part(tXdP, du);
         tmem_wait_ld();
         tc_fence_before();
         __syncwarp();
@@ -551,7 +572,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           }
         }
       }
-    } else if (warp == kBwdCW + 1 && lane == 0) {
+    } else if (warp == kBwdCW + 1 && (kBwdWarpIssue || lane == 0)) {
       // ---------------- UMMA issuer A: the two score-shaped products, S^T = K Q^T and dP^T = V dO^T, which take
       // turns in X: each is issued as soon as the element-wise warps have read its predecessor.
       // Two threads issue because a thread that issues returns only a few MMAs ahead of the pipe: with one issuer
@@ -566,7 +587,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       uint32_t qa_par = 0, rb_par = 0;
       bool ok = true;
 #ifdef HK_TRACE
-      const bool trace_on = p.trace != nullptr;
+      const bool trace_on = p.trace != nullptr && lane == 0;
       int trace_n = 0;
 #endif
       for (int round = 0; ok; ++round) {
@@ -577,31 +598,37 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
         const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
         if (w.n_iter == 0) continue;  // key block wholly beyond this batch element's length: nothing to do
-        ok = mbar_wait(bars + KV_FULL, item_cnt & 1, abortp, kWaitLimitCycles);
+        ok = iss_wait(bars + KV_FULL, item_cnt & 1, abortp, kWaitLimitCycles);
         if (!ok) break;
         ++item_cnt;
         for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
-          // S^T(n): dP^T of the previous pair has been read out of X (first pair ever: passes at once)
-          ok = mbar_wait(bars + DP_FREE, (it & 1) ^ 1, abortp, kWaitLimitCycles) &&
-               mbar_wait(bars + QA_FULL + qa, qa_par, abortp, kWaitLimitCycles);
+          // S^T(n): dP^T of the previous pair has been read out of X (first pair ever: passes at once); with a
+          // region of its own, S^T(n) only waits for S^T(n-1) to be read
+          ok = iss_wait(bars + (kSplitX ? S_FREE : DP_FREE), (it & 1) ^ 1, abortp, kWaitLimitCycles) &&
+               iss_wait(bars + QA_FULL + qa, qa_par, abortp, kWaitLimitCycles);
           if (!ok) break;
           tc_fence_after();
           HK_STAMP(2, 12);
-          bwd_issue_ss<D>(tmem + cX, k_lo, q_lo0 + qa * tile16);
-          umma_commit(bars + ST_FULL);
+          if (iss_elect()) {
+            bwd_issue_ss<D>(tmem + cX, k_lo, q_lo0 + qa * tile16);
+            umma_commit(bars + ST_FULL);
+          }
           HK_STAMP(2, 13);
           if (++qa == RA) {
             qa = 0;
             qa_par ^= 1;
           }
-          // dP^T(n): S^T(n) has been read out of X
-          ok = mbar_wait(bars + S_FREE, it & 1, abortp, kWaitLimitCycles) &&
-               mbar_wait(bars + RB_FULL + rb, rb_par, abortp, kWaitLimitCycles);
+          // dP^T(n): S^T(n) has been read out of X (own region: dP^T(n-1) has been read)
+          ok = iss_wait(bars + (kSplitX ? DP_FREE : S_FREE), kSplitX ? ((it & 1) ^ 1) : (it & 1), abortp,
+                        kWaitLimitCycles) &&
+               iss_wait(bars + RB_FULL + rb, rb_par, abortp, kWaitLimitCycles);
           if (!ok) break;
           tc_fence_after();
-          bwd_issue_ss<D>(tmem + cX, v_lo, do_lo0 + rb * tile16);
-          umma_commit(bars + DP_FULL);
-          umma_commit(bars + RB_EMPTY + rb);  // first of two arrivals (issuer B: after dV of this stage)
+          if (iss_elect()) {
+            bwd_issue_ss<D>(tmem + cXdP, v_lo, do_lo0 + rb * tile16);
+            umma_commit(bars + DP_FULL);
+            umma_commit(bars + RB_EMPTY + rb);  // first of two arrivals (issuer B: after dV of this stage)
+          }
           HK_STAMP(2, 17);
           if (++rb == RB) {
             rb = 0;
@@ -609,9 +636,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           }
         }
         if (!ok) break;
-        umma_commit(bars + KV_EMPTY);
+        if (iss_elect()) umma_commit(bars + KV_EMPTY);
       }
-    } else if (warp == kBwdCW + 2 && lane == 0) {
+    } else if (warp == kBwdCW + 2 && (kBwdWarpIssue || lane == 0)) {
       // ---------------- UMMA issuer B: the two gradient-shaped products, dV += P^T dO and dK += dS^T Q
       constexpr uint32_t tile16 = kTile >> 4;
       constexpr uint32_t idesc = make_idesc_bf16(kBlockM, D, true);
@@ -623,7 +650,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       uint32_t qa_par = 0, rb_par = 0;
       bool ok = true;
 #ifdef HK_TRACE
-      const bool trace_on = p.trace != nullptr;
+      const bool trace_on = p.trace != nullptr && lane == 0;
       int trace_n = 0;
 #endif
       for (int round = 0; ok; ++round) {
@@ -635,37 +662,37 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
         if (w.n_iter == 0) continue;  // key block wholly beyond this batch element's length: nothing to do
         for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
-          ok = mbar_wait(bars + P_FULL, it & 1, abortp, kWaitLimitCycles) &&
-               mbar_wait(bars + RB_FULL + rb, rb_par, abortp, kWaitLimitCycles);
+          ok = iss_wait(bars + P_FULL, it & 1, abortp, kWaitLimitCycles) &&
+               iss_wait(bars + RB_FULL + rb, rb_par, abortp, kWaitLimitCycles);
           if (!ok) break;
           tc_fence_after();
           HK_STAMP(3, 10);
-          {
+          if (iss_elect()) {
             const uint32_t b_lo = do_mn0 + rb * tile16;
 #pragma unroll
             for (int k = 0; k < kBlockN / 16; ++k)
               umma_ts_lohi(tmem + cDV, tmem + cY + k * 8, b_lo + k * 128, desc_hi, idesc, (n > 0 || k > 0) ? 1u : 0u);
+            umma_commit(bars + RB_EMPTY + rb);  // second of two arrivals
           }
-          umma_commit(bars + RB_EMPTY + rb);  // second of two arrivals
           HK_STAMP(3, 11);
           if (++rb == RB) {
             rb = 0;
             rb_par ^= 1;
           }
-          ok = mbar_wait(bars + DS_FULL, it & 1, abortp, kWaitLimitCycles) &&
-               mbar_wait(bars + QA_FULL + qa, qa_par, abortp, kWaitLimitCycles);
+          ok = iss_wait(bars + DS_FULL, it & 1, abortp, kWaitLimitCycles) &&
+               iss_wait(bars + QA_FULL + qa, qa_par, abortp, kWaitLimitCycles);
           if (!ok) break;
           tc_fence_after();
           HK_STAMP(3, 14);
-          {
+          if (iss_elect()) {
             const uint32_t b_lo = q_mn0 + qa * tile16;
 #pragma unroll
             for (int k = 0; k < kBlockN / 16; ++k)
               umma_ts_lohi(tmem + cDK, tmem + cY + 64 + k * 8, b_lo + k * 128, desc_hi, idesc, (n > 0 || k > 0) ? 1u : 0u);
+            // S^T of this stage (issuer A) completed before dS^T could be computed, so this one arrival frees Q
+            umma_commit(bars + QA_EMPTY + qa);
+            umma_commit(bars + Y_FREE);
           }
-          // S^T of this stage (issuer A) completed before dS^T could be computed, so this one arrival frees Q
-          umma_commit(bars + QA_EMPTY + qa);
-          umma_commit(bars + Y_FREE);
           HK_STAMP(3, 15);
           if (++qa == RA) {
             qa = 0;
@@ -673,7 +700,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           }
         }
         if (!ok) break;
-        umma_commit(bars + ACC_FULL);
+        if (iss_elect()) umma_commit(bars + ACC_FULL);
       }
     } else if (warp == kBwdCW + 3) {
       // ---------------- statistics loader: L and delta of each query tile -> shared memory (indexed by column in
@@ -1009,7 +1036,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           }
         }
       }
-    } else if (warp == kBwdCW + 1 && lane == 0) {
+    } else if (warp == kBwdCW + 1 && (kBwdWarpIssue || lane == 0)) {
       // ---------------- UMMA issuer A: S = Q K^T, as soon as the previous S has been read
       // Two issuing threads, as in the dK/dV kernel: this one runs ahead with the S products, issuer B follows
       // with dP (as soon as the previous dP has been read) and dQ += dS K.
@@ -1021,7 +1048,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       uint32_t ks_par = 0;
       bool ok = true;
 #ifdef HK_TRACE
-      const bool trace_on = p.trace != nullptr;
+      const bool trace_on = p.trace != nullptr && lane == 0;
       int trace_n = 0;
 #endif
       for (int round = 0; ok; ++round) {
@@ -1031,17 +1058,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           continue;
         }
         const DqItem w = decode_dq_item<CAUSAL>(p, idx);
-        ok = mbar_wait(bars + QDO_FULL, item_cnt & 1, abortp, kWaitLimitCycles);
+        ok = iss_wait(bars + QDO_FULL, item_cnt & 1, abortp, kWaitLimitCycles);
         if (!ok) break;
         ++item_cnt;
         for (int n = 0; n < w.n_iter && ok; ++n, ++sf_cnt) {
-          ok = mbar_wait(bars + S_FREE, (sf_cnt & 1) ^ 1, abortp, kWaitLimitCycles) &&
-               mbar_wait(bars + KA_FULL + ks, ks_par, abortp, kWaitLimitCycles);
+          ok = iss_wait(bars + S_FREE, (sf_cnt & 1) ^ 1, abortp, kWaitLimitCycles) &&
+               iss_wait(bars + KA_FULL + ks, ks_par, abortp, kWaitLimitCycles);
           if (!ok) break;
           tc_fence_after();
           HK_STAMP(2, 12);
-          bwd_issue_ss<D>(tmem + cS, q_lo, k_lo0 + ks * tile16);
-          umma_commit(bars + S_FULL);
+          if (iss_elect()) {
+            bwd_issue_ss<D>(tmem + cS, q_lo, k_lo0 + ks * tile16);
+            umma_commit(bars + S_FULL);
+          }
           HK_STAMP(2, 13);
           if (++ks == RA) {
             ks = 0;
@@ -1049,9 +1078,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           }
         }
         if (!ok) break;
-        umma_commit(bars + QDO_EMPTY);  // Q has fed its last product (issuer B arrives for dO)
+        if (iss_elect()) umma_commit(bars + QDO_EMPTY);  // Q has fed its last product (issuer B arrives for dO)
       }
-    } else if (warp == kBwdCW + 2 && lane == 0) {
+    } else if (warp == kBwdCW + 2 && (kBwdWarpIssue || lane == 0)) {
       // ---------------- UMMA issuer B: dP = dO V^T, dQ += dS K
       constexpr uint32_t tile16 = kTile >> 4;
       const uint32_t do_lo = smem_desc_lo(smem_u32(sDO), 16);
@@ -1062,18 +1091,20 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       uint32_t kq_par = 0, vb_par = 0;
       bool ok = true;
 #ifdef HK_TRACE
-      const bool trace_on = p.trace != nullptr;
+      const bool trace_on = p.trace != nullptr && lane == 0;
       int trace_n = 0;
 #endif
       auto issue_dp = [&]() -> bool {
         // the previous dP has been read (first dP ever: passes at once)
-        if (!mbar_wait(bars + DP_FREE, (dpf_cnt & 1) ^ 1, abortp, kWaitLimitCycles)) return false;
-        if (!mbar_wait(bars + VB_FULL + vb, vb_par, abortp, kWaitLimitCycles)) return false;
+        if (!iss_wait(bars + DP_FREE, (dpf_cnt & 1) ^ 1, abortp, kWaitLimitCycles)) return false;
+        if (!iss_wait(bars + VB_FULL + vb, vb_par, abortp, kWaitLimitCycles)) return false;
         ++dpf_cnt;
         tc_fence_after();
-        bwd_issue_ss<D>(tmem + cDP, do_lo, v_lo0 + vb * tile16);
-        umma_commit(bars + DP_FULL);
-        umma_commit(bars + VB_EMPTY + vb);
+        if (iss_elect()) {
+          bwd_issue_ss<D>(tmem + cDP, do_lo, v_lo0 + vb * tile16);
+          umma_commit(bars + DP_FULL);
+          umma_commit(bars + VB_EMPTY + vb);
+        }
         if (++vb == RB) {
           vb = 0;
           vb_par ^= 1;
@@ -1087,35 +1118,35 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           continue;
         }
         const DqItem w = decode_dq_item<CAUSAL>(p, idx);
-        ok = mbar_wait(bars + QDO_FULL, item_cnt & 1, abortp, kWaitLimitCycles);
+        ok = iss_wait(bars + QDO_FULL, item_cnt & 1, abortp, kWaitLimitCycles);
         if (!ok) break;
         ++item_cnt;
         ok = issue_dp();
         if (!ok) break;
-        if (w.n_iter == 1) umma_commit(bars + QDO_EMPTY);  // dO has fed its last product
+        if (w.n_iter == 1 && iss_elect()) umma_commit(bars + QDO_EMPTY);  // dO has fed its last product
         for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
           if (n + 1 < w.n_iter) {
             ok = issue_dp();
             if (!ok) break;
-            if (n + 2 == w.n_iter) umma_commit(bars + QDO_EMPTY);
+            if (n + 2 == w.n_iter && iss_elect()) umma_commit(bars + QDO_EMPTY);
             HK_STAMP(3, 12);
           }
-          ok = mbar_wait(bars + DS_FULL, it & 1, abortp, kWaitLimitCycles) &&
-               mbar_wait(bars + KA_FULL + kq, kq_par, abortp, kWaitLimitCycles);
+          ok = iss_wait(bars + DS_FULL, it & 1, abortp, kWaitLimitCycles) &&
+               iss_wait(bars + KA_FULL + kq, kq_par, abortp, kWaitLimitCycles);
           if (!ok) break;
           tc_fence_after();
           HK_STAMP(3, 10);
-          {
+          if (iss_elect()) {
             constexpr uint32_t idesc = make_idesc_bf16(kBlockM, D, true);
             constexpr uint32_t desc_hi = smem_desc_hi(1024);
             const uint32_t b_lo = k_mn0 + kq * tile16;
 #pragma unroll
             for (int k = 0; k < kBlockN / 16; ++k)
               umma_ts_lohi(tmem + cDQ, tmem + cDS + k * 8, b_lo + k * 128, desc_hi, idesc, (n > 0 || k > 0) ? 1u : 0u);
+            // S of this tile (issuer A) completed before dS could be computed, so this one arrival frees the K tile
+            umma_commit(bars + KA_EMPTY + kq);
+            umma_commit(bars + DS_FREE);
           }
-          // S of this tile (issuer A) completed before dS could be computed, so this one arrival frees the K tile
-          umma_commit(bars + KA_EMPTY + kq);
-          umma_commit(bars + DS_FREE);
           HK_STAMP(3, 11);
           if (++kq == RA) {
             kq = 0;
@@ -1123,7 +1154,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           }
         }
         if (!ok) break;
-        umma_commit(bars + DQ_FULL);
+        if (iss_elect()) umma_commit(bars + DQ_FULL);
       }
     }
   }
