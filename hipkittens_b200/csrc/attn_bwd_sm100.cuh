@@ -377,7 +377,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     uint32_t it = 0, acc_cnt = 0;
     bool ok = true;
 #ifdef HK_TRACE
-    const bool trace_on = (warp == 0) && lane == 0 && p.trace != nullptr;
+    const bool trace_on = (warp == 0 || warp == kBwdCW - 1) && lane == 0 && p.trace != nullptr;
+    const int trole = warp == 0 ? 0 : 1;  // first and last element-wise warp: their distance is the skew between warps
     int trace_n = 0;
 #endif
     for (int round = 0; ok; ++round) {
@@ -388,6 +389,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       }
       const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
       const bool pad_row = w.j * kBlockN + row >= w.kv_len;  // this key is padding (or lies beyond N)
+      const bool pad_block = (w.j + 1) * kBlockN > w.kv_len;  // uniform over the CTA: only such a block has padded keys
       if (w.n_iter == 0) {
         // the whole key block is padding: its gradients are zero and no product was issued for it
         if (w.j * kBlockN + row < p.N) {
@@ -402,7 +404,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         continue;
       }
       for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
-        HK_STAMP(0, 0);
+        HK_STAMP(trole, 0);
         const bool diag = CAUSAL && (n % w.cnt_i == 0);  // the query tile at the key block's own position
         const float* sL = sStat + (it & 1) * 256 + part * kBwdPC;
         const float* sDl = sL + 128;
@@ -412,7 +414,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        HK_STAMP(0, 1);
+        HK_STAMP(trole, 1);
         uint32_t su[kBwdPC];
         bwd_ld_part(tX, su);
         tmem_wait_ld();
@@ -442,19 +444,19 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
             for (int col = 0; col < kBwdPC; ++col) su[col] = (part * kBwdPC + col) < row ? 0u : su[col];
           }
-          if (pad_row) {
+          if (pad_block) {
             // a padded key is seen by nobody: P^T and dS^T rows are zero, so are its dK and dV rows
 #pragma unroll
-            for (int col = 0; col < kBwdPC; ++col) su[col] = 0u;
+            for (int col = 0; col < kBwdPC; ++col) su[col] = pad_row ? 0u : su[col];
           }
         }
-        HK_STAMP(0, 2);
+        HK_STAMP(trole, 2);
         // ---- dP^T into registers; X is free for S^T of the next pair
         ok = mbar_wait(bars + DP_FULL, it & 1, abortp, kWaitLimitCycles);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        HK_STAMP(0, 3);
+        HK_STAMP(trole, 3);
         uint32_t du[kBwdPC];
         bwd_ld_part(tXdP, du);
         tmem_wait_ld();
@@ -477,7 +479,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + P_FULL);
-        HK_STAMP(0, 4);
+        HK_STAMP(trole, 4);
         // ---- dS^T = P^T * (dP^T - delta)
         {
           uint32_t pk[kBwdPC / 2];
@@ -503,7 +505,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           mbar_arrive(bars + DS_FULL);
           mbar_arrive(bars + STAT_EMPTY + (it & 1));
         }
-        HK_STAMP(0, 5);
+        HK_STAMP(trole, 5);
       }
       if (!ok) break;
       // ---- epilogue: dK = scale * acc, dV = acc
