@@ -377,7 +377,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     uint32_t it = 0, acc_cnt = 0;
     bool ok = true;
 #ifdef HK_TRACE
-    const bool trace_on = (warp == 0 || warp == kBwdCW - 1) && lane == 0 && p.trace != nullptr;
+#ifndef HK_TRACE_WARP
+#define HK_TRACE_WARP (kBwdCW - 1)
+#endif
+    const bool trace_on = (warp == 0 || warp == HK_TRACE_WARP) && lane == 0 && p.trace != nullptr;
     const int trole = warp == 0 ? 0 : 1;  // first and last element-wise warp: their distance is the skew between warps
     int trace_n = 0;
 #endif
