@@ -18,14 +18,13 @@
 //   attn_bwd_dq_kernel    one query tile of 128 rows stays in shared memory; the K/V tiles stream past it:
 //                         S = Q K^T, dP = dO V^T, dQ += dS K.
 // Both kernels are persistent (one CTA per SM, 640 threads by default): warps 0-15 do the element-wise work
-// (four threads per TMEM lane, 32 columns each), then one warp each for the TMA producer, two UMMA issuing threads
-// (one per dependency chain) and, in the dK/dV kernel, the loader of the per-row statistics.
+// (four threads per TMEM lane, 32 columns each), then one warp each for the TMA producer, the two UMMA-issuing
+// roles and, in the dK/dV kernel, the loader of the per-row statistics.
 // TMEM is laid out so that a score-shaped accumulator is free for the next product as soon as the element-wise
 // warps hold it in registers (its bf16 successor goes elsewhere: see the column maps in the kernels).
 //
 // Any sequence length works (the reference's kernels need a multiple of 256): TMA zero-fills the rows of a partial
 // last tile, their statistics are read as zero, and their gradient rows are not stored.
-#pragma once
 
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -35,54 +34,15 @@
 #include "attn_fwd_sm100.cuh"
 #include "sm100_ptx.cuh"
 
+// This header may be included more than once: the part that does not depend on the thread layout is compiled
+// once; the main kernels and their helpers are compiled into namespace hk::HK_BWD_NS with HK_BWD_PARTS threads per
+// TMEM lane, so that a translation unit can hold two layouts (the 8-warp one serves the causal instantiations,
+// where it measured 3 to 7 % faster; the 16-warp one the others).
+#ifndef HK_ATTN_BWD_SHARED_PART
+#define HK_ATTN_BWD_SHARED_PART
 namespace hk {
 
-// Element-wise warps: kBwdParts threads share one TMEM lane (one score row), each owning 128 / kBwdParts columns.
-// 4 parts = 16 element-wise warps (4 per scheduler) in a 640-thread CTA without register re-allocation; 2 parts =
-// 8 warps in a 384-thread CTA that re-balances registers like the forward kernel. Both were measured at the same
-// throughput (the kernels run against the power cap, not against their cycle count); 4 is the default because it
-// needs no setmaxnreg bookkeeping.
-#ifndef HK_BWD_PARTS
-#define HK_BWD_PARTS 4
-#endif
-constexpr int kBwdParts = HK_BWD_PARTS;
-static_assert(kBwdParts == 2 || kBwdParts == 4, "2 or 4 threads per TMEM lane");
-constexpr int kBwdCW = 4 * kBwdParts;              // element-wise warps
-constexpr int kBwdPC = 128 / kBwdParts;            // score columns per element-wise thread
-constexpr int kBwdThreads = 32 * (kBwdCW + 4);     // + TMA producer, two UMMA issuers, statistics loader (idle in dQ)
-// Register budget: all warps start with kBwdRegsAtLaunch; the element-wise warps then grow by exactly what the
-// other four warps give up (setmaxnreg only moves registers inside the CTA's own allocation: asking for more than
-// was released would block forever): 8 x (208 - 168) = 4 x (168 - 88). With 4 parts (640 threads) every thread keeps
-// its 96 registers: the element-wise code fits, and no re-allocation is done.
-constexpr int kBwdRegsAtLaunch = kBwdParts == 2 ? 168 : 96;
-constexpr int kBwdRegsGrown = kBwdParts == 2 ? 208 : 96;
-constexpr int kBwdRegsShrunk = kBwdParts == 2 ? 88 : 96;
-static_assert(kBwdCW * (kBwdRegsGrown - kBwdRegsAtLaunch) == 4 * (kBwdRegsAtLaunch - kBwdRegsShrunk),
-              "registers taken by the element-wise warps must equal the registers released by the other warps");
-
 enum : int { kStatusSmemAlign = 3 };  // dynamic shared memory did not start on a 1024-byte boundary
-
-// kBwdPC fp32 columns of this thread's lane -> registers / kBwdPC/2 packed bf16 columns -> TMEM
-__device__ __forceinline__ void bwd_ld_part(uint32_t taddr, uint32_t* r) {
-#pragma unroll
-  for (int c = 0; c < kBwdPC / 32; ++c) ptx::tmem_ld32(taddr + c * 32, r + c * 32);
-}
-__device__ __forceinline__ void bwd_st_packed(uint32_t taddr, const uint32_t* r) {
-  if constexpr (kBwdPC == 64) ptx::tmem_st32(taddr, r);
-  else ptx::tmem_st16(taddr, r);
-}
-__device__ __forceinline__ void bwd_grow_registers() {
-  if constexpr (kBwdParts == 2) {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
-    static_assert(kBwdParts != 2 || kBwdRegsGrown == 208, "keep the immediate above in step");
-  }
-}
-__device__ __forceinline__ void bwd_shrink_registers() {
-  if constexpr (kBwdParts == 2) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
-    static_assert(kBwdParts != 2 || kBwdRegsShrunk == 88, "keep the immediate above in step");
-  }
-}
 
 struct BwdParams {
   const float* lse;     // [B,H,1,N] from the forward pass (natural log)
@@ -179,6 +139,60 @@ __global__ void __launch_bounds__(256) attn_dq_shuffle_kernel(const uint4* __res
 
 // Dynamic shared memory of both main kernels: tiles first (1024-byte aligned for the 128-byte swizzle),
 // then the (L, delta) stages, then the mbarriers and two control words.
+}  // namespace hk
+#endif  // HK_ATTN_BWD_SHARED_PART
+
+#ifndef HK_BWD_NS
+#define HK_BWD_NS bwd_layout
+#endif
+namespace hk {
+namespace HK_BWD_NS {
+
+
+// Element-wise warps: kBwdParts threads share one TMEM lane (one score row), each owning 128 / kBwdParts columns.
+// 4 parts = 16 element-wise warps (4 per scheduler) in a 640-thread CTA without register re-allocation; 2 parts =
+// 8 warps in a 384-thread CTA that re-balances registers like the forward kernel. Sixteen warps measured 1 to 2 %
+// faster on the non-causal shapes, eight 3 to 7 % faster on the causal ones (every barrier the issuers wait for
+// collects half as many arrivals); 4 is the default when nothing is said.
+#ifndef HK_BWD_PARTS
+#define HK_BWD_PARTS 4
+#endif
+constexpr int kBwdParts = HK_BWD_PARTS;
+static_assert(kBwdParts == 2 || kBwdParts == 4, "2 or 4 threads per TMEM lane");
+constexpr int kBwdCW = 4 * kBwdParts;              // element-wise warps
+constexpr int kBwdPC = 128 / kBwdParts;            // score columns per element-wise thread
+constexpr int kBwdThreads = 32 * (kBwdCW + 4);     // + TMA producer, two UMMA issuers, statistics loader (idle in dQ)
+// Register budget: all warps start with kBwdRegsAtLaunch; the element-wise warps then grow by exactly what the
+// other four warps give up (setmaxnreg only moves registers inside the CTA's own allocation: asking for more than
+// was released would block forever): 8 x (208 - 168) = 4 x (168 - 88). With 4 parts (640 threads) every thread keeps
+// its 96 registers: the element-wise code fits, and no re-allocation is done.
+constexpr int kBwdRegsAtLaunch = kBwdParts == 2 ? 168 : 96;
+constexpr int kBwdRegsGrown = kBwdParts == 2 ? 208 : 96;
+constexpr int kBwdRegsShrunk = kBwdParts == 2 ? 88 : 96;
+static_assert(kBwdCW * (kBwdRegsGrown - kBwdRegsAtLaunch) == 4 * (kBwdRegsAtLaunch - kBwdRegsShrunk),
+              "registers taken by the element-wise warps must equal the registers released by the other warps");
+
+// kBwdPC fp32 columns of this thread's lane -> registers / kBwdPC/2 packed bf16 columns -> TMEM
+__device__ __forceinline__ void bwd_ld_part(uint32_t taddr, uint32_t* r) {
+#pragma unroll
+  for (int c = 0; c < kBwdPC / 32; ++c) ptx::tmem_ld32(taddr + c * 32, r + c * 32);
+}
+__device__ __forceinline__ void bwd_st_packed(uint32_t taddr, const uint32_t* r) {
+  if constexpr (kBwdPC == 64) ptx::tmem_st32(taddr, r);
+  else ptx::tmem_st16(taddr, r);
+}
+__device__ __forceinline__ void bwd_grow_registers() {
+  if constexpr (kBwdParts == 2) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    static_assert(kBwdParts != 2 || kBwdRegsGrown == 208, "keep the immediate above in step");
+  }
+}
+__device__ __forceinline__ void bwd_shrink_registers() {
+  if constexpr (kBwdParts == 2) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+    static_assert(kBwdParts != 2 || kBwdRegsShrunk == 88, "keep the immediate above in step");
+  }
+}
 
 // ------------------------------------------------------------------------------------ shared helpers
 // The two UMMA-issuing roles run either as one thread (lane 0 of their warp) or as a whole warp that keeps
@@ -1180,4 +1194,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   }
 }
 
+}  // namespace HK_BWD_NS
 }  // namespace hk
+#undef HK_BWD_NS
+#undef HK_BWD_PARTS

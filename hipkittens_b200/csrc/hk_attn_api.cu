@@ -9,6 +9,13 @@
 #include <mutex>
 
 #include "../../include/hk_attn.h"
+// The backward kernels are compiled in two thread layouts (see the header): 16 element-wise warps for the
+// non-causal instantiations, 8 for the causal ones.
+#define HK_BWD_NS bwd16
+#define HK_BWD_PARTS 4
+#include "attn_bwd_sm100.cuh"
+#define HK_BWD_NS bwd8
+#define HK_BWD_PARTS 2
 #include "attn_bwd_sm100.cuh"
 #include "attn_fwd_sm100.cuh"
 #include "paged_decode_sm100.cuh"
@@ -74,17 +81,34 @@ int prepare_fwd_kernel() {
   return HK_OK;
 }
 
+// The layout that serves an instantiation, with its kernels and launch constants.
+template <bool CAUSAL>
+struct BwdLayout;
+template <>
+struct BwdLayout<false> {
+  static constexpr int kThreads = hk::bwd16::kBwdThreads, kRegsAtLaunch = hk::bwd16::kBwdRegsAtLaunch;
+  static constexpr bool kExactRegs = hk::bwd16::kBwdRegsGrown != hk::bwd16::kBwdRegsAtLaunch;
+  template <int D> static constexpr auto dkdv() { return &hk::bwd16::attn_bwd_dkdv_kernel<D, false>; }
+  template <int D> static constexpr auto dq() { return &hk::bwd16::attn_bwd_dq_kernel<D, false>; }
+};
+template <>
+struct BwdLayout<true> {
+  static constexpr int kThreads = hk::bwd8::kBwdThreads, kRegsAtLaunch = hk::bwd8::kBwdRegsAtLaunch;
+  static constexpr bool kExactRegs = hk::bwd8::kBwdRegsGrown != hk::bwd8::kBwdRegsAtLaunch;
+  template <int D> static constexpr auto dkdv() { return &hk::bwd8::attn_bwd_dkdv_kernel<D, true>; }
+  template <int D> static constexpr auto dq() { return &hk::bwd8::attn_bwd_dq_kernel<D, true>; }
+};
+
 template <typename Kernel>
-int prepare_bwd_kernel(Kernel* fn, int dyn_bytes, const char* name) {
+int prepare_bwd_kernel(Kernel* fn, int dyn_bytes, const char* name, int regs_at_launch, bool exact) {
   HK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn_bytes));
   cudaFuncAttributes attr;
   HK_CUDA(cudaFuncGetAttributes(&attr, fn));
   // With register re-balancing between warps (the 8-warp layout) the count at launch has to be exact, as for the
   // forward kernel: refuse to launch a build it would not add up in. Without it any count that fits is fine.
-  const bool exact = hk::kBwdRegsGrown != hk::kBwdRegsAtLaunch;
-  if (exact ? attr.numRegs != hk::kBwdRegsAtLaunch : attr.numRegs > hk::kBwdRegsAtLaunch) {
+  if (exact ? attr.numRegs != regs_at_launch : attr.numRegs > regs_at_launch) {
     snprintf(g_cuda_err, sizeof(g_cuda_err), "%s compiled to %d registers, expected %d", name, attr.numRegs,
-             hk::kBwdRegsAtLaunch);
+             regs_at_launch);
     return HK_EUNSUPPORTED;
   }
   if (attr.sharedSizeBytes != 0) {  // the kernels assume their dynamic shared memory starts the CTA's window
@@ -97,9 +121,12 @@ int prepare_bwd_kernel(Kernel* fn, int dyn_bytes, const char* name) {
 
 template <int D, bool CAUSAL>
 int prepare_bwd_kernels() {
-  int rc = prepare_bwd_kernel(hk::attn_bwd_dkdv_kernel<D, CAUSAL>, hk::BwdSmem<D>::kDynBytes, "attn_bwd_dkdv_kernel");
+  using Lay = BwdLayout<CAUSAL>;
+  int rc = prepare_bwd_kernel(Lay::template dkdv<D>(), hk::BwdSmem<D>::kDynBytes, "attn_bwd_dkdv_kernel",
+                              Lay::kRegsAtLaunch, Lay::kExactRegs);
   if (rc != HK_OK) return rc;
-  return prepare_bwd_kernel(hk::attn_bwd_dq_kernel<D, CAUSAL>, hk::BwdSmem<D>::kDynBytes, "attn_bwd_dq_kernel");
+  return prepare_bwd_kernel(Lay::template dq<D>(), hk::BwdSmem<D>::kDynBytes, "attn_bwd_dq_kernel", Lay::kRegsAtLaunch,
+                            Lay::kExactRegs);
 }
 
 int init_device(int device) {
@@ -205,7 +232,8 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
   long long* const trace_buf = p.trace;
   p.trace = g_trace_bwd_kernel == 0 ? trace_buf : nullptr;
 #endif
-  hk::attn_bwd_dkdv_kernel<D, CAUSAL><<<grid, hk::kBwdThreads, hk::BwdSmem<D>::kDynBytes, stream>>>(tq, tk, tv, tdo, p);
+  using Lay = BwdLayout<CAUSAL>;
+  Lay::template dkdv<D>()<<<grid, Lay::kThreads, hk::BwdSmem<D>::kDynBytes, stream>>>(tq, tk, tv, tdo, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   HK_CUDA(cudaGetLastError());
   p.n_items = B * H * nb;
@@ -213,7 +241,7 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
 #ifdef HK_TRACE
   p.trace = g_trace_bwd_kernel == 1 ? trace_buf : nullptr;
 #endif
-  hk::attn_bwd_dq_kernel<D, CAUSAL><<<grid, hk::kBwdThreads, hk::BwdSmem<D>::kDynBytes, stream>>>(tq, tk, tv, tdo, p);
+  Lay::template dq<D>()<<<grid, Lay::kThreads, hk::BwdSmem<D>::kDynBytes, stream>>>(tq, tk, tv, tdo, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   HK_CUDA(cudaGetLastError());
   return HK_OK;
