@@ -8,10 +8,16 @@ forward; split + combine launches for decode; delta prep + dK/dV + dQ launches f
 shape: B=16, N=2048, H=64, H_KV=8, D=128, non-causal (kernels/attn/gqa/test_python.py:22-27).
 TFLOPS = 4*B*N^2*H*D / (2 if causal) / time, the reference's convention (test_python.py:35-38).
 
-With N > 1 (torchrun, one rank per GPU) every rank runs the same workload on its own seeded inputs
-(weak scaling: (batch, kv-head) units are independent, there is no collective on the data path);
-`value` is the sum over ranks divided by the slowest rank's time. `--scaling strong` instead splits the
-one workload's units over the ranks with hipkittens_b200.shard.
+With N > 1 (torchrun, one rank per GPU) the one workload's (batch, kv-head) units are dealt to the ranks with
+hipkittens_b200.shard.partition_units (strong scaling; the units are independent, there is no collective on the
+data path) and `value` is the workload's FLOP divided by the slowest rank's time. Outside the timed region the ranks
+then check their shards on the GPU (`shard_parity`: NCCL gather of O and L against one single-GPU launch) and time the
+replica arrangement as well (`replicas`: every rank the whole workload on its own inputs). `--scaling weak` makes
+the replica arrangement the headline instead.
+
+The default single-GPU run also times the other configurations for K steps each (`other_workloads`: causal N = 8192,
+D = 64 MHA, paged decode, the backward) and runs the headline workload back to back for two seconds
+(`sustained`), after the headline numbers have been taken.
 
 One JSON line is printed by rank 0.
 """
@@ -108,7 +114,7 @@ class ClockSampler:
     def __init__(self, device_index: int, period_s: float = 0.01):
         self.period = period_s
         self.samples = []
-        self.timed = False
+        self.tag = None   # name of the timed region in progress (None outside timed regions)
         self._stop = threading.Event()
         self._thread = None
         self.sm_max = None
@@ -138,7 +144,7 @@ class ClockSampler:
                     mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
                 except Exception:
                     mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
-                self.samples.append((self.timed, mhz, mask))
+                self.samples.append((self.tag, mhz, mask))
             except Exception:
                 pass
             self._stop.wait(self.period)
@@ -153,10 +159,12 @@ class ClockSampler:
         if self._thread is not None:
             self._thread.join(timeout=2)
 
-    def summary(self):
+    def summary(self, tag="timed"):
+        """Median SM clock and the union of throttle reasons over the samples taken while region `tag` was timed
+        (over all samples when that region was too short to be sampled three times)."""
         if self.handle is None or not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [], "samples": 0}
-        timed = [s for s in self.samples if s[0]]
+        timed = [s for s in self.samples if s[0] == tag]
         use = timed if len(timed) >= 3 else self.samples
         mask = 0
         for s in use:
@@ -167,7 +175,7 @@ class ClockSampler:
             "sm_max_mhz": self.sm_max,
             "reasons": reasons,
             "samples": len(use),
-            "window": "timed" if use is timed else "warmup+timed",
+            "window": "timed" if use is timed else "whole run",
         }
 
 
@@ -226,6 +234,272 @@ def cpu_decode_sample(budget_s: float):
     return toks, int(cl.sum()) * done, time.perf_counter() - t0, done
 
 
+# ------------------------------------------------------------------------------------------ workloads on the device
+L2_BYTES = 126e6
+
+
+def workload_config(name: str) -> dict:
+    """The `config` object of a workload: printed identically by the GPU arm and by the reference arm."""
+    kind, b, n, h, hkv, d, causal = WORKLOADS[name]
+    if kind == "decode":
+        return {"workload": name, "S": b, "H": h, "H_KV": hkv, "D": d, "page": 16,
+                "pool_pages": DECODE_POOL_PAGES[name], "ctx": "U{512..8192}", "cache": "inputs_exceed_l2"}
+    in_bytes = 2 * b * n * d * (h + 2 * hkv) * (2 if kind == "bwd" else 1)
+    return {"workload": name, "B": b, "N": n, "H": h, "H_KV": hkv, "D": d, "causal": causal,
+            "cache": "inputs_exceed_l2" if in_bytes > L2_BYTES else "inputs_fit_l2"}
+
+
+class PrefillRun:
+    """One rank's share of a forward or backward workload, resident in HBM.
+
+    `slices` (from hipkittens_b200.shard.partition_units) selects this rank's (batch, kv-head) units of the one
+    seeded workload; None = the whole workload. When the share's inputs would fit in L2, several differently
+    seeded input sets are kept and the steps rotate through them, so that no step finds its inputs cached by the
+    previous one."""
+
+    def __init__(self, hk, dev, stream, kind, b, n, h, hkv, d, causal, seed, slices=None):
+        from hipkittens_b200.shard import shard_tensors
+        from hipkittens_b200.synthetic import make_prefill_inputs
+
+        self.hk, self.kind, self.causal, self.stream, self.n, self.d = hk, kind, causal, stream, n, d
+        self.sets = []
+        self.members = []
+        n_sets = 1
+        while True:
+            qf, kf, vf = make_prefill_inputs(b, n, h, hkv, d, seed=seed + 7919 * len(self.sets))
+            if slices is None:
+                parts = [(qf, kf, vf, None)]
+            else:
+                parts = shard_tensors(qf, kf, vf, hkv, slices)
+            shards = [(qs.to(dev), ks.to(dev), vs.to(dev)) for qs, ks, vs, _m in parts]
+            if not self.sets:
+                self.members = [m for _q, _k, _v, m in parts]
+                self.in_bytes = sum(t.numel() * 2 for sh in shards for t in sh) * (2 if kind == "bwd" else 1)
+                if self.in_bytes <= L2_BYTES:
+                    n_sets = int(L2_BYTES // max(self.in_bytes, 1)) + 2
+            outs = [(torch.empty_like(qs), torch.empty((qs.shape[0], qs.shape[2], 1, n), dtype=torch.float32,
+                                                       device=dev)) for qs, _k, _v in shards]
+            bwd_in = None
+            if kind == "bwd":
+                # the backward's inputs: dO (seeded), and O and L from one forward pass outside the timed region
+                gen = torch.Generator(device=dev).manual_seed(1000 + seed + len(self.sets))
+                bwd_in = []
+                for (qs, ks, vs), (o, l) in zip(shards, outs):
+                    hk.attn_fwd(qs, ks, vs, causal=causal, out=o, lse=l, stream=stream)
+                    d_o = torch.randn(qs.shape, generator=gen, device=dev).to(torch.bfloat16)
+                    bwd_in.append((d_o, torch.empty_like(l), torch.empty_like(qs), torch.empty_like(ks),
+                                   torch.empty_like(vs)))
+            self.sets.append((shards, outs, bwd_in))
+            del qf, kf, vf
+            if len(self.sets) >= n_sets:
+                break
+        flops_of = fwd_flops if kind == "fwd" else bwd_flops
+        self.flops = sum(flops_of(qs.shape[0], n, qs.shape[2], d, causal) for qs, _k, _v in self.sets[0][0])
+        self.launches_per_step = len(self.sets[0][0]) * (1 if kind == "fwd" else 3)
+        self.cache = ("inputs_exceed_l2" if len(self.sets) == 1 else
+                      f"inputs_exceed_l2 (steps rotate through {len(self.sets)} input sets of {self.in_bytes / 1e6:.0f} MB)")
+
+    def step(self, i: int = 0):
+        hk, stream, causal = self.hk, self.stream, self.causal
+        shards, outs, bwd_in = self.sets[i % len(self.sets)]
+        if self.kind == "fwd":
+            for (qs, ks, vs), (o, l) in zip(shards, outs):
+                hk.attn_fwd(qs, ks, vs, causal=causal, out=o, lse=l, stream=stream)
+        else:
+            for (qs, ks, vs), (o, l), (d_o, delta, dq, dk, dv) in zip(shards, outs, bwd_in):
+                hk.attn_bwd_prep(o, d_o, delta, stream=stream)
+                hk.attn_bwd(qs, ks, vs, d_o, l, delta, causal=causal, dq=dq, dk=dk, dv=dv, stream=stream)
+
+
+class DecodeRun:
+    def __init__(self, hk, dev, stream, name, b, h, hkv, d, seed):
+        from hipkittens_b200.synthetic import make_paged_inputs
+
+        q, kp, vp, bt, cl = make_paged_inputs(b, h, hkv, d, 16, DECODE_POOL_PAGES[name], 512, 8192, seed=seed,
+                                               pool_on=str(dev))
+        self.hk, self.stream = hk, stream
+        self.q, self.bt, self.cl, self.kp, self.vp = q.to(dev), bt.to(dev), cl.to(dev), kp, vp
+        self.ws = torch.empty(hk.paged_decode_workspace_bytes(b, h, d, bt.shape[1]), dtype=torch.uint8, device=dev)
+        self.o = torch.empty_like(self.q)
+        self.l = torch.empty((b, h, 1, 1), dtype=torch.float32, device=dev)
+        self.sum_ctx = int(cl.sum())
+        self.tokens = float(b)                          # tokens generated per step
+        self.kv_bytes = 2 * self.sum_ctx * hkv * d * 2  # K and V of the live context, once
+        self.launches_per_step = 2
+        self.cache = "inputs_exceed_l2"
+
+    def step(self, i: int = 0):
+        self.hk.paged_decode(self.q, self.kp, self.vp, self.bt, self.cl, out=self.o, lse=self.l, workspace=self.ws,
+                             stream=self.stream)
+
+
+def time_steps(run, steps, warmup, stream, barrier, sampler=None, tag=None):
+    """W untimed steps, then K steps between two events on the launching stream, a barrier and a device
+    synchronisation on both sides. Returns the milliseconds between the events."""
+    for i in range(warmup):
+        run.step(i)
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    if sampler is not None:
+        sampler.tag = tag
+    e0.record(stream)
+    for i in range(steps):
+        run.step(i)
+    e1.record(stream)
+    barrier()
+    if sampler is not None:
+        sampler.tag = None
+    return e0.elapsed_time(e1)
+
+
+def prefill_roofline(name, kind, ach_tflops, peaks, peaks_src, flops_per_launch):
+    r = {"bound": "tensor", "achieved": ach_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+         "frac": ach_tflops / peaks["bf16_tflops"], "peak_sustained": peaks["bf16_tflops_sustained"],
+         "frac_of_sustained": ach_tflops / peaks["bf16_tflops_sustained"],
+         "peak_kind": f"of {peaks_src} (burst cuBLAS bf16)", "traffic": NCU_TRAFFIC_BYTES.get(name),
+         "flops_per_launch": flops_per_launch}
+    if kind == "bwd":
+        r["note"] = ("a step is three launches (delta prep, dK/dV kernel, dQ kernel) timed together; flops are the "
+                     "reference's 2.5 x forward count, the recomputation of S and dP in the second kernel is not counted")
+    return r
+
+
+def decode_roofline(name, ach_gbs, peaks, peaks_src, kv_bytes):
+    return {"bound": "hbm", "achieved": ach_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": ach_gbs / peaks["hbm_gbs"], "peak_kind": f"of {peaks_src} (copy)",
+            "traffic": NCU_TRAFFIC_BYTES.get(name), "bytes_per_launch": kv_bytes}
+
+
+METRIC = {
+    "fwd": "bf16 GQA attn-fwd TFLOPS (4*B*N^2*H*D, /2 causal)",
+    "bwd": "bf16 GQA attn-bwd TFLOPS (2.5 * 4*B*N^2*H*D, /2 causal; delta prep + dK/dV + dQ kernels)",
+    "decode": "paged-KV GQA decode tokens/s",
+}
+# The other configurations of the benchmark, timed after the headline workload in the default single-GPU run.
+OTHER_WORKLOADS = ["gqa_causal_fwd_b4_n8192_h64_kv8_d128", "mha_fwd_b16_n4096_h16_d64",
+                   "paged_decode_s64_ctx512_8192_h64_kv8_d128", "gqa_bwd_b16_n2048_h64_kv8_d128"]
+
+
+def run_other_workloads(hk, _native, dev, stream, local_rank, sampler, barrier, peaks, peaks_src, steps, warmup):
+    """One entry per remaining configuration: same timing rules as the headline (W warm-up steps, K timed steps
+    between events on the launching stream, clocks sampled during the timed steps)."""
+    out = []
+    for name in OTHER_WORKLOADS:
+        kind, b, n, h, hkv, d, causal = WORKLOADS[name]
+        if kind == "decode":
+            run = DecodeRun(hk, dev, stream, name, b, h, hkv, d, seed=0)
+        else:
+            run = PrefillRun(hk, dev, stream, kind, b, n, h, hkv, d, causal, seed=0)
+        l0 = hk.kernel_launch_count()
+        ms = time_steps(run, steps, warmup, stream, barrier, sampler, tag=name) / steps
+        launches = hk.kernel_launch_count() - l0 - warmup * run.launches_per_step
+        if _native.device_status(local_rank) != 0:
+            raise SystemExit(f"device status non-zero after {name}")
+        entry = {"workload": name, "metric": METRIC[kind], "steps": steps, "warmup": warmup, "ms_per_step": ms,
+                 "gpu_launches": int(launches), "config": dict(workload_config(name), cache=run.cache)}
+        if kind == "decode":
+            entry.update({"value": run.tokens / (ms * 1e-3), "unit": "tokens/s",
+                          "roofline": decode_roofline(name, run.kv_bytes / (ms * 1e-3) / 1e9, peaks, peaks_src,
+                                                      run.kv_bytes)})
+            entry["roofline"]["sum_ctx"] = run.sum_ctx
+        else:
+            tf = run.flops / (ms * 1e-3) / 1e12
+            entry.update({"value": tf, "unit": "TFLOP/s",
+                          "roofline": prefill_roofline(name, kind, tf, peaks, peaks_src, run.flops)})
+        entry["clocks"] = sampler.summary(name)
+        out.append(entry)
+        del run
+        torch.cuda.empty_cache()
+    return out
+
+
+def run_sustained(hk, run, stream, barrier, sampler, seconds, ms_per_step_hint, flops):
+    """The headline workload back to back for at least `seconds`: the figure a long job sees once the part sits at
+    its power limit, beside the burst figure of the K-step run. Clocks are sampled, never set."""
+    steps = max(50, int(math.ceil(seconds * 1e3 / max(ms_per_step_hint, 1e-3) * 1.25)))
+    ms = time_steps(run, steps, 0, stream, barrier, sampler, tag="sustained")
+    c = sampler.summary("sustained")
+    return {"steps": steps, "seconds": ms * 1e-3, "ms_per_step": ms / steps, "value": flops * steps / (ms * 1e-3) / 1e12,
+            "unit": "TFLOP/s", "sm_mhz_median": c["sm_mhz"], "sm_max_mhz": c["sm_max_mhz"], "reasons": c["reasons"],
+            "samples": c["samples"]}
+
+
+def fp32_attention_on_device(q, k, v, causal):
+    """fp32 restatement of the math for ONE (batch, kv-head) unit, evaluated with torch on the GPU; a checker for
+    the shard parity report, not part of any timed region. q [N,G,D], k, v [N,D] -> O [N,G,D] fp32, L [G,N]."""
+    n, g, d = q.shape
+    s = torch.einsum("ngd,md->gnm", q.float(), k.float()) / math.sqrt(d)
+    if causal:
+        s = s.masked_fill(torch.ones(n, n, dtype=torch.bool, device=q.device).triu(1), float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    o = torch.einsum("gnm,md->ngd", torch.softmax(s, dim=-1), v.float())
+    return o, lse
+
+
+def shard_parity_report(hk, dist, run, dev, stream, rank, world, b, n, h, hkv, d, causal):
+    """Outside every timed region: (1) every rank checks one unit of its own O / L shard against the fp32
+    restatement on its GPU; (2) the O and L shards of all ranks are gathered with NCCL (all_gather_into_tensor when
+    the shards have one shape, else one broadcast per rank) and rank 0 compares the reassembled tensors with one
+    single-GPU launch on the whole workload from the same seed. Returns the dict rank 0 prints."""
+    from hipkittens_b200.shard import partition_units, scatter_outputs
+    from hipkittens_b200.synthetic import make_prefill_inputs
+
+    g = h // hkv
+    shards, outs, _ = run.sets[0]
+    for (qs, ks, vs), (o, l) in zip(shards, outs):
+        hk.attn_fwd(qs, ks, vs, causal=causal, out=o, lse=l, stream=stream)
+    torch.cuda.synchronize()
+    (qs, ks, vs), (o, l) = shards[0], outs[0]
+    o_ref, l_ref = fp32_attention_on_device(qs[0, :, :g], ks[0, :, 0], vs[0, :, 0], causal)
+    unit_err = torch.tensor([float((o[0, :, :g].float() - o_ref).abs().max()),
+                             float((l[0, :g, 0] - l_ref).abs().max())], dtype=torch.float64, device=dev)
+    dist.all_reduce(unit_err, op=dist.ReduceOp.MAX)
+
+    o_full = torch.zeros((b, n, h, d), dtype=torch.bfloat16, device=dev)
+    l_full = torch.zeros((b, h, 1, n), dtype=torch.float32, device=dev)
+    shapes = []
+    for r in range(world):
+        groups = {}
+        for sl in partition_units(b, hkv, world, r):
+            groups.setdefault(sl.kvh_hi - sl.kvh_lo, []).append(sl)
+        shapes.append([(width, members) for width, members in sorted(groups.items())])
+    same = all(len(sh) == 1 and len(sh[0][1]) == len(shapes[0][0][1]) and sh[0][0] == shapes[0][0][0] for sh in shapes)
+    if same:
+        og = torch.empty((world,) + tuple(outs[0][0].shape), dtype=torch.bfloat16, device=dev)
+        lg = torch.empty((world,) + tuple(outs[0][1].shape), dtype=torch.float32, device=dev)
+        dist.all_gather_into_tensor(og, outs[0][0].contiguous())
+        dist.all_gather_into_tensor(lg, outs[0][1].contiguous())
+        for r in range(world):
+            scatter_outputs(o_full, l_full, og[r], lg[r], shapes[r][0][1], hkv)
+        how = "all_gather_into_tensor"
+    else:
+        for r in range(world):
+            for gi, (width, members) in enumerate(shapes[r]):
+                if r == rank:
+                    ob, lb = outs[gi][0].contiguous(), outs[gi][1].contiguous()
+                else:
+                    ob = torch.empty((len(members), n, width * g, d), dtype=torch.bfloat16, device=dev)
+                    lb = torch.empty((len(members), width * g, 1, n), dtype=torch.float32, device=dev)
+                dist.broadcast(ob, src=r)
+                dist.broadcast(lb, src=r)
+                scatter_outputs(o_full, l_full, ob, lb, members, hkv)
+        how = "broadcast per rank (shards of unequal shape)"
+    report = None
+    if rank == 0:
+        qf, kf, vf = make_prefill_inputs(b, n, h, hkv, d, seed=0)
+        o1, l1 = hk.attn_fwd(qf.to(dev), kf.to(dev), vf.to(dev), causal=causal, stream=stream)
+        torch.cuda.synchronize()
+        report = {"max_abs_o": float((o_full.float() - o1.float()).abs().max()),
+                  "max_abs_l": float((l_full - l1).abs().max()),
+                  "unit_vs_fp32_max_abs_o": float(unit_err[0]), "unit_vs_fp32_max_abs_l": float(unit_err[1]),
+                  "gather": how,
+                  "what": "O and L shards of all ranks gathered over NCCL and compared on rank 0 with one single-GPU "
+                          "launch on the whole workload (same seed); plus, on every rank, one (batch, kv-head) unit "
+                          "against an fp32 restatement on the GPU (max over ranks)"}
+    return report
+
+
 # ------------------------------------------------------------------------------------------ main
 def main() -> int:
     ap = argparse.ArgumentParser()
@@ -234,10 +508,13 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--scaling", default=None, choices=["weak", "strong"],
+                    help="default: strong (one workload split over the ranks) with more than one rank")
     ap.add_argument("--cpu-budget-s", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-others", action="store_true", help="skip the other configurations and the sustained run")
+    ap.add_argument("--sustained-s", type=float, default=2.0)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -245,6 +522,10 @@ def main() -> int:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     kind, b, n, h, hkv, d, causal = WORKLOADS[args.workload]
+    if args.scaling is None:
+        args.scaling = "strong" if (world > 1 and kind in ("fwd", "bwd")) else "weak"
+    if kind == "decode":
+        args.scaling = "weak"   # sequences are drawn per rank; the decode workload is not split
     peaks, peaks_src = load_peaks()
 
     if kind in ("rotary", "append"):
@@ -254,13 +535,13 @@ def main() -> int:
 
     import hipkittens_b200 as hk
     from hipkittens_b200 import _native
-    from hipkittens_b200.shard import partition_units, shard_tensors
-    from hipkittens_b200.synthetic import make_paged_inputs, make_prefill_inputs
+    from hipkittens_b200.shard import partition_units
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    dist = None
     if world > 1:
         import torch.distributed as dist
 
@@ -275,73 +556,25 @@ def main() -> int:
     sampler = ClockSampler(local_rank)
 
     # ---------------- inputs resident in HBM
+    strong = args.scaling == "strong" and world > 1
     if kind in ("fwd", "bwd"):
-        if args.scaling == "strong" and world > 1:
-            qf, kf, vf = make_prefill_inputs(b, n, h, hkv, d, seed=0)
-            parts = shard_tensors(qf, kf, vf, hkv, partition_units(b, hkv, world, rank))
-            shards = [(qs.to(dev), ks.to(dev), vs.to(dev)) for qs, ks, vs, _m in parts]
-            del qf, kf, vf
+        if strong:
+            run = PrefillRun(hk, dev, stream, kind, b, n, h, hkv, d, causal, seed=0,
+                             slices=partition_units(b, hkv, world, rank))
         else:
-            qf, kf, vf = make_prefill_inputs(b, n, h, hkv, d, seed=rank)
-            shards = [(qf.to(dev), kf.to(dev), vf.to(dev))]
-        outs = [(torch.empty_like(qs), torch.empty((qs.shape[0], qs.shape[2], 1, n), dtype=torch.float32, device=dev))
-                for qs, _k, _v in shards]
-        flops_of = fwd_flops if kind == "fwd" else bwd_flops
-        my_flops = sum(flops_of(qs.shape[0], n, qs.shape[2], d, causal) for qs, _k, _v in shards)
-        my_units = float(my_flops)
-        in_bytes = sum(t.numel() * 2 for sh in shards for t in sh)
-
-        if kind == "fwd":
-            def step():
-                for (qs, ks, vs), (o, l) in zip(shards, outs):
-                    hk.attn_fwd(qs, ks, vs, causal=causal, out=o, lse=l, stream=stream)
-        else:
-            # the backward's inputs: dO (seeded), and O and L from one forward pass outside the timed region
-            gen = torch.Generator(device=dev).manual_seed(1000 + rank)
-            bwd_in = []
-            for (qs, ks, vs), (o, l) in zip(shards, outs):
-                hk.attn_fwd(qs, ks, vs, causal=causal, out=o, lse=l, stream=stream)
-                d_o = torch.randn(qs.shape, generator=gen, device=dev).to(torch.bfloat16)
-                bwd_in.append((d_o, torch.empty_like(l), torch.empty_like(qs), torch.empty_like(ks), torch.empty_like(vs)))
-            in_bytes += sum(t[0].numel() * 4 for t in bwd_in)
-
-            def step():
-                for (qs, ks, vs), (o, l), (d_o, delta, dq, dk, dv) in zip(shards, outs, bwd_in):
-                    hk.attn_bwd_prep(o, d_o, delta, stream=stream)
-                    hk.attn_bwd(qs, ks, vs, d_o, l, delta, causal=causal, dq=dq, dk=dk, dv=dv, stream=stream)
+            run = PrefillRun(hk, dev, stream, kind, b, n, h, hkv, d, causal, seed=rank)
+        my_units = float(run.flops)
+        flops_per_launch = run.flops / max(len(run.sets[0][0]), 1)
     else:
-        q, kp, vp, bt, cl = make_paged_inputs(b, h, hkv, d, 16, DECODE_POOL_PAGES[args.workload], 512, 8192, seed=rank,
-                                               pool_on=str(dev))
-        q, bt, cl = q.to(dev), bt.to(dev), cl.to(dev)
-        ws = torch.empty(hk.paged_decode_workspace_bytes(b, h, d, bt.shape[1]), dtype=torch.uint8, device=dev)
-        o = torch.empty_like(q)
-        l = torch.empty((b, h, 1, 1), dtype=torch.float32, device=dev)
-        sum_ctx = int(cl.sum())
-        my_units = float(b)  # tokens generated per step
-        kv_bytes = 2 * sum_ctx * hkv * d * 2
+        run = DecodeRun(hk, dev, stream, args.workload, b, h, hkv, d, seed=rank)
+        my_units = run.tokens
+    headline_cache = run.cache
 
-        def step():
-            hk.paged_decode(q, kp, vp, bt, cl, out=o, lse=l, workspace=ws, stream=stream)
-
-        in_bytes = kp.numel() * 4
-
-    # ---------------- device-resident timing
+    # ---------------- device-resident timing of the headline workload
     sampler.start()
-    for _ in range(args.warmup):
-        step()
-    barrier()
     launches0 = hk.kernel_launch_count()
-    e0 = torch.cuda.Event(enable_timing=True)
-    e1 = torch.cuda.Event(enable_timing=True)
-    sampler.timed = True
-    e0.record(stream)
-    for _ in range(args.steps):
-        step()
-    e1.record(stream)
-    barrier()
-    sampler.timed = False
-    launches = hk.kernel_launch_count() - launches0
-    ms_total = e0.elapsed_time(e1)
+    ms_total = time_steps(run, args.steps, args.warmup, stream, barrier, sampler, tag="timed")
+    launches = hk.kernel_launch_count() - launches0 - args.warmup * run.launches_per_step
     status = _native.device_status(local_rank)
     if status != 0:
         raise SystemExit(f"device status {status} after the timed region")
@@ -349,11 +582,10 @@ def main() -> int:
     # ---------------- end-to-end through the reference-facing module, host buffers
     e2e = None
     if not args.no_e2e:
-        e2e = measure_e2e(hk, kind, args, dev, stream, causal, b, n, h, hkv, d,
-                          shards if kind != "decode" else None,
-                          (q, kp, vp, bt, cl, ws) if kind == "decode" else None, barrier,
-                          (outs, bwd_in) if kind == "bwd" else None)
-    sampler.stop()
+        shards0, outs0, bwd0 = run.sets[0] if kind != "decode" else (None, None, None)
+        e2e = measure_e2e(hk, kind, args, dev, stream, causal, b, n, h, hkv, d, shards0,
+                          (run.q, run.kp, run.vp, run.bt, run.cl, run.ws) if kind == "decode" else None, barrier,
+                          (outs0, bwd0) if kind == "bwd" else None)
 
     # ---------------- reduce over ranks: slowest rank's time, summed work
     ms = torch.tensor([ms_total, e2e["ms_total"] if e2e else 0.0], dtype=torch.float64, device=dev)
@@ -365,58 +597,78 @@ def main() -> int:
     total_units = float(units[0])
     ms_per_step = ms_total_max / args.steps
 
+    # ---------------- N > 1: shard parity on the GPUs, and the replica (weak-scaling) figure beside the split one
+    shard_parity = replicas = None
+    if strong and kind == "fwd":
+        shard_parity = shard_parity_report(hk, dist, run, dev, stream, rank, world, b, n, h, hkv, d, causal)
+    if strong:
+        del run
+        torch.cuda.empty_cache()
+        rep = PrefillRun(hk, dev, stream, kind, b, n, h, hkv, d, causal, seed=rank)
+        rep_ms = torch.tensor([time_steps(rep, args.steps, args.warmup, stream, barrier)], dtype=torch.float64,
+                              device=dev)
+        dist.all_reduce(rep_ms, op=dist.ReduceOp.MAX)
+        replicas = {"scaling": "weak", "ms_per_step": float(rep_ms[0]) / args.steps,
+                    "value": rep.flops * world / (float(rep_ms[0]) / args.steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "what": "every rank runs the whole workload on its own seeded inputs (independent replicas)"}
+        run = rep
+
+    # ---------------- N = 1: the other configurations and the sustained figure, after the headline numbers
+    others = sustained = None
+    if world == 1 and not args.no_others and args.workload == DEFAULT_WORKLOAD:
+        sustained_run = run
+        others = run_other_workloads(hk, _native, dev, stream, local_rank, sampler, barrier, peaks, peaks_src,
+                                     args.steps, args.warmup)
+        sustained = run_sustained(hk, sustained_run, stream, barrier, sampler, args.sustained_s,
+                                  ms_total / args.steps, run.flops)
+        if _native.device_status(local_rank) != 0:
+            raise SystemExit("device status non-zero after the sustained run")
+    sampler.stop()
+
     if rank == 0:
-        clocks = sampler.summary()
+        clocks = sampler.summary("timed")
         line = {
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "data": "synthetic",
             "gpu_launches": int(launches), "clocks": clocks, "peaks_source": peaks_src,
+            "metric": METRIC[kind], "dtype": "bf16", "config": workload_config(args.workload),
         }
         if kind in ("fwd", "bwd"):
             tflops = total_units / (ms_per_step * 1e-3) / 1e12
-            per_launch_flops = my_flops / max(len(shards), 1)
-            ach = my_flops / (ms_total / args.steps * 1e-3) / 1e12
+            ach = my_units / (ms_total / args.steps * 1e-3) / 1e12
             line.update({
-                "metric": ("bf16 GQA attn-fwd TFLOPS (4*B*N^2*H*D, /2 causal)" if kind == "fwd" else
-                           "bf16 GQA attn-bwd TFLOPS (2.5 * 4*B*N^2*H*D, /2 causal; delta prep + dK/dV + dQ kernels)"),
                 "value": tflops, "unit": "TFLOP/s",
-                "dtype": "bf16",
-                "config": {"workload": args.workload, "B": b, "N": n, "H": h, "H_KV": hkv, "D": d,
-                           "causal": causal, "per_gpu_batch": b if args.scaling == "weak" else b / world,
-                           "cache": "inputs_exceed_l2" if in_bytes > 126e6 else "inputs_fit_l2",
-                           "sharding": "independent (batch, kv-head) units, no collective"},
-                "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                             "frac": ach / peaks["bf16_tflops"],
-                             "peak_sustained": peaks["bf16_tflops_sustained"],
-                             "frac_of_sustained": ach / peaks["bf16_tflops_sustained"],
-                             "peak_kind": f"of {peaks_src} (burst cuBLAS bf16)",
-                             "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-                             "flops_per_launch": per_launch_flops},
+                "partition": {"scaling": args.scaling,
+                              "units_total": b * hkv * (world if not strong else 1),
+                              "units_per_gpu": (b * hkv / world) if strong else b * hkv,
+                              "per_gpu_batch": (b / world) if strong else b,
+                              "cache": headline_cache,
+                              "sharding": "independent (batch, kv-head) units dealt contiguously to ranks, no collective "
+                                          "on the data path"},
+                "roofline": prefill_roofline(args.workload, kind, ach, peaks, peaks_src, flops_per_launch),
             })
-            if kind == "bwd":
-                line["roofline"]["note"] = ("a step is three launches (delta prep, dK/dV kernel, dQ kernel) timed together; "
-                                            "flops are the reference's 2.5 x forward count, the recomputation of S and dP "
-                                            "in the second kernel is not counted")
             if e2e:
                 line["e2e"] = {"value": total_units / (e2e_ms_max / e2e["steps"] * 1e-3) / 1e12, "unit": "TFLOP/s",
                                "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
                                "steps": e2e["steps"], "path": e2e["path"]}
         else:
             tok_s = total_units / (ms_per_step * 1e-3)
-            ach = kv_bytes / (ms_total / args.steps * 1e-3) / 1e9
-            line.update({
-                "metric": "paged-KV GQA decode tokens/s", "value": tok_s, "unit": "tokens/s", "dtype": "bf16",
-                "config": {"workload": args.workload, "S": b, "H": h, "H_KV": hkv, "D": d, "page": 16,
-                           "pool_pages": DECODE_POOL_PAGES[args.workload], "ctx": "U{512..8192}", "sum_ctx": sum_ctx,
-                           "cache": "inputs_exceed_l2"},
-                "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                             "frac": ach / peaks["hbm_gbs"], "peak_kind": f"of {peaks_src} (copy)",
-                             "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "bytes_per_launch": kv_bytes},
-            })
+            ach = run.kv_bytes / (ms_total / args.steps * 1e-3) / 1e9
+            line.update({"value": tok_s, "unit": "tokens/s",
+                         "roofline": decode_roofline(args.workload, ach, peaks, peaks_src, run.kv_bytes)})
+            line["roofline"]["sum_ctx"] = run.sum_ctx
             if e2e:
                 line["e2e"] = {"value": total_units / (e2e_ms_max / e2e["steps"] * 1e-3), "unit": "tokens/s",
                                "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
                                "steps": e2e["steps"], "path": e2e["path"]}
+        if shard_parity is not None:
+            line["shard_parity"] = shard_parity
+        if replicas is not None:
+            line["replicas"] = replicas
+        if others is not None:
+            line["other_workloads"] = others
+        if sustained is not None:
+            line["sustained"] = sustained
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(kind, b, n, h, hkv, d, causal, args.cpu_budget_s)
         print(json.dumps(line), flush=True)
@@ -518,13 +770,13 @@ def run_stream_workload(args, rank, world, local_rank, kind, b, n, h, hkv, d, pe
     torch.cuda.synchronize()
     l0 = hk.kernel_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler.timed = True
+    sampler.tag = "timed"
     e0.record(stream)
     for _ in range(args.steps):
         step()
     e1.record(stream)
     torch.cuda.synchronize()
-    sampler.timed = False
+    sampler.tag = None
     launches = hk.kernel_launch_count() - l0
     ms = e0.elapsed_time(e1) / args.steps
     if _native.device_status(local_rank) != 0:
@@ -740,16 +992,15 @@ def run_reference_arm(args, rank, world, kind, b, n, h, hkv, d, causal) -> int:
                   "bf16 GQA attn-bwd TFLOPS (2.5 * 4*B*N^2*H*D, /2 causal; delta prep + dK/dV + dQ kernels)")
         sample = (f"each step: as many (batch, kv-head) units of the workload shape as fit in {per_step_budget:.1f} s "
                   f"(of {b * hkv} per full pass)")
-        config = {"workload": args.workload, "B": b, "N": n, "H": h, "H_KV": hkv, "D": d, "causal": causal}
     else:
         value, unit = total_w / total_t, "tokens/s"
         metric = "paged-KV GQA decode tokens/s"
         sample = f"each step: passes over 8 sequences with ctx ~ U{{512..8192}} for {per_step_budget:.1f} s"
-        config = {"workload": args.workload, "S": b, "H": h, "H_KV": hkv, "D": d, "page": 16}
     line = {
         "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": total_t / max(len(times), 1) * 1e3, "higher_is_better": True,
-        "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.workload),
         "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,

@@ -17,7 +17,7 @@ import torch
 _PKG = os.path.dirname(os.path.abspath(__file__))
 _LIB = os.path.join(_PKG, "lib", "libhk_attn.so")
 
-HK_OK, HK_EINVAL, HK_EUNSUPPORTED, HK_ECUDA, HK_ETIMEOUT, HK_EWORKSPACE, HK_EBADPAGE = 0, -1, -2, -3, -4, -5, -6
+HK_OK, HK_EINVAL, HK_EUNSUPPORTED, HK_ECUDA, HK_ETIMEOUT, HK_EWORKSPACE, HK_EBADPAGE, HK_EBADLEN = 0, -1, -2, -3, -4, -5, -6, -7
 
 # Every symbol declared in include/hk_attn.h.
 EXPORTED_SYMBOLS = (
@@ -137,6 +137,17 @@ def _require_cuda_bf16(name: str, t: torch.Tensor, ndim: int) -> None:
         raise RuntimeError(f"{name} must have {ndim} dimensions, got {t.dim()}")
 
 
+def _require_same_device(ref: torch.Tensor, **tensors) -> None:
+    """Every pointer handed to the library must be device memory on the device the call names; a CPU tensor's
+    pointer would be dereferenced by a kernel."""
+    for name, t in tensors.items():
+        if t is None:
+            continue
+        if not isinstance(t, torch.Tensor) or t.device != ref.device:
+            raise RuntimeError(f"{name} must be a tensor on {ref.device} (got "
+                               f"{t.device if isinstance(t, torch.Tensor) else type(t).__name__})")
+
+
 def attn_fwd(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -180,6 +191,7 @@ def attn_fwd(
         raise RuntimeError("out must be a contiguous bf16 tensor of q's shape")
     if lse.shape != (b, h, 1, n) or lse.dtype != torch.float32 or not lse.is_contiguous():
         raise RuntimeError("lse must be a contiguous fp32 tensor [B, H, 1, N]")
+    _require_same_device(q, k=k, v=v, out=out, lse=lse)
     s = stream if stream is not None else torch.cuda.current_stream(q.device)
     if kv_lens is not None:
         if kv_lens.dtype != torch.int32 or kv_lens.shape != (b,) or kv_lens.device != q.device:
@@ -219,6 +231,7 @@ def attn_bwd_prep(o: torch.Tensor, d_o: torch.Tensor, delta: Optional[torch.Tens
         delta = torch.empty((b, h, 1, n), dtype=torch.float32, device=o.device)
     if delta.shape != (b, h, 1, n) or delta.dtype != torch.float32 or not delta.is_contiguous():
         raise RuntimeError("delta must be a contiguous fp32 tensor [B, H, 1, N]")
+    _require_same_device(o, d_o=d_o, delta=delta)
     s = stream if stream is not None else torch.cuda.current_stream(o.device)
     _check(capi().hk_attn_bwd_prep(o.data_ptr(), d_o.data_ptr(), delta.data_ptr(), b, n, h, d, o.device.index,
                                    s.cuda_stream), "hk_attn_bwd_prep")
@@ -267,6 +280,7 @@ def attn_bwd(
     for name, t, shp in (("dq", dq, dq_shape), ("dk", dk, tuple(k.shape)), ("dv", dv, tuple(v.shape))):
         if tuple(t.shape) != tuple(shp) or t.dtype != torch.bfloat16 or not t.is_contiguous():
             raise RuntimeError(f"{name} must be a contiguous bf16 tensor of shape {tuple(shp)}")
+    _require_same_device(q, k=k, v=v, d_o=d_o, dq=dq, dk=dk, dv=dv)
     s = stream if stream is not None else torch.cuda.current_stream(q.device)
     if kv_lens is not None and (kv_lens.dtype != torch.int32 or kv_lens.shape != (b,) or kv_lens.device != q.device):
         raise RuntimeError("kv_lens must be an int32 tensor [B] on q's device")
@@ -290,6 +304,7 @@ def dq_shuffle(dq_bhnd: torch.Tensor, dq_bnhd: Optional[torch.Tensor] = None,
         raise RuntimeError("dq_bnhd must be a contiguous tensor [B, N, H, D] of the source's dtype")
     if dq_bhnd.dtype != torch.bfloat16:
         raise RuntimeError("dq_bhnd must be torch.bfloat16")
+    _require_same_device(dq_bhnd, dq_bnhd=dq_bnhd)
     s = stream if stream is not None else torch.cuda.current_stream(dq_bhnd.device)
     _check(capi().hk_attn_dq_shuffle(dq_bhnd.data_ptr(), dq_bnhd.data_ptr(), b, n, h, d, dq_bhnd.device.index,
                                      s.cuda_stream), "hk_attn_dq_shuffle")
@@ -316,6 +331,7 @@ def rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, out: Optional[
         out = torch.empty_like(x)
     if out.shape != x.shape or out.dtype != x.dtype or not out.is_contiguous():
         raise RuntimeError("out must be a contiguous bf16 tensor of x's shape")
+    _require_same_device(x, cos=cos, sin=sin, out=out)
     s = stream if stream is not None else torch.cuda.current_stream(x.device)
     _check(capi().hk_rotary(x.data_ptr(), out.data_ptr(), sin.data_ptr(), cos.data_ptr(), b, h, n, d,
                             2 * cos.shape[1], x.device.index, s.cuda_stream), "hk_rotary")
@@ -361,8 +377,14 @@ def paged_decode(
     if lse is None:
         lse = torch.empty((s_n, h, 1, 1), dtype=torch.float32, device=q.device)
     need = paged_decode_workspace_bytes(s_n, h, d, max_pages, page)
+    if need == 0:
+        raise HkError(HK_EUNSUPPORTED, "hk_attn_paged_decode",
+                      "shape outside the decode kernels' limits (D = 128, 16-token pages, S <= 65535, "
+                      "max_pages <= 8192)")
     if workspace is None:
         workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=q.device)
+    _require_same_device(q, k_pages=k_pages, v_pages=v_pages, block_table=block_table, ctx_lens=ctx_lens, out=out,
+                         lse=lse, workspace=workspace)
     st = stream if stream is not None else torch.cuda.current_stream(q.device)
     rc = capi().hk_attn_paged_decode(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
                                      block_table.data_ptr(), ctx_lens.data_ptr(), out.data_ptr(), lse.data_ptr(),
@@ -397,6 +419,8 @@ def paged_kv_append(
         raise RuntimeError("k_new/v_new must be [S,T,H_KV,D] and k_pages/v_pages [P,page,H_KV,D]")
     if block_table.dim() != 2 or block_table.shape[0] != s_n or start_pos.shape != (s_n,):
         raise RuntimeError("block_table must be [S, max_pages] and start_pos [S]")
+    _require_same_device(k_new, v_new=v_new, k_pages=k_pages, v_pages=v_pages, block_table=block_table,
+                         start_pos=start_pos)
     st = stream if stream is not None else torch.cuda.current_stream(k_new.device)
     rc = capi().hk_paged_kv_append(k_new.data_ptr(), v_new.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
                                    block_table.data_ptr(), start_pos.data_ptr(), s_n, t_n, hkv, d, page,

@@ -294,13 +294,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
           for (int i = 0; i < kBlockN; ++i) su[i] = (i >= rem) ? 0xff800000u : su[i];
         }
-#if defined(HK_DEBUG_MINSOFTMAX)
-        // timing experiment only: the shortest possible softmax stage (load S, store something as P)
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) tmem_st16(tP + cc * 16, su + cc * 32);
-        l += 1.0f;
-        if (false) {
-#endif
         float bm0 = fmaxf(HK_S(0), HK_S(1)), bm1 = fmaxf(HK_S(2), HK_S(3));
         float bm2 = fmaxf(HK_S(4), HK_S(5)), bm3 = fmaxf(HK_S(6), HK_S(7));
 #pragma unroll
@@ -358,10 +351,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             const uint64_t x2 = fma2(pack2(HK_S(cc * 32 + 2 * i), HK_S(cc * 32 + 2 * i + 1)), c2, nmc2);
             uint64_t p2;
             float p0, p1;
-#if defined(HK_DEBUG_NOEXP)
-            p2 = x2;  // timing experiment only: no exponentials
-            unpack2(p2, p0, p1);
-#else
             if ((i % kEmuMod) < kEmuCnt) {
               float x0, x1;
               unpack2(x2, x0, x1);
@@ -375,7 +364,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               p1 = ex2_approx(x1);
               p2 = pack2(p0, p1);
             }
-#endif
             if (i & 1) lacc1 = add2(lacc1, p2); else lacc0 = add2(lacc0, p2);
             pk[i] = pack_bf16x2(p0, p1);
           }
@@ -387,9 +375,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           unpack2(lacc1, b0, b1);
           l += (a0 + a1) + (b0 + b1);
         }
-#if defined(HK_DEBUG_MINSOFTMAX)
-        }
-#endif
         HK_STAMP2(slot, 4);
         tmem_wait_st();
         tc_fence_before();

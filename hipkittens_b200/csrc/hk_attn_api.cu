@@ -56,8 +56,8 @@ EncodeTiledFn get_encode() {
 
 // Per-device state: SM count, the device status word, one-time kernel attribute set-up.
 struct DeviceState {
-  std::once_flag once;
-  int init_rc = HK_OK;
+  std::mutex mu;
+  bool ready = false;     // set once init_device succeeded; a failed attempt is retried by the next call
   int sm_count = 0;
   int cc_major = 0;
   int* status = nullptr;  // device word
@@ -140,8 +140,6 @@ int init_device(int device) {
              prop.minor);
     return HK_EUNSUPPORTED;
   }
-  HK_CUDA(cudaMalloc(&st.status, sizeof(int)));
-  HK_CUDA(cudaMemset(st.status, 0, sizeof(int)));
   int rc;
   if ((rc = prepare_fwd_kernel<128, false>()) != HK_OK) return rc;
   if ((rc = prepare_fwd_kernel<128, true>()) != HK_OK) return rc;
@@ -152,20 +150,60 @@ int init_device(int device) {
   if ((rc = prepare_bwd_kernels<128, true>()) != HK_OK) return rc;
   if ((rc = prepare_bwd_kernels<64, false>()) != HK_OK) return rc;
   if ((rc = prepare_bwd_kernels<64, true>()) != HK_OK) return rc;
+  // the one allocation this library makes: the status word (last, so that a failure above leaves nothing behind)
+  int* word = nullptr;
+  HK_CUDA(cudaMalloc(&word, sizeof(int)));
+  cudaError_t e = cudaMemset(word, 0, sizeof(int));
+  if (e != cudaSuccess) {
+    cudaFree(word);
+    return cuda_fail(e, "cudaMemset(status word)");
+  }
+  st.status = word;
   return HK_OK;
 }
 
-// Makes `device` current (when >= 0) and returns its state, initialising it on first use.
-int use_device(int device, DeviceState** out) {
-  if (device < 0) HK_CUDA(cudaGetDevice(&device));
-  if (device >= kMaxDevices) return HK_EINVAL;
-  HK_CUDA(cudaSetDevice(device));
-  DeviceState& st = g_dev[device];
-  std::call_once(st.once, [&] { st.init_rc = init_device(device); });
-  if (st.init_rc != HK_OK) return st.init_rc;
-  *out = &st;
-  return HK_OK;
-}
+// Makes a device current for the duration of one entry point and puts the caller's current device back when the
+// entry point returns (the reference launcher never touches the current device; a torch program whose current
+// device is another GPU must not find it changed).
+class DeviceScope {
+ public:
+  DeviceScope() = default;
+  DeviceScope(const DeviceScope&) = delete;
+  DeviceScope& operator=(const DeviceScope&) = delete;
+  ~DeviceScope() {
+    if (prev_ >= 0 && prev_ != cur_) cudaSetDevice(prev_);
+  }
+  // Switches to `device` (< 0: stay on the current one) and reports the index in use through *resolved.
+  int enter_raw(int device, int* resolved) {
+    HK_CUDA(cudaGetDevice(&prev_));
+    if (device < 0) device = prev_;
+    if (device >= kMaxDevices) return HK_EINVAL;
+    if (device != prev_) HK_CUDA(cudaSetDevice(device));
+    cur_ = device;
+    *resolved = device;
+    return HK_OK;
+  }
+  // enter_raw plus the device's state, initialised on first use. A failed initialisation is not remembered: the
+  // next call tries again (the failing thread finds the reason in hk_last_cuda_error()).
+  int enter(int device, DeviceState** out) {
+    int rc = enter_raw(device, &device);
+    if (rc != HK_OK) return rc;
+    DeviceState& st = g_dev[device];
+    {
+      std::lock_guard<std::mutex> lock(st.mu);
+      if (!st.ready) {
+        rc = init_device(device);
+        if (rc != HK_OK) return rc;
+        st.ready = true;
+      }
+    }
+    *out = &st;
+    return HK_OK;
+  }
+
+ private:
+  int prev_ = -1, cur_ = -1;
+};
 
 #ifdef HK_TRACE
 long long* g_trace_buf = nullptr;
@@ -173,6 +211,24 @@ int g_trace_bwd_kernel = 0;  // which backward kernel stamps: 0 = dK/dV, 1 = dQ
 #endif
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int unsupported_decode_shape(int S, int H_KV, int max_pages) {
+  snprintf(g_cuda_err, sizeof(g_cuda_err),
+           "paged decode supports S <= 65535, H_KV <= 65535 and max_pages_per_seq <= %d (got S=%d, H_KV=%d, "
+           "max_pages_per_seq=%d)", hk::kMaxCombineSplits * hk::kChunkPagesMin, S, H_KV, max_pages);
+  return HK_EUNSUPPORTED;
+}
+
+// Device status word -> HK_* code.
+int status_to_code(int word) {
+  switch (word) {
+    case hk::kStatusOk: return HK_OK;
+    case hk::kStatusSmemAlign: return HK_EUNSUPPORTED;
+    case hk::kStatusBadPage: return HK_EBADPAGE;
+    case hk::kStatusBadLen: return HK_EBADLEN;
+    default: return HK_ETIMEOUT;
+  }
+}
 
 // 4-D map over a contiguous bf16 [B, N, heads, D] tensor, box = 64 columns x 1 head x 128 rows,
 // 128-byte swizzle (rows of the box are 128 B, the layout tcgen05 descriptors expect).
@@ -288,7 +344,8 @@ int hk_attn_fwd_varlen(const void* q, const void* k, const void* v, void* o, flo
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || (reinterpret_cast<uintptr_t>(lse) & 3))
     return HK_EINVAL;
   DeviceState* st = nullptr;
-  int rc = use_device(device, &st);
+  DeviceScope scope;
+  int rc = scope.enter(device, &st);
   if (rc != HK_OK) return rc;
 
   CUtensorMap tq, tk, tv;
@@ -339,7 +396,8 @@ int hk_attn_bwd_prep(const void* o, const void* d_o, float* delta, int B, int N,
   if (D != 64 && D != 128) return HK_EUNSUPPORTED;
   if (!aligned16(o) || !aligned16(d_o) || (reinterpret_cast<uintptr_t>(delta) & 3)) return HK_EINVAL;
   DeviceState* st = nullptr;
-  int rc = use_device(device, &st);
+  DeviceScope scope;
+  int rc = scope.enter(device, &st);
   if (rc != HK_OK) return rc;
   const long long rows = static_cast<long long>(B) * N * H;
   const int rows_per_block = 8 * (32 / (D / 8));  // 8 warps, D/8 lanes per row
@@ -376,7 +434,8 @@ int hk_attn_bwd_varlen(const void* q, const void* k, const void* v, const void* 
       !aligned16(dv) || (reinterpret_cast<uintptr_t>(lse) & 3) || (reinterpret_cast<uintptr_t>(delta) & 3))
     return HK_EINVAL;
   DeviceState* st = nullptr;
-  int rc = use_device(device, &st);
+  DeviceScope scope;
+  int rc = scope.enter(device, &st);
   if (rc != HK_OK) return rc;
 
   const long long qs[3] = {(long long)N * H * D, (long long)H * D, D};
@@ -428,7 +487,8 @@ int hk_attn_dq_shuffle(const void* dq_bhnd, void* dq_bnhd, int B, int N, int H, 
   if (B <= 0 || N <= 0 || H <= 0 || D <= 0 || D % 8 != 0) return HK_EINVAL;
   if (!aligned16(dq_bhnd) || !aligned16(dq_bnhd)) return HK_EINVAL;
   DeviceState* st = nullptr;
-  int rc = use_device(device, &st);
+  DeviceScope scope;
+  int rc = scope.enter(device, &st);
   if (rc != HK_OK) return rc;
   const int vec = D / 8;
   const long long total = static_cast<long long>(B) * N * H * vec;
@@ -449,7 +509,8 @@ int hk_rotary(const void* x, void* o, const void* sin, const void* cos, int B, i
   if (D % 8 != 0 || rotary_dim % 16 != 0 || rotary_dim > D) return HK_EUNSUPPORTED;
   if (!aligned16(x) || !aligned16(o) || !aligned16(sin) || !aligned16(cos)) return HK_EINVAL;
   DeviceState* st = nullptr;
-  int rc = use_device(device, &st);
+  DeviceScope scope;
+  int rc = scope.enter(device, &st);
   if (rc != HK_OK) return rc;
   hk::RotaryParams p;
   p.x = static_cast<const __nv_bfloat16*>(x);
@@ -484,10 +545,12 @@ int hk_attn_paged_decode(const void* q, const void* k_pages, const void* v_pages
   const int G = H / H_KV;
   if (G < 1 || G > 8) return HK_EUNSUPPORTED;  // the heads of a group sit in the 8 usable rows of one MMA tile
   if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(o)) return HK_EINVAL;
+  if (!hk::decode_shape_supported(S, H_KV, max_pages_per_seq)) return unsupported_decode_shape(S, H_KV, max_pages_per_seq);
   const size_t need = hk::decode_workspace_bytes(S, H, D, max_pages_per_seq, page_size);
   if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)) return HK_EWORKSPACE;
   DeviceState* st = nullptr;
-  int rc = use_device(device, &st);
+  DeviceScope scope;
+  int rc = scope.enter(device, &st);
   if (rc != HK_OK) return rc;
   hk::DecodeParams p;
   p.q = static_cast<const __nv_bfloat16*>(q);
@@ -522,7 +585,8 @@ int hk_paged_kv_append(const void* k_new, const void* v_new, void* k_pages, void
   if ((H_KV * D) % 8 != 0 || T > 65535 || S > 65535) return HK_EINVAL;
   if (!aligned16(k_new) || !aligned16(v_new) || !aligned16(k_pages) || !aligned16(v_pages)) return HK_EINVAL;
   DeviceState* st = nullptr;
-  int rc = use_device(device, &st);
+  DeviceScope scope;
+  int rc = scope.enter(device, &st);
   if (rc != HK_OK) return rc;
   hk::AppendParams p;
   p.k_new = static_cast<const __nv_bfloat16*>(k_new);
@@ -548,20 +612,20 @@ int hk_paged_kv_append(const void* k_new, const void* v_new, void* k_pages, void
 
 int hk_last_device_status(int device) {
   DeviceState* st = nullptr;
-  int rc = use_device(device, &st);
+  DeviceScope scope;
+  int rc = scope.enter(device, &st);
   if (rc != HK_OK) return rc;
   HK_CUDA(cudaDeviceSynchronize());
   int word = 0;
   HK_CUDA(cudaMemcpy(&word, st->status, sizeof(int), cudaMemcpyDeviceToHost));
   if (word != 0) HK_CUDA(cudaMemset(st->status, 0, sizeof(int)));
-  if (word == hk::kStatusOk) return HK_OK;
-  if (word == hk::kStatusSmemAlign) return HK_EUNSUPPORTED;
-  return word == hk::kStatusBadPage ? HK_EBADPAGE : HK_ETIMEOUT;
+  return status_to_code(word);
 }
 
 int hk_selftest_bounded_wait(int device, unsigned limit_us) {
   DeviceState* st = nullptr;
-  int rc = use_device(device, &st);
+  DeviceScope scope;
+  int rc = scope.enter(device, &st);
   if (rc != HK_OK) return rc;
   if (limit_us == 0 || limit_us > 1000000u) return HK_EINVAL;
   bounded_wait_selftest_kernel<<<1, 32>>>(st->status, static_cast<unsigned long long>(limit_us) * 1000ull);
@@ -581,6 +645,7 @@ const char* hk_strerror(int code) {
     case HK_ETIMEOUT: return "bounded device-side wait expired";
     case HK_EWORKSPACE: return "workspace missing, misaligned or too small";
     case HK_EBADPAGE: return "block-table entry outside the page pool";
+    case HK_EBADLEN: return "context length beyond the block table's capacity (clamped)";
     default: return "unknown error code";
   }
 }
@@ -600,8 +665,8 @@ static __device__ int g_decode_static_status;
 namespace {
 
 struct StaticDecodeState {
-  std::once_flag once;
-  int init_rc = HK_OK;
+  std::mutex mu;
+  bool ready = false;       // a failed set-up is retried by the next call
   int sm_count = 0;
   void* scratch = nullptr;  // device address of g_decode_static_scratch on this device
   int* status = nullptr;    // device address of g_decode_static_status on this device
@@ -642,6 +707,7 @@ extern "C" int hk_attn_paged_decode_static(const void* q, const void* k_pages, c
   const int G = H / H_KV;
   if (G < 1 || G > 8) return HK_EUNSUPPORTED;  // the heads of a group sit in the 8 usable rows of one MMA tile
   if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(o)) return HK_EINVAL;
+  if (!hk::decode_shape_supported(S, H_KV, max_pages_per_seq)) return unsupported_decode_shape(S, H_KV, max_pages_per_seq);
   const size_t need = hk::decode_workspace_bytes(S, H, D, max_pages_per_seq, page_size);
   if (need == 0 || need > HK_DECODE_STATIC_SCRATCH_BYTES) {
     snprintf(g_cuda_err, sizeof(g_cuda_err),
@@ -649,12 +715,20 @@ extern "C" int hk_attn_paged_decode_static(const void* q, const void* k_pages, c
              unsigned(HK_DECODE_STATIC_SCRATCH_BYTES));
     return HK_EWORKSPACE;
   }
-  if (device < 0) HK_CUDA(cudaGetDevice(&device));
-  if (device >= kMaxDevices) return HK_EINVAL;
-  HK_CUDA(cudaSetDevice(device));
+  DeviceScope scope;  // the caller's current device is put back on return
+  {
+    const int rc = scope.enter_raw(device, &device);
+    if (rc != HK_OK) return rc;
+  }
   StaticDecodeState& st = g_static_dev[device];
-  std::call_once(st.once, [&] { st.init_rc = init_static_decode(device); });
-  if (st.init_rc != HK_OK) return st.init_rc;
+  {
+    std::lock_guard<std::mutex> lock(st.mu);
+    if (!st.ready) {
+      const int rc = init_static_decode(device);
+      if (rc != HK_OK) return rc;
+      st.ready = true;
+    }
+  }
 
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   // the status word is shared by all calls and keeps the last call's value: start this call from zero
@@ -684,7 +758,7 @@ extern "C" int hk_attn_paged_decode_static(const void* q, const void* k_pages, c
     int word = 0;
     HK_CUDA(cudaMemcpyAsync(&word, st.status, sizeof(int), cudaMemcpyDeviceToHost, stream));
     HK_CUDA(cudaStreamSynchronize(stream));
-    *status_out = (word == hk::kStatusOk) ? HK_OK : (word == hk::kStatusBadPage ? HK_EBADPAGE : HK_ETIMEOUT);
+    *status_out = status_to_code(word);
   }
   return HK_OK;
 }

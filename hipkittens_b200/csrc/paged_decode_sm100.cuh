@@ -32,7 +32,7 @@ constexpr int kStageBytes = 2 * kSlabBytes;           // K slab + V slab
 constexpr int kDecodeSmemBytes = kDecodeWarps * kDecodeStages * kStageBytes;  // 96 KB
 constexpr int kMaxCombineSplits = 256;
 
-enum : int { kStatusBadPage = 2 };
+enum : int { kStatusBadPage = 2, kStatusBadLen = 4 };  // 3 is the backward kernels' kStatusSmemAlign
 
 struct DecodeParams {
   const __nv_bfloat16* q;        // [S,1,H,128]
@@ -61,8 +61,16 @@ inline int decode_pick_chunk_pages(int S, int H_KV, int max_pages, int sm_count)
   return ctas >= 4ll * sm_count ? kChunkPagesMax : kChunkPagesMin;
 }
 // Workspace: partial O as fp32 [S][H][splits][128], then (m, l) pairs as fp32 [S][H][splits][2].
+// Shapes the two kernels can be launched for: the combine kernel holds one weight per split in shared memory
+// (kMaxCombineSplits of them, counted for the smaller chunk size so that either chunk choice fits), and sequences
+// and kv heads are grid dimensions y and z.
+inline bool decode_shape_supported(int S, int H_KV, int max_pages) {
+  return S > 0 && S <= 65535 && H_KV > 0 && H_KV <= 65535 && max_pages > 0 &&
+         decode_max_splits(max_pages) <= kMaxCombineSplits;
+}
 inline size_t decode_workspace_bytes(int S, int H, int D, int max_pages, int page_size) {
-  if (S <= 0 || H <= 0 || D != kDecodeD || page_size != kPageTokens || max_pages <= 0) return 0;
+  if (S <= 0 || S > 65535 || H <= 0 || D != kDecodeD || page_size != kPageTokens || max_pages <= 0) return 0;
+  if (decode_max_splits(max_pages) > kMaxCombineSplits) return 0;
   const size_t splits = decode_max_splits(max_pages);
   const size_t o_bytes = size_t(S) * H * splits * kDecodeD * sizeof(float);
   const size_t ml_bytes = size_t(S) * H * splits * 2 * sizeof(float);
@@ -107,7 +115,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_split_kernel(c
   using namespace dec;
   extern __shared__ __align__(128) uint8_t dsmem[];
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
-  const int ctx = p.ctx_lens[seq];
+  // A length beyond what the block-table row can address is clamped to the row's capacity and reported; nothing
+  // past the row is read.
+  int ctx = p.ctx_lens[seq];
+  if (ctx > p.max_pages * kPageTokens) {
+    ctx = p.max_pages * kPageTokens;
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, kStatusBadLen);
+  }
   const int chunk_tokens = p.chunk_pages * kPageTokens;
   const int tok0 = split * chunk_tokens;
   if (tok0 >= ctx) return;
@@ -303,7 +317,7 @@ __global__ void __launch_bounds__(kDecodeD) paged_decode_combine_kernel(const De
   // partials are visible (a no-op under an ordinary launch)
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const int head = blockIdx.x, seq = blockIdx.y;
-  const int ctx = p.ctx_lens[seq];
+  const int ctx = min(p.ctx_lens[seq], p.max_pages * kPageTokens);  // clamped as in the split kernel, which reports it
   const int d = threadIdx.x;
   if (ctx <= 0) {  // defined output for an empty context
     p.o[(size_t(seq) * p.H + head) * kDecodeD + d] = __float2bfloat16(0.f);

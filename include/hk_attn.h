@@ -4,6 +4,11 @@
  * otherwise. Every function returns 0 on success or a negative HK_E* code; none aborts or throws.
  * Kernels are launched asynchronously on `cuda_stream` (NULL = the legacy default stream), exactly as
  * the reference launcher does (kernels/attn/gqa/kernel.cpp:576-581).
+ * `device` is the CUDA device index the pointers live on (< 0 = the calling thread's current device). An entry
+ * point makes that device current while it runs and puts the caller's current device back before it returns.
+ * The first call on a device sets the kernels' attributes and allocates one 4-byte status word there (the only
+ * allocation the library makes; hk_attn_paged_decode_static does not need it); if that set-up fails the call
+ * returns the error and the next call tries again.
  */
 #ifndef HK_ATTN_H_
 #define HK_ATTN_H_
@@ -22,6 +27,7 @@ extern "C" {
 #define HK_ETIMEOUT (-4)     /* a bounded device-side wait expired; results are invalid */
 #define HK_EWORKSPACE (-5)   /* workspace missing or too small */
 #define HK_EBADPAGE (-6)     /* a block-table entry outside [0, num_pages) was met; it was not dereferenced */
+#define HK_EBADLEN (-7)      /* a context length beyond max_pages_per_seq * page_size was met; it was clamped */
 
 /* Attention forward.
  * Replaces dispatch_micro<D>(attn_globals<D>) (kernels/attn/gqa/kernel.cpp:93-100,576-581, causal twin
@@ -62,8 +68,11 @@ int hk_attn_fwd_varlen(const void* q, const void* k, const void* v, void* o, flo
  *   k_pages, v_pages : bf16 [num_pages, page_size, H_KV, D]
  *   block_table : int32 [S, max_pages_per_seq]; token j of sequence s is row j % page_size of page
  *                 block_table[s, j / page_size]; entries must lie in [0, num_pages)
- *   ctx_lens    : int32 [S], 1 <= ctx_lens[s] <= max_pages_per_seq * page_size
- *   D = 128, page_size = 16, H / H_KV from 1 to 8.
+ *   ctx_lens    : int32 [S], 1 <= ctx_lens[s] <= max_pages_per_seq * page_size. A larger value is clamped to
+ *                 that capacity on the device (nothing beyond the block-table row is read) and reported as
+ *                 HK_EBADLEN by hk_last_device_status; a value <= 0 gives O = 0 and L = -inf.
+ *   D = 128, page_size = 16, H / H_KV from 1 to 8; S and H_KV at most 65535, max_pages_per_seq at most 8192
+ *   (HK_EUNSUPPORTED beyond, and hk_attn_paged_decode_workspace_bytes then returns 0).
  *   workspace   : device scratch of at least hk_attn_paged_decode_workspace_bytes(...) bytes, 256-byte
  *                 aligned; holds the per-split partial results between the two kernels. */
 size_t hk_attn_paged_decode_workspace_bytes(int S, int H, int D, int max_pages_per_seq, int page_size);
@@ -149,17 +158,22 @@ int hk_paged_kv_append(const void* k_new, const void* v_new, void* k_pages, void
  * synchronisation. hk_attn_paged_decode() makes such callers bring a workspace (and its first call on a device
  * allocates a status word); this variant brings its own: the per-chunk partial results live in a fixed
  * HK_DECODE_STATIC_SCRATCH_BYTES array that is part of the library image, so every GPU that loads the library
- * holds that much memory until the process exits, whether or not this function is ever called. It calls no
- * cudaMalloc / cudaFree and no allocating library routine.
+ * holds that much memory until the process exits. (With CUDA's default lazy module loading the array takes its
+ * place in device memory when the library's kernels are first used on that device - by any entry point, this
+ * one included - not when the shared object is loaded; an engine that is about to claim all remaining HBM
+ * should therefore make one call on each device first.) It calls no cudaMalloc / cudaFree and no allocating
+ * library routine.
  *
  * Same arguments and results as hk_attn_paged_decode() minus the workspace, plus `status_out`:
  *   status_out  HOST pointer or NULL. When given, the call waits for its own kernels on `cuda_stream` and stores
- *               HK_OK or HK_EBADPAGE there; with NULL the call is asynchronous and the status is dropped.
+ *               HK_OK, HK_EBADPAGE or HK_EBADLEN there; with NULL the call is asynchronous and the status is
+ *               dropped. Pass NULL while `cuda_stream` is being captured: the wait is a stream synchronisation,
+ *               which a capturing stream refuses (HK_ECUDA).
  * Limit: hk_attn_paged_decode_workspace_bytes(S, H, D, max_pages_per_seq, page_size) must not exceed
  * HK_DECODE_STATIC_SCRATCH_BYTES (e.g. S=16, H=64 at up to 7680 tokens per sequence); larger problems are
  * refused with HK_EWORKSPACE before anything is launched - use hk_attn_paged_decode() for them.
- * The first call on each device looks up the device address of the array (one-time set-up, under a lock); make
- * that first call before any stream capture begins.
+ * The first call on each device looks up the device address of the array (one-time set-up, under a lock; a
+ * failed set-up is retried by the next call); make that first call before any stream capture begins.
  * All calls on a device share the one array: it still holds the previous call's partials (every value a call
  * reads it has written first, and the status word is cleared on the stream at the start of each call), and two
  * calls whose kernels overlap on the GPU - different streams, or different host threads - race on it. Serialise them. */
@@ -170,7 +184,7 @@ int hk_attn_paged_decode_static(const void* q, const void* k_pages, const void* 
                                 float softmax_scale, int device, void* cuda_stream, int* status_out);
 
 /* Synchronises `device` and reports the device-side status word of the kernels above: HK_OK,
- * HK_ETIMEOUT when a bounded wait inside a kernel expired, or HK_EBADPAGE. The word is cleared on read.
+ * HK_ETIMEOUT when a bounded wait inside a kernel expired, HK_EBADPAGE or HK_EBADLEN. The word is cleared on read.
  * The reference launchers check nothing after launch (include/pyutils/util.cuh:6-16). */
 int hk_last_device_status(int device);
 
@@ -186,6 +200,14 @@ unsigned long long hk_kernel_launch_count(void);
 /* Text for an HK_* code, and the text of the last CUDA error seen by the calling thread. */
 const char* hk_strerror(int code);
 const char* hk_last_cuda_error(void);
+
+#ifdef HK_TRACE
+/* Tuning builds only (the library compiled with -DHK_TRACE; the shipped build has neither symbol): the prefill
+ * kernels' first CTA appends (event, SM clock) pairs per role to `buf`, a device array of 3 x 4096 int64, or
+ * stamps nothing when buf is NULL. For the backward, `which` selects the kernel that stamps (0 dK/dV, 1 dQ). */
+void hk_debug_set_trace(long long* buf);
+void hk_debug_set_trace_bwd_kernel(int which);
+#endif
 
 #ifdef __cplusplus
 }

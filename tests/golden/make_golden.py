@@ -140,6 +140,54 @@ def rotary_main() -> None:
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def lse_pin_main() -> None:
+    """Pin L by the reference code that CONSUMES it: ``simple_flash_backward(Q, K, V, dO, L)`` of the backward
+    harness (kernels/attn/gqa_backwards/test_python.py:100-137) recomputes P = exp(Q K^T scale - L) from a saved L
+    and derives dQ, dK, dV from that P. The function and its helper ``expand_kv_for_gqa`` (test_python.py:74-80) are
+    taken out of the harness source with ``ast`` (the file imports its compiled modules and AITER at the top) and
+    run in fp64 on the non-causal fixtures' inputs (the function applies no mask) with the L this repository's
+    oracle computes. Stored per case in ``lpin_<case>.npz``:
+      lse_fed      the L that was fed in, fp32 [B,H,N] (natural log, scaled logits)
+      p_rowsum     row sums of the function's own P: its Delta output for V = 1, dO = 1/D (then O = rowsum(P) in
+                   every column and Delta = sum_d dO * O = rowsum(P)); 1 exactly iff L is what the function expects
+      dq/dk/dv     its gradients for the fixture's dO, to be compared with the module's autograd gradients that
+                   the case_*.npz files already hold
+    """
+    import ast
+
+    ref_root = reference_root()
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from oracle.attn_oracle import attn_fwd_oracle
+
+    src = open(os.path.join(ref_root, "kernels", "attn", "gqa_backwards", "test_python.py")).read()
+    tree = ast.parse(src)
+    wanted = [n for n in tree.body
+              if isinstance(n, ast.FunctionDef) and n.name in ("expand_kv_for_gqa", "simple_flash_backward")]
+    assert len(wanted) == 2
+    for name, b, n, h, hkv, d, causal, _seed in CASES:
+        if causal:
+            continue
+        z = np.load(os.path.join(HERE, f"case_{name}.npz"))
+        unbits = lambda a: torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16)  # noqa: E731
+        q, k, v, d_o = (unbits(z[key]) for key in ("q", "k", "v", "d_o"))
+        _o, lse = attn_fwd_oracle(q, k, v, False)                    # [B,H,1,N] fp32
+        lse_bhn = lse[:, :, 0, :].contiguous()
+        ns = {"torch": torch, "math": math, "h_q": h, "h_kv": hkv}
+        exec(compile(ast.Module(body=wanted, type_ignores=[]), "gqa_backwards_harness_functions", "exec"), ns)
+        sfb = ns["simple_flash_backward"]
+        to_bhnd = lambda t: t.double().permute(0, 2, 1, 3).contiguous()  # noqa: E731
+        qd, kd, vd, dod = to_bhnd(q), to_bhnd(k), to_bhnd(v), to_bhnd(d_o)
+        _dq1, _dk1, _dv1, rowsum = sfb(qd, kd, torch.ones_like(vd), torch.full_like(dod, 1.0 / d), lse_bhn.double())
+        dq, dk, dv, _delta = sfb(qd, kd, vd, dod, lse_bhn.double())
+        path = os.path.join(HERE, f"lpin_{name}.npz")
+        np.savez_compressed(path, lse_fed=lse_bhn.numpy(), p_rowsum=rowsum[..., 0].numpy(),
+                            dq=dq.permute(0, 2, 1, 3).float().numpy(), dk=dk.permute(0, 2, 1, 3).float().numpy(),
+                            dv=dv.permute(0, 2, 1, 3).float().numpy())
+        print("wrote", path, os.path.getsize(path), "bytes; max |rowsum(P) - 1| =",
+              float((rowsum - 1).abs().max()))
+
+
 if __name__ == "__main__":
     main()
     rotary_main()
+    lse_pin_main()

@@ -87,6 +87,27 @@ def test_parity_against_reference_module_outputs(dev, path):
     assert float((l[:, :, 0, :] - torch.from_numpy(z["lse_def_fp64"]).float()).abs().max()) <= TOL_L
 
 
+LPIN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "lpin_*.npz")))
+
+
+@pytest.mark.parametrize("path", LPIN, ids=[os.path.basename(p) for p in LPIN])
+def test_lse_against_the_l_the_reference_backward_consumed(dev, path):
+    """The fixture's L was accepted by the reference's own simple_flash_backward (rows of its exp(S - L) sum to one
+    and its gradients equal the module's; tests/test_oracle.py). The kernel's L must be that L within 1e-3, and the
+    same check the fixture passed is repeated on the kernel's L itself: rows of exp(scale q k^T - L) sum to one."""
+    z = np.load(path)
+    case = np.load(path.replace("lpin_", "case_"))
+    b, n, h, hkv, d, _causal, _seed = [int(x) for x in case["shape"]]
+    bf = lambda a: torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16)  # noqa: E731
+    q, k, v = bf(case["q"]).reshape(b, n, h, d), bf(case["k"]).reshape(b, n, hkv, d), bf(case["v"]).reshape(b, n, hkv, d)
+    _o, l = run_fwd(q, k, v, False, dev)
+    assert float((l[:, :, 0, :] - torch.from_numpy(z["lse_fed"])).abs().max()) <= TOL_L
+    kk = k.double().repeat_interleave(h // hkv, dim=2)
+    s = torch.einsum("bthd,bshd->bhts", q.double(), kk) / math.sqrt(d)
+    rowsum = torch.exp(s - l[:, :, 0, :].double().unsqueeze(-1)).sum(-1)
+    assert float((rowsum - 1).abs().max()) <= TOL_L
+
+
 def test_through_reference_entry_points(dev):
     """tk_kernel.dispatch_micro and tk_kernel_fwd.dispatch_fwd, called as the reference's harness and
     training code call them (kernels/attn/gqa/test_python.py:97-102, hipkittens.py:43-51)."""
@@ -308,3 +329,23 @@ def test_bounded_wait_reports_timeout_and_context_survives(dev):
     q, k, v = make_prefill_inputs(1, 128, 2, 1, 64, seed=18)
     o, l = run_fwd(q, k, v, False, dev)
     assert_parity(o, l, *attn_fwd_oracle(q, k, v, False))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two visible GPUs")
+def test_callers_current_device_is_left_alone():
+    """A call on another GPU's tensors must not change the calling thread's current device (the reference
+    launcher never touches it): torch's current device and stream stay what they were."""
+    torch.cuda.set_device(0)
+    try:
+        other = torch.device("cuda:1")
+        q, k, v = (t.to(other) for t in make_prefill_inputs(1, 256, 4, 2, 128, seed=3))
+        o, l = hk.attn_fwd(q, k, v, causal=True)
+        assert torch.cuda.current_device() == 0
+        assert _native.device_status(1) == 0
+        assert torch.cuda.current_device() == 0
+        o_ref, l_ref = attn_fwd_oracle(q.cpu(), k.cpu(), v.cpu(), True)
+        assert float((o.float().cpu() - o_ref.float()).abs().max()) <= TOL_O
+        # the runtime's own view, not just torch's cached one: a fresh allocation lands on device 0
+        assert torch.ones(4, device="cuda").device.index == 0
+    finally:
+        torch.cuda.set_device(0)

@@ -51,6 +51,30 @@ def test_oracle_matches_reference_module(path):
         assert float((o.float() - o_nat.float()).abs().max()) <= 2e-2
 
 
+LPIN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "lpin_*.npz")))
+
+
+@pytest.mark.parametrize("path", LPIN, ids=[os.path.basename(p) for p in LPIN])
+def test_lse_is_what_the_reference_backward_harness_consumes(path):
+    """L is pinned by the reference code that uses it: the backward harness's simple_flash_backward
+    (kernels/attn/gqa_backwards/test_python.py:100-137) recomputes P = exp(S - L); the fixture holds what that
+    function, taken from the harness source and run on the oracle's L, returned. (i) the L stored there is the L the
+    oracle computes now; (ii) rows of the function's P sum to one; (iii) its gradients are the reference module's
+    autograd gradients. A wrong base of the logarithm, a missing scale or a transposed layout fails (ii) and (iii)."""
+    z = np.load(path)
+    case = np.load(path.replace("lpin_", "case_"))
+    b, n, h, hkv, d, causal, _seed = [int(x) for x in case["shape"]]
+    assert not causal  # the harness function applies no mask
+    q, k, v = _bf16(case["q"]), _bf16(case["k"]), _bf16(case["v"])
+    _o, lse = attn_fwd_oracle(q, k, v, causal=False)
+    assert z["lse_fed"].shape == (b, h, n)
+    assert float((lse[:, :, 0, :] - torch.from_numpy(z["lse_fed"])).abs().max()) <= 1e-6
+    assert float(np.abs(z["p_rowsum"] - 1.0).max()) <= 1e-6
+    for name in ("dq", "dk", "dv"):
+        ref = case[name + "_ref_fp32"]
+        assert float(np.abs(z[name] - ref).max()) <= 2e-5 * float(np.abs(ref).max())
+
+
 def test_generators_reproduce_golden_inputs():
     z = np.load([p for p in GOLDEN if "c1_" in p][0])
     b, n, h, hkv, d, _c, seed = [int(x) for x in z["shape"]]

@@ -101,6 +101,50 @@ def test_out_of_range_page_id_is_reported_not_dereferenced(dev):
     assert float((o.float() - o_ref.float()).abs().max()) <= TOL_O
 
 
+def test_context_length_beyond_the_block_table_is_clamped_and_reported(dev):
+    """ctx_lens is device data the host never reads: a length above max_pages * 16 must not make the kernels walk
+    past the block-table row. It is clamped to the row's capacity, reported as HK_EBADLEN, and the result equals the
+    result for the clamped length."""
+    q, kp, vp, bt, cl = make_paged_inputs(3, 8, 2, 128, 16, 400, 900, 1500, seed=31)
+    cap = bt.shape[1] * 16
+    cl_full = cl.clone()
+    cl_full[-1] = cap                       # the last sequence's row is the end of the block-table buffer
+    o_ref, l_ref = run_decode(q, kp, vp, bt, cl_full, dev)
+    for excess in (1, 5000, 2 ** 30):
+        cl_bad = cl_full.clone()
+        cl_bad[-1] = cap + excess
+        s, _, h, d = q.shape
+        ws = torch.empty(hk.paged_decode_workspace_bytes(s, h, d, bt.shape[1]), dtype=torch.uint8, device=dev)
+        o, l = hk.paged_decode(q.to(dev), kp.to(dev), vp.to(dev), bt.to(dev), cl_bad.to(dev), workspace=ws)
+        assert _native.device_status(0) == _native.HK_EBADLEN
+        assert torch.equal(o.cpu(), o_ref) and torch.equal(l.cpu(), l_ref)
+    # the status word is cleared on read and a clean call is clean again
+    run_decode(q, kp, vp, bt, cl_full, dev)
+
+
+def test_unsupported_shapes_are_refused_before_any_launch(dev):
+    assert hk.paged_decode_workspace_bytes(2, 8, 128, 8192) > 0
+    assert hk.paged_decode_workspace_bytes(2, 8, 128, 8193) == 0     # more than 256 chunks of 32 pages
+    assert hk.paged_decode_workspace_bytes(70000, 8, 128, 64) == 0   # sequences are a grid dimension
+    q, kp, vp, bt, cl = make_paged_inputs(1, 8, 1, 128, 16, 40, 100, 200, seed=32)
+    wide = torch.zeros((1, 8200), dtype=torch.int32, device=dev)
+    before = hk.kernel_launch_count()
+    rc = hk.capi().hk_attn_paged_decode(q.to(dev).data_ptr(), kp.to(dev).data_ptr(), vp.to(dev).data_ptr(),
+                                        wide.data_ptr(), cl.to(dev).data_ptr(), q.to(dev).data_ptr(),
+                                        torch.empty(8, device=dev).data_ptr(), 1, 8, 1, 128, 16, 8200, 40, 0.0,
+                                        torch.empty(1 << 20, dtype=torch.uint8, device=dev).data_ptr(), 1 << 20, 0, None)
+    assert rc == _native.HK_EUNSUPPORTED and hk.kernel_launch_count() == before
+    assert b"max_pages_per_seq" in hk.capi().hk_last_cuda_error()
+
+
+def test_host_tensors_are_rejected_by_the_front_end(dev):
+    q, kp, vp, bt, cl = make_paged_inputs(1, 8, 1, 128, 16, 40, 100, 200, seed=33)
+    with pytest.raises(RuntimeError, match="block_table must be a tensor on cuda"):
+        hk.paged_decode(q.to(dev), kp.to(dev), vp.to(dev), bt, cl.to(dev))   # bt left on the host
+    with pytest.raises(RuntimeError, match="ctx_lens must be a tensor on cuda"):
+        hk.paged_decode(q.to(dev), kp.to(dev), vp.to(dev), bt.to(dev), cl)
+
+
 def test_full_size_configuration(dev):
     """BASELINE config 5: 64 sequences, ctx ~ U{512..8192}, H=64, H_KV=8, D=128, 40 000-page pool."""
     q, kp, vp, bt, cl = make_paged_inputs(64, 64, 8, 128, 16, 40000, 512, 8192, seed=0, pool_on="cuda:0")

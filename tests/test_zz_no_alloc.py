@@ -2,11 +2,15 @@
 engine that gave all of HBM to its own allocator; a decode loop that must never hit cudaMalloc's device-wide
 synchronisation). Its scratch is a fixed array inside the library, so the things to check are that it computes
 exactly what hk_attn_paged_decode computes, that a second call is not disturbed by what the first one left in
-the shared array, and that problems beyond the array's size are refused.
+the shared array, that problems beyond the array's size are refused, and that the device's free memory is the
+same before and after warm calls.
 
 Collected last on purpose (file name): if it fails under -x every other test has already run.
 """
 import ctypes
+import os
+import subprocess
+import sys
 
 import pytest
 import torch
@@ -88,3 +92,51 @@ def test_problems_beyond_the_built_in_array_are_refused():
                                          ctypes.byref(status))
     assert rc == _native.HK_EWORKSPACE and status.value == -99
     assert b"built-in array" in lib.hk_last_cuda_error()
+
+
+def test_warm_calls_leave_the_free_device_memory_unchanged():
+    """The property in the entry point's name: once the first call on the device has happened, later calls take
+    nothing from the device's memory. The driver's own count of free bytes is read before and after the second and
+    third call (torch's caching allocator is not involved: the call gets raw pointers)."""
+    dev = torch.device("cuda:0")
+    lib = hk.capi()
+    q, kp, vp, bt, cl = _problem(dev, 6, 16, 2, 900, 600, 2000, 25)
+    o = torch.empty_like(q)
+    l = torch.empty((6, 16, 1, 1), dtype=torch.float32, device=dev)
+    rc, status = _call_static(lib, q, kp, vp, bt, cl, o, l)   # first call: one-time set-up may happen here
+    assert rc == 0 and status == 0
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info(dev)[0]
+    for _ in range(2):
+        rc, status = _call_static(lib, q, kp, vp, bt, cl, o, l)
+        assert rc == 0 and status == 0
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info(dev)[0] == free_before
+
+
+def test_static_entry_as_the_first_library_call_of_a_process():
+    """In a fresh process the static entry is the first hk_* call on the device, so its own set-up (address
+    look-up of the built-in array, kernel attributes) is what runs, not the ordinary entry's. The child also checks
+    that the caller's current device is what it was."""
+    code = r"""
+import ctypes, sys, torch
+sys.path.insert(0, %r)
+import hipkittens_b200 as hk
+from hipkittens_b200.synthetic import make_paged_inputs
+dev = torch.device("cuda:0")
+q, kp, vp, bt, cl = [t.to(dev) for t in make_paged_inputs(3, 8, 1, 128, 16, 400, 1, 1500, 22)]
+o = torch.empty_like(q); l = torch.empty((3, 8, 1, 1), dtype=torch.float32, device=dev)
+lib = hk.capi()
+assert lib.hk_kernel_launch_count() == 0
+status = ctypes.c_int(-99)
+rc = lib.hk_attn_paged_decode_static(q.data_ptr(), kp.data_ptr(), vp.data_ptr(), bt.data_ptr(), cl.data_ptr(),
+        o.data_ptr(), l.data_ptr(), 3, 8, 1, 128, 16, bt.shape[1], kp.shape[0], 0.0, 0,
+        torch.cuda.current_stream(dev).cuda_stream, ctypes.byref(status))
+assert rc == 0 and status.value == 0, (rc, status.value, lib.hk_last_cuda_error())
+o_ref, l_ref = hk.paged_decode(q, kp, vp, bt, cl)
+torch.cuda.synchronize()
+assert torch.equal(o, o_ref) and torch.equal(l, l_ref)
+print("ok")
+""" % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and out.stdout.strip().endswith("ok"), out.stdout + out.stderr
