@@ -24,9 +24,11 @@ EXPORTED_SYMBOLS = (
     "hk_attn_fwd",
     "hk_attn_fwd_strided",
     "hk_attn_fwd_varlen",
+    "hk_attn_fwd_cross",
     "hk_attn_bwd_prep",
     "hk_attn_bwd",
     "hk_attn_bwd_varlen",
+    "hk_attn_bwd_cross",
     "hk_attn_dq_shuffle",
     "hk_rotary",
     "hk_attn_paged_decode_workspace_bytes",
@@ -78,12 +80,16 @@ def capi() -> ctypes.CDLL:
     lib.hk_attn_fwd_strided.restype = ci
     lib.hk_attn_fwd_varlen.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ll3, ll3, ll3, vp, ci, cf, ci, vp]
     lib.hk_attn_fwd_varlen.restype = ci
+    lib.hk_attn_fwd_cross.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ll3, ll3, ll3, vp, ci, cf, ci, vp]
+    lib.hk_attn_fwd_cross.restype = ci
     lib.hk_attn_bwd_prep.argtypes = [vp, vp, vp, ci, ci, ci, ci, ci, vp]
     lib.hk_attn_bwd_prep.restype = ci
     lib.hk_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, cf, ci, ci, vp]
     lib.hk_attn_bwd.restype = ci
     lib.hk_attn_bwd_varlen.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, ci, cf, ci, ci, vp]
     lib.hk_attn_bwd_varlen.restype = ci
+    lib.hk_attn_bwd_cross.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp, ci, cf, ci, ci, vp]
+    lib.hk_attn_bwd_cross.restype = ci
     lib.hk_attn_dq_shuffle.argtypes = [vp, vp, ci, ci, ci, ci, ci, vp]
     lib.hk_attn_dq_shuffle.restype = ci
     lib.hk_rotary.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]
@@ -161,11 +167,13 @@ def attn_fwd(
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """O = softmax(scale q k^T) v and L = logsumexp(scale q k^T) on the GPU.
 
-    q [B,N,H,D] bf16, k/v [B,N,H_KV,D] bf16 CUDA tensors, contiguous or strided views with a contiguous
-    last dimension (e.g. slices of a packed qkv projection; no copy is made); returns O [B,N,H,D] bf16 and
-    L [B,H,1,N] fp32 (the layouts of kernels/attn/gqa/test_python.py:97-98). Asynchronous on `stream`
-    (default: torch's current stream). `kv_lens` (int32 [B], non-causal only) restricts batch element b to its
-    first kv_lens[b] keys, the reference's key_padding_mask (base.py:97-103).
+    q [B,N,H,D] bf16, k/v [B,Nk,H_KV,D] bf16 CUDA tensors (Nk may differ from N), contiguous or strided views with
+    a contiguous last dimension (e.g. slices of a packed qkv projection; no copy is made); returns O [B,N,H,D] bf16
+    and L [B,H,1,N] fp32 (the layouts of kernels/attn/gqa/test_python.py:97-98). Asynchronous on `stream`
+    (default: torch's current stream). `kv_lens` (int32 [B]) restricts batch element b to its first kv_lens[b]
+    keys, the reference's key_padding_mask (base.py:97-103). With `causal`, query row r sees keys up to
+    r + (kv_len_b - N): the mask is aligned to the last query and the last kept key as in base.py:104-116; a row
+    that sees no key gets O = 0 and L = -inf.
     """
     strided = not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous())
     for name, t in (("q", q), ("k", k), ("v", v)):
@@ -181,8 +189,9 @@ def attn_fwd(
             raise RuntimeError(f"{name} must be torch.bfloat16")
     b, n, h, d = q.shape
     hkv = k.shape[2]
-    if k.shape != v.shape or k.shape[0] != b or k.shape[1] != n or k.shape[3] != d:
-        raise RuntimeError("k/v must be [B, N, H_KV, D] matching q")
+    nk = k.shape[1]
+    if k.shape != v.shape or k.shape[0] != b or k.shape[3] != d:
+        raise RuntimeError("k/v must be [B, Nk, H_KV, D] matching q's batch and head dimension")
     if out is None:
         out = torch.empty((b, n, h, d), dtype=torch.bfloat16, device=q.device)
     if lse is None:
@@ -193,13 +202,14 @@ def attn_fwd(
         raise RuntimeError("lse must be a contiguous fp32 tensor [B, H, 1, N]")
     _require_same_device(q, k=k, v=v, out=out, lse=lse)
     s = stream if stream is not None else torch.cuda.current_stream(q.device)
-    if kv_lens is not None:
-        if kv_lens.dtype != torch.int32 or kv_lens.shape != (b,) or kv_lens.device != q.device:
+    if kv_lens is not None or nk != n:
+        if kv_lens is not None and (kv_lens.dtype != torch.int32 or kv_lens.shape != (b,) or kv_lens.device != q.device):
             raise RuntimeError("kv_lens must be an int32 tensor [B] on q's device")
         arr = lambda t: (ctypes.c_longlong * 3)(*t.stride()[:3])  # noqa: E731
-        rc = capi().hk_attn_fwd_varlen(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                                       b, n, h, hkv, d, arr(q), arr(k), arr(v), kv_lens.data_ptr(),
-                                       int(bool(causal)), float(softmax_scale or 0.0), q.device.index, s.cuda_stream)
+        rc = capi().hk_attn_fwd_cross(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                      b, n, nk, h, hkv, d, arr(q), arr(k), arr(v),
+                                      kv_lens.data_ptr() if kv_lens is not None else None,
+                                      int(bool(causal)), float(softmax_scale or 0.0), q.device.index, s.cuda_stream)
     elif strided:
         arr = lambda t: (ctypes.c_longlong * 3)(*t.stride()[:3])  # noqa: E731
         rc = capi().hk_attn_fwd_strided(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
@@ -255,18 +265,19 @@ def attn_bwd(
     kv_lens: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """dQ, dK, dV of the attention forward (the reference's ``dispatch_bwd_combined``,
-    kernels/attn/gqa_backwards/attn_bkwd_non_causal.cpp:37-49). q, d_o [B,N,H,D], k, v [B,N,H_KV,D] bf16;
-    lse, delta [B,H,1,N] fp32. dQ comes back as [B,N,H,D], or [B,H,N,D] with ``dq_layout=HK_DQ_BHND``
-    (the reference's pre-shuffle layout). Any N >= 1. `kv_lens` (int32 [B], non-causal only) is the padding of
-    ``attn_fwd(..., kv_lens=)``: dK and dV rows of padded keys come back as zeros."""
+    kernels/attn/gqa_backwards/attn_bkwd_non_causal.cpp:37-49). q, d_o [B,N,H,D], k, v [B,Nk,H_KV,D] bf16 (Nk may
+    differ from N); lse, delta [B,H,1,N] fp32. dQ comes back as [B,N,H,D], or [B,H,N,D] with
+    ``dq_layout=HK_DQ_BHND`` (the reference's pre-shuffle layout). Any N, Nk >= 1. `kv_lens` (int32 [B]) and `causal`
+    mean what they mean in ``attn_fwd``: dK and dV rows of keys nobody sees come back as zeros."""
     for name, t in (("q", q), ("k", k), ("v", v), ("d_o", d_o)):
         _require_cuda_bf16(name, t, 4)
         if t.dtype != torch.bfloat16:
             raise RuntimeError(f"{name} must be torch.bfloat16")
     b, n, h, d = q.shape
     hkv = k.shape[2]
-    if k.shape != v.shape or k.shape[0] != b or k.shape[1] != n or k.shape[3] != d or d_o.shape != q.shape:
-        raise RuntimeError("k/v must be [B, N, H_KV, D] and d_o [B, N, H, D] matching q")
+    nk = k.shape[1]
+    if k.shape != v.shape or k.shape[0] != b or k.shape[3] != d or d_o.shape != q.shape:
+        raise RuntimeError("k/v must be [B, Nk, H_KV, D] and d_o [B, N, H, D] matching q")
     for name, t in (("lse", lse), ("delta", delta)):
         if t.shape != (b, h, 1, n) or t.dtype != torch.float32 or not t.is_contiguous() or t.device != q.device:
             raise RuntimeError(f"{name} must be a contiguous fp32 tensor [B, H, 1, N] on q's device")
@@ -284,9 +295,9 @@ def attn_bwd(
     s = stream if stream is not None else torch.cuda.current_stream(q.device)
     if kv_lens is not None and (kv_lens.dtype != torch.int32 or kv_lens.shape != (b,) or kv_lens.device != q.device):
         raise RuntimeError("kv_lens must be an int32 tensor [B] on q's device")
-    rc = capi().hk_attn_bwd_varlen(q.data_ptr(), k.data_ptr(), v.data_ptr(), d_o.data_ptr(), lse.data_ptr(),
-                                   delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), b, n, h, hkv, d,
-                                   kv_lens.data_ptr() if kv_lens is not None else None,
+    rc = capi().hk_attn_bwd_cross(q.data_ptr(), k.data_ptr(), v.data_ptr(), d_o.data_ptr(), lse.data_ptr(),
+                                  delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), b, n, nk, h, hkv, d,
+                                  kv_lens.data_ptr() if kv_lens is not None else None,
                                    int(bool(causal)), float(softmax_scale or 0.0), int(dq_layout), q.device.index,
                                    s.cuda_stream)
     _check(rc, "hk_attn_bwd")

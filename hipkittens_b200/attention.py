@@ -9,8 +9,9 @@ input dtype and (q, k, v, O, L) are saved for the backward pass, which runs the 
 L, delta)`` and ``dispatch_dq_shuffle(dQ_in, dQ)``.
 
 Differences: dQ_in is not zero-filled (nothing is accumulated into it); a right-padded ``key_padding_mask``
-(True = keep, as in ``base.py:88-103``) is honoured through per-batch key lengths, where the reference's modules
-accept the argument and ignore it (hipkittens.py:147-162); and causality and the softmax scale are honoured here (they are baked into the reference's compiled module, and its modules
+(True = keep, as in ``base.py:88-103``) is honoured through per-batch key lengths, also together with ``causal``
+and with more keys than queries (``base.py:104-116``), where the reference's modules accept the argument and ignore
+it (hipkittens.py:147-162); and causality and the softmax scale are honoured here (they are baked into the reference's compiled module, and its modules
 ignore the ``causal`` and ``softmax_scale`` they are constructed with, hipkittens.py:147-162).
 """
 from __future__ import annotations
@@ -56,18 +57,19 @@ class HipAttnFunction(Function):
     def forward(ctx, q_bnhd: torch.Tensor, k_bnhd: torch.Tensor, v_bnhd: torch.Tensor, causal: bool = True,
                 softmax_scale=None, kv_lens=None):
         B, N, H, D = q_bnhd.shape
-        HKV = k_bnhd.shape[2]
+        HKV, NK = k_bnhd.shape[2], k_bnhd.shape[1]
         dev = q_bnhd.device
         out_dtype = q_bnhd.dtype
-        assert k_bnhd.shape == (B, N, HKV, D), f"K shape mismatch: expected ({B}, {N}, {HKV}, {D}), got {k_bnhd.shape}"
-        assert v_bnhd.shape == (B, N, HKV, D), f"V shape mismatch: expected ({B}, {N}, {HKV}, {D}), got {v_bnhd.shape}"
+        assert k_bnhd.shape == (B, NK, HKV, D), f"K shape mismatch: expected ({B}, {NK}, {HKV}, {D}), got {k_bnhd.shape}"
+        assert v_bnhd.shape == (B, NK, HKV, D), f"V shape mismatch: expected ({B}, {NK}, {HKV}, {D}), got {v_bnhd.shape}"
         assert q_bnhd.is_cuda and k_bnhd.is_cuda and v_bnhd.is_cuda, "All tensors must be on CUDA device"
         assert q_bnhd.device == k_bnhd.device == v_bnhd.device, "All tensors must be on same device"
         assert H % HKV == 0, f"H ({H}) must be divisible by HKV ({HKV}) for GQA"
 
         O = torch.empty((B, N, H, D), dtype=torch.bfloat16, device=dev)
         L = torch.empty((B, H, 1, N), dtype=torch.float32, device=dev)
-        if kv_lens is not None or (all(_tma_viewable(t) for t in (q_bnhd, k_bnhd, v_bnhd)) and not all(
+        ctx.general = kv_lens is not None or NK != N  # cases the reference's compiled modules have no entry for
+        if ctx.general or (all(_tma_viewable(t) for t in (q_bnhd, k_bnhd, v_bnhd)) and not all(
                 t.is_contiguous() for t in (q_bnhd, k_bnhd, v_bnhd))):
             # bf16 views of a packed projection (what qkv.unbind(2) gives): the kernel reads them through
             # strided TMA descriptors, so the reference's three .contiguous() copies (hipkittens.py:37-39) go
@@ -107,15 +109,15 @@ class HipAttnFunction(Function):
 
         dQ_in = torch.empty((B, H, N, D), dtype=torch.bfloat16, device=dev)  # BHND (pre-shuffle)
         dQ = torch.empty((B, N, H, D), dtype=torch.bfloat16, device=dev)
-        dK = torch.empty((B, N, HKV, D), dtype=torch.bfloat16, device=dev)
-        dV = torch.empty((B, N, HKV, D), dtype=torch.bfloat16, device=dev)
+        dK = torch.empty(k.shape, dtype=torch.bfloat16, device=dev)
+        dV = torch.empty(v.shape, dtype=torch.bfloat16, device=dev)
         delta = torch.empty((B, H, 1, N), dtype=torch.float32, device=dev)
 
-        if ctx.kv_lens is not None:
-            # padded batch: the C ABI's varlen entry (no counterpart among the reference's three calls); dQ is written
-            # in its final layout, so no shuffle pass
+        if ctx.general:
+            # padded batch, or more keys than queries: the C ABI's general entry (no counterpart among the reference's
+            # three calls); dQ is written in its final layout, so no shuffle pass
             attn_bwd_prep(O, dO, delta)
-            attn_bwd(q, k, v, dO, L, delta, causal=False, softmax_scale=ctx.softmax_scale, dq=dQ, dk=dK, dv=dV,
+            attn_bwd(q, k, v, dO, L, delta, causal=ctx.causal, softmax_scale=ctx.softmax_scale, dq=dQ, dk=dK, dv=dV,
                      kv_lens=ctx.kv_lens)
             status = device_status(dev.index)
             if status != 0:
@@ -161,8 +163,6 @@ class HipSelfAttention(nn.Module):
         causal = self.causal if causal is None else causal
         kv_lens = None
         if key_padding_mask is not None:
-            if causal:
-                raise ValueError("key_padding_mask together with causal is not supported by the kernels")
             kv_lens = _lens_from_key_padding_mask(key_padding_mask, qkv.shape[1])
         q, k, v = qkv.unbind(dim=2)
         out_bnhd = HipAttnFunction.apply(q, k, v, causal, self.softmax_scale, kv_lens)
@@ -170,7 +170,9 @@ class HipSelfAttention(nn.Module):
 
 
 class HipCrossAttention(nn.Module):
-    """q [B, S, H, D], kv [B, S, 2, H_KV, D] -> [B, S, H, D] (hipkittens.py:165-202)."""
+    """q [B, Sq, H, D], kv [B, Sk, 2, H_KV, D] -> [B, Sq, H, D] (hipkittens.py:165-202). Sq may differ from Sk and
+    `causal` may be combined with a right-padded `key_padding_mask`, with the reference math path's alignment of the
+    causal mask to the last query and the last kept key (base.py:104-116)."""
 
     def __init__(self, causal=False, softmax_scale=None, attention_dropout=0.0, deterministic=False):
         super().__init__()
@@ -185,8 +187,6 @@ class HipCrossAttention(nn.Module):
         assert kv.shape[0] == batch_size and kv.shape[4] == q.shape[3]
         kv_lens = None
         if key_padding_mask is not None:
-            if causal:
-                raise ValueError("key_padding_mask together with causal is not supported by the kernels")
             kv_lens = _lens_from_key_padding_mask(key_padding_mask, kv.shape[1])
         k, v = kv.unbind(dim=2)
         out_bnhd = HipAttnFunction.apply(q, k, v, causal, self.softmax_scale, kv_lens)

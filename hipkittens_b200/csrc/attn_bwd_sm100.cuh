@@ -48,15 +48,19 @@ struct BwdParams {
   const float* lse;     // [B,H,1,N] from the forward pass (natural log)
   const float* delta;   // [B,H,1,N] rowsum(dO * O)
   __nv_bfloat16* dq;    // written through the three strides below
-  __nv_bfloat16* dk;    // [B,N,H_KV,D]
-  __nv_bfloat16* dv;    // [B,N,H_KV,D]
+  __nv_bfloat16* dk;    // [B,NK,H_KV,D]
+  __nv_bfloat16* dv;    // [B,NK,H_KV,D]
   long long dq_stride_b, dq_stride_n, dq_stride_h;  // elements; [B,N,H,D] or [B,H,N,D]
-  int B, N, H, H_KV;
+  int B, N, H, H_KV;    // N = query rows per batch element
+  int NK;               // keys per batch element (N for self-attention)
   int n_items;
   int group_units;      // causal order: (batch, kv-head) units swept together (L2 residency)
+  int group_items;      // work items of a full group (all items when there is one group)
+  int rounds_per_group; // ceil(group_items / CTAs): a group is dealt in rounds of its own (see item_for_round)
+  int total_rounds;     // rounds_per_group * number of groups
   float scale;
   float scale_log2;
-  const int* kv_lens;   // optional device [B]: batch b attends to keys [0, kv_lens[b]) only (non-causal); null = N
+  const int* kv_lens;   // optional device [B]: batch b attends to keys [0, kv_lens[b]) only; null = NK
   int* status;
 #ifdef HK_TRACE
   long long* trace;     // [4 roles][4096] clock stamps of CTA 0 (debug builds only)
@@ -265,8 +269,12 @@ __device__ __forceinline__ void bwd_store_part_row(uint32_t taddr, __nv_bfloat16
 struct DkdvItem {
   int b, kvh, j;   // batch, kv head, key block
   int kv_len;      // keys this batch element attends to
+  int off;         // causal: query row r sees keys [0, r + off], off = kv_len - N (the reference aligns the mask to
+                   // the last query and the last kept key, training/llama/llama/models/attentions/base.py:104-116)
+  int i_min;       // first query tile this key block meets
   int cnt_i;       // query tiles per head this key block meets
-  int n_iter;      // heads of the group x query tiles; 0 for a key block that lies wholly beyond kv_len
+  int n_iter;      // heads of the group x query tiles; 0 for a key block nobody sees (beyond kv_len, or causal
+                   // with every query before it)
 };
 
 // Work order: one (batch, kv head) unit's key blocks are adjacent so that the CTAs running at the same
@@ -275,24 +283,28 @@ struct DkdvItem {
 template <bool CAUSAL>
 __device__ __forceinline__ DkdvItem decode_dkdv_item(const BwdParams& p, int idx) {
   DkdvItem w;
-  const int NB = (p.N + kBlockN - 1) / kBlockN;  // the last block may be partial
+  const int NBK = (p.NK + kBlockN - 1) / kBlockN;  // key blocks; the last may be partial
+  const int NBQ = (p.N + kBlockM - 1) / kBlockM;   // query tiles
   const int units = p.B * p.H_KV;
   int unit;
   if (CAUSAL) {
     const int U = p.group_units;
-    const int grp = min(idx / (U * NB), (units - 1) / U);
-    const int within = idx - grp * (U * NB);
+    const int grp = min(idx / (U * NBK), (units - 1) / U);
+    const int within = idx - grp * (U * NBK);
     const int in_grp = min(U, units - grp * U);
     w.j = within / in_grp;
     unit = grp * U + within % in_grp;
   } else {
-    unit = idx / NB;
-    w.j = idx % NB;
+    unit = idx / NBK;
+    w.j = idx % NBK;
   }
   w.b = unit / p.H_KV;
   w.kvh = unit % p.H_KV;
-  w.kv_len = (!CAUSAL && p.kv_lens) ? min(max(p.kv_lens[w.b], 1), p.N) : p.N;
-  w.cnt_i = CAUSAL ? NB - w.j : NB;
+  w.kv_len = p.kv_lens ? min(max(p.kv_lens[w.b], 1), p.NK) : p.NK;
+  w.off = w.kv_len - p.N;
+  // causal: key c is seen by query rows r >= c - off; the first key of the block, j*128, is the one seen by most
+  w.i_min = CAUSAL ? max(w.j * kBlockN - w.off, 0) / kBlockM : 0;
+  w.cnt_i = max(NBQ - w.i_min, 0);
   w.n_iter = (w.j * kBlockN >= w.kv_len) ? 0 : (p.H / p.H_KV) * w.cnt_i;
   return w;
 }
@@ -399,19 +411,18 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     int trace_n = 0;
 #endif
     for (int round = 0; ok; ++round) {
-      const int idx = item_for_round(round, blockIdx.x, gridDim.x);
-      if (idx >= p.n_items) {
-        if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
-        continue;
-      }
+      if (round >= p.total_rounds) break;
+      const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+      if (idx < 0) continue;  // a partial round leaves some CTAs without an item
       const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
-      const bool pad_row = w.j * kBlockN + row >= w.kv_len;  // this key is padding (or lies beyond N)
+      const bool pad_row = w.j * kBlockN + row >= w.kv_len;  // this key is padding (or lies beyond NK)
       const bool pad_block = (w.j + 1) * kBlockN > w.kv_len;  // uniform over the CTA: only such a block has padded keys
       if (w.n_iter == 0) {
-        // the whole key block is padding: its gradients are zero and no product was issued for it
-        if (w.j * kBlockN + row < p.N) {
+        // nobody sees this key block (padding, or causal with every query before it): its gradients are zero and no
+        // product was issued for it
+        if (w.j * kBlockN + row < p.NK) {
           const size_t off =
-              ((static_cast<size_t>(w.b) * p.N + w.j * kBlockN + row) * p.H_KV + w.kvh) * D + part * (D / kBwdParts);
+              ((static_cast<size_t>(w.b) * p.NK + w.j * kBlockN + row) * p.H_KV + w.kvh) * D + part * (D / kBwdParts);
 #pragma unroll
           for (int v = 0; v < D / kBwdParts / 8; ++v) {
             reinterpret_cast<uint4*>(p.dk + off)[v] = make_uint4(0, 0, 0, 0);
@@ -422,7 +433,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       }
       for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
         HK_STAMP(trole, 0);
-        const bool diag = CAUSAL && (n % w.cnt_i == 0);  // the query tile at the key block's own position
+        // a query tile the diagonal runs through: its first row does not see the block's last key (with an offset
+        // that is not a multiple of the tile these are two tiles per head, else the one at the block's own position)
+        const int i_t = w.i_min + n % w.cnt_i;
+        const bool diag = CAUSAL && (i_t * kBlockM + w.off < w.j * kBlockN + kBlockN - 1);
         const float* sL = sStat + (it & 1) * 256 + part * kBwdPC;
         const float* sDl = sL + 128;
         // ---- S^T into registers; X is free for dP^T of this pair right away
@@ -457,9 +471,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             su[q4 * 4 + 3] = __float_as_uint(ex2_approx(x3));
           }
           if (diag) {
-            // the query tile at the key block's own position: queries earlier than the key see nothing
+            // key j*128 + row is seen by query i_t*128 + col iff key <= query + off: earlier queries see nothing
+            // (this also zeroes the infinities that rows without any key, whose L is -inf, produce above)
+            const int lim = row + (w.j - i_t) * kBlockN - w.off;
 #pragma unroll
-            for (int col = 0; col < kBwdPC; ++col) su[col] = (part * kBwdPC + col) < row ? 0u : su[col];
+            for (int col = 0; col < kBwdPC; ++col) su[col] = (part * kBwdPC + col) < lim ? 0u : su[col];
           }
           if (pad_block) {
             // a padded key is seen by nobody: P^T and dS^T rows are zero, so are its dK and dV rows
@@ -531,8 +547,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       if (!ok) break;
       ++acc_cnt;
       tc_fence_after();
-      const size_t off = ((static_cast<size_t>(w.b) * p.N + w.j * kBlockN + row) * p.H_KV + w.kvh) * D + part * (D / kBwdParts);
-      const bool row_exists = w.j * kBlockN + row < p.N;  // keys of a partial last block beyond N are computed, not stored
+      const size_t off = ((static_cast<size_t>(w.b) * p.NK + w.j * kBlockN + row) * p.H_KV + w.kvh) * D + part * (D / kBwdParts);
+      const bool row_exists = w.j * kBlockN + row < p.NK;  // keys of a partial last block beyond NK are computed, not stored
       bwd_store_part_row<D>(tmem + lane_addr + cDK + part * (D / kBwdParts), p.dk + off, p.scale, row_exists);
       bwd_store_part_row<D>(tmem + lane_addr + cDV + part * (D / kBwdParts), p.dv + off, 1.0f, row_exists);
       tc_fence_before();  // orders these reads before the next item's first dV product (published through P_FULL)
@@ -550,11 +566,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       uint32_t qa_par = 0, rb_par = 0;
       bool ok = true;
       for (int round = 0; ok; ++round) {
-        const int idx = item_for_round(round, blockIdx.x, gridDim.x);
-        if (idx >= p.n_items) {
-          if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
-          continue;
-        }
+        if (round >= p.total_rounds) break;
+        const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+        if (idx < 0) continue;  // a partial round leaves some CTAs without an item
         const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
         if (w.n_iter == 0) continue;  // key block wholly beyond this batch element's length: nothing to do
         ok = mbar_wait(bars + KV_EMPTY, (item_cnt & 1) ^ 1, abortp, kWaitLimitCycles);
@@ -568,7 +582,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
         for (int n = 0; n < w.n_iter && ok; ++n) {
           const int head = w.kvh * G + n / w.cnt_i;
-          const int i = (CAUSAL ? w.j : 0) + n % w.cnt_i;
+          const int i = w.i_min + n % w.cnt_i;
           ok = mbar_wait(bars + QA_EMPTY + qa, qa_par ^ 1, abortp, kWaitLimitCycles);
           if (!ok) break;
           mbar_expect_tx(bars + QA_FULL + qa, kTile);
@@ -610,11 +624,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       int trace_n = 0;
 #endif
       for (int round = 0; ok; ++round) {
-        const int idx = item_for_round(round, blockIdx.x, gridDim.x);
-        if (idx >= p.n_items) {
-          if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
-          continue;
-        }
+        if (round >= p.total_rounds) break;
+        const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+        if (idx < 0) continue;  // a partial round leaves some CTAs without an item
         const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
         if (w.n_iter == 0) continue;  // key block wholly beyond this batch element's length: nothing to do
         ok = iss_wait(bars + KV_FULL, item_cnt & 1, abortp, kWaitLimitCycles);
@@ -673,11 +685,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       int trace_n = 0;
 #endif
       for (int round = 0; ok; ++round) {
-        const int idx = item_for_round(round, blockIdx.x, gridDim.x);
-        if (idx >= p.n_items) {
-          if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
-          continue;
-        }
+        if (round >= p.total_rounds) break;
+        const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+        if (idx < 0) continue;  // a partial round leaves some CTAs without an item
         const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
         if (w.n_iter == 0) continue;  // key block wholly beyond this batch element's length: nothing to do
         for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
@@ -733,7 +743,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       float lv[kBlockM / 32], dv_[kBlockM / 32];
       auto fetch = [&](const DkdvItem& w, int n) {
         const int head = w.kvh * G + n / w.cnt_i;
-        const int i = (CAUSAL ? w.j : 0) + n % w.cnt_i;
+        const int i = w.i_min + n % w.cnt_i;
         const size_t base = (static_cast<size_t>(w.b) * p.H + head) * p.N;
 #pragma unroll
         for (int t = 0; t < kBlockM / 32; ++t) {
@@ -745,11 +755,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
       };
       for (int round = 0; ok; ++round) {
-        const int idx = item_for_round(round, blockIdx.x, gridDim.x);
-        if (idx >= p.n_items) {
-          if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
-          continue;
-        }
+        if (round >= p.total_rounds) break;
+        const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+        if (idx < 0) continue;  // a partial round leaves some CTAs without an item
         const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
         if (w.n_iter == 0) continue;  // key block wholly beyond this batch element's length: nothing to do
         fetch(w, 0);
@@ -792,7 +800,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 struct DqItem {
   int b, h, kvh, i;  // batch, query head, its kv head, query tile
   int kv_len;        // keys this batch element attends to
-  int n_iter;        // key tiles this query tile meets
+  int off;           // causal: query row r sees keys [0, r + off], off = kv_len - N
+  int n_iter;        // key tiles this query tile meets (0: none of its rows sees a key; dQ = 0)
 };
 
 // Work order: the query tiles of one (batch, kv head) unit are adjacent so that concurrently running CTAs
@@ -823,8 +832,11 @@ __device__ __forceinline__ DqItem decode_dq_item(const BwdParams& p, int idx) {
   w.b = unit / p.H_KV;
   w.kvh = unit % p.H_KV;
   w.h = w.kvh * G + g;
-  w.kv_len = (!CAUSAL && p.kv_lens) ? min(max(p.kv_lens[w.b], 1), p.N) : p.N;
-  w.n_iter = CAUSAL ? w.i + 1 : (w.kv_len + kBlockN - 1) / kBlockN;
+  w.kv_len = p.kv_lens ? min(max(p.kv_lens[w.b], 1), p.NK) : p.NK;
+  w.off = w.kv_len - p.N;
+  const int n_kv = (w.kv_len + kBlockN - 1) / kBlockN;
+  // causal: the last row of the tile sees keys up to i*128 + 127 + off
+  w.n_iter = CAUSAL ? min(max((w.i * kBlockM + kBlockM + w.off + kBlockN - 1) / kBlockN, 0), n_kv) : n_kv;
   return w;
 }
 
@@ -911,18 +923,28 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     int trace_n = 0;
 #endif
     for (int round = 0; ok; ++round) {
-      const int idx = item_for_round(round, blockIdx.x, gridDim.x);
-      if (idx >= p.n_items) {
-        if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
-        continue;
-      }
+      if (round >= p.total_rounds) break;
+      const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+      if (idx < 0) continue;  // a partial round leaves some CTAs without an item
       const DqItem w = decode_dq_item<CAUSAL>(p, idx);
       const size_t srow = (static_cast<size_t>(w.b) * p.H + w.h) * p.N + static_cast<size_t>(w.i) * kBlockM + row;
       const bool row_exists = w.i * kBlockM + row < p.N;  // rows of a partial last tile beyond N: zero statistics
+      if (w.n_iter == 0) {
+        // causal with more queries than kept keys: no row of this tile sees a key, dQ = 0 and no product is issued
+        if (row_exists) {
+          __nv_bfloat16* dst0 = p.dq + w.b * p.dq_stride_b + (static_cast<long long>(w.i) * kBlockM + row) * p.dq_stride_n +
+                                w.h * p.dq_stride_h + part * (D / kBwdParts);
+#pragma unroll
+          for (int v = 0; v < D / kBwdParts / 8; ++v) reinterpret_cast<uint4*>(dst0)[v] = make_uint4(0, 0, 0, 0);
+        }
+        continue;
+      }
       const float nl = row_exists ? p.lse[srow] * -1.4426950408889634f : 0.f;
       const float dl = row_exists ? p.delta[srow] : 0.f;
       for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
-        const bool diag = CAUSAL && (n == w.n_iter - 1);
+        // a key tile the diagonal (or the end of the kept keys) runs through: the tile's first row does not see
+        // its last key
+        const bool diag = CAUSAL && ((n + 1) * kBlockN - 1 > min(w.i * kBlockM + w.off, w.kv_len - 1));
         HK_STAMP(0, 0);
         ok = mbar_wait(bars + S_FULL, it & 1, abortp, kWaitLimitCycles);
         ok = __all_sync(0xffffffffu, ok);
@@ -945,9 +967,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             su[2 * i + 1] = __float_as_uint(ex2_approx(x1));
           }
           if (diag) {
-            // diagonal tile: keys later than the query see nothing
+            // key n*128 + col is seen by query i*128 + row iff it is <= query + off and < kv_len (this also zeroes
+            // the infinities of a row without any key, whose L is -inf)
+            const int lim = min(w.i * kBlockM + row + w.off, w.kv_len - 1) - n * kBlockN;
 #pragma unroll
-            for (int col = 0; col < kBwdPC; ++col) su[col] = (part * kBwdPC + col) > row ? 0u : su[col];
+            for (int col = 0; col < kBwdPC; ++col) su[col] = (part * kBwdPC + col) > lim ? 0u : su[col];
           }
           if (!CAUSAL && n == w.n_iter - 1 && (w.kv_len & (kBlockN - 1)) != 0) {
             // partial last tile: keys at or beyond the length are padding
@@ -1017,12 +1041,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       uint32_t ka_par = 0, vb_par = 0;
       bool ok = true;
       for (int round = 0; ok; ++round) {
-        const int idx = item_for_round(round, blockIdx.x, gridDim.x);
-        if (idx >= p.n_items) {
-          if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
-          continue;
-        }
+        if (round >= p.total_rounds) break;
+        const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+        if (idx < 0) continue;  // a partial round leaves some CTAs without an item
         const DqItem w = decode_dq_item<CAUSAL>(p, idx);
+        if (w.n_iter == 0) continue;  // no row of this tile sees a key: nothing is loaded or issued
         ok = mbar_wait(bars + QDO_EMPTY, (item_cnt & 1) ^ 1, abortp, kWaitLimitCycles);
         if (!ok) break;
         ++item_cnt;
@@ -1071,12 +1094,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       int trace_n = 0;
 #endif
       for (int round = 0; ok; ++round) {
-        const int idx = item_for_round(round, blockIdx.x, gridDim.x);
-        if (idx >= p.n_items) {
-          if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
-          continue;
-        }
+        if (round >= p.total_rounds) break;
+        const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+        if (idx < 0) continue;  // a partial round leaves some CTAs without an item
         const DqItem w = decode_dq_item<CAUSAL>(p, idx);
+        if (w.n_iter == 0) continue;  // no row of this tile sees a key: nothing is loaded or issued
         ok = iss_wait(bars + QDO_FULL, item_cnt & 1, abortp, kWaitLimitCycles);
         if (!ok) break;
         ++item_cnt;
@@ -1131,12 +1153,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         return true;
       };
       for (int round = 0; ok; ++round) {
-        const int idx = item_for_round(round, blockIdx.x, gridDim.x);
-        if (idx >= p.n_items) {
-          if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
-          continue;
-        }
+        if (round >= p.total_rounds) break;
+        const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+        if (idx < 0) continue;  // a partial round leaves some CTAs without an item
         const DqItem w = decode_dq_item<CAUSAL>(p, idx);
+        if (w.n_iter == 0) continue;  // no row of this tile sees a key: nothing is loaded or issued
         ok = iss_wait(bars + QDO_FULL, item_cnt & 1, abortp, kWaitLimitCycles);
         if (!ok) break;
         ++item_cnt;

@@ -10,12 +10,13 @@
 //   warp  8     TMA producer: Q tiles once per work item, K/V tiles through a shared-memory ring
 //   warp  9     UMMA issuer: S = Q K^T (both operands in shared memory) and O += P V (P read from
 //               TMEM, V from shared memory, MN-major), accumulators in TMEM
-//   warps 10-11 idle (they complete the producer warpgroup for the register re-allocation)
+//   warp  10    D = 64 only: second UMMA issuer (warp 9 then issues the Q K^T products, warp 10 the P V ones)
+//   warps 10-11 otherwise idle (they complete the producer warpgroup for the register re-allocation)
 // A work item is a pair of 128-row query tiles ("slots") that share one KV head, so each K/V tile
 // staged in shared memory feeds two S and two O accumulators. While the tensor pipe works on one
 // slot the other slot's softmax runs, which is what hides the exponentials under the MMAs.
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D); bf16 P overwrites the
-// first 64 columns of its own S.
+// first 64 columns of its own S (D = 128) or has columns [384,448) / [448,512) of its own (D = 64).
 //
 // Numerics: Q stays unscaled bf16; p = exp2(s*c - m*c) with c = scale*log2(e) in fp32; the running
 // max m is only refreshed when it grew by more than 8 in log2 units (the reference's lazy rescale,
@@ -38,14 +39,20 @@ constexpr int kFwdThreads = 384;
 constexpr int kFwdRegsAtLaunch = 168;   // 65536 / 384, rounded down to a multiple of 8; see setmaxnreg below
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThresholdLog2 = 8.0f;
+// Of every kEmuMod column pairs of a score row, this many take their exponentials from a cubic polynomial on the
+// FMA pipe (ptx::ex2_poly2) instead of the MUFU. Per head dimension: with D = 64 there is one exponential per 64
+// multiply-adds instead of 128 and the MUFU is the busiest unit; with D = 128 every added instruction lengthens the
+// chain S -> softmax -> P V that bounds the kernel, and the polynomial measured slower at every share.
 #ifndef HK_EMU_MOD
 #define HK_EMU_MOD 4
 #endif
-#ifndef HK_EMU_CNT
-#define HK_EMU_CNT 0
+#ifndef HK_EMU_CNT_D64
+#define HK_EMU_CNT_D64 1
 #endif
-constexpr int kEmuMod = HK_EMU_MOD;   // of every kEmuMod column pairs ...
-constexpr int kEmuCnt = HK_EMU_CNT;   // ... this many compute exp2 with the polynomial instead of the MUFU
+#ifndef HK_EMU_CNT_D128
+#define HK_EMU_CNT_D128 0
+#endif
+constexpr int kEmuMod = HK_EMU_MOD;
 constexpr uint64_t kWaitLimitCycles = 8000ull * 1000 * 1000;  // SM cycles, > 4 s: far beyond any legitimate wait
 
 // Device status codes written to FwdParams::status (0 = OK).
@@ -54,13 +61,17 @@ enum : int { kStatusOk = 0, kStatusTimeout = 1 };
 struct FwdParams {
   __nv_bfloat16* o;     // [B,N,H,D]
   float* lse;           // [B,H,1,N]
-  int B, N, H, H_KV;
+  int B, N, H, H_KV;    // N = query rows per batch element
+  int NK;               // keys per batch element (N for self-attention)
   int n_items;          // number of work items (slot pairs)
   int pair_heads;       // 1: slots = two heads of one group at the same q block; 0: two q blocks of one head
   int group_units;      // causal order: (batch, kv-head) units swept together, sized so their K/V fit in L2
+  int group_items;      // work items of a full group (all items when there is one group)
+  int rounds_per_group; // ceil(group_items / CTAs): a group is dealt in rounds of its own
+  int total_rounds;     // rounds_per_group * number of groups
   float scale;          // softmax scale
   float scale_log2;     // scale * log2(e)
-  const int* kv_lens;   // optional device [B]: batch b attends to keys [0, kv_lens[b]) only (non-causal); null = N
+  const int* kv_lens;   // optional device [B]: batch b attends to keys [0, kv_lens[b]) only; null = NK
   int* status;          // device word: first non-zero status wins
 #ifdef HK_TRACE
   long long* trace;     // [3 roles][4096] clock stamps of CTA 0 (debug builds only)
@@ -78,6 +89,8 @@ struct FwdSmem {
 struct WorkItem {
   int b, kvh;
   int kv_len;  // keys this batch element attends to
+  int off;     // causal: query row r sees keys [0, r + off], off = kv_len - N (the reference aligns the mask to the
+               // last query and the last kept key, training/llama/llama/models/attentions/base.py:104-116)
   int head[2];
   int qb[2];
   int n[2];  // KV tiles each slot consumes (0 = slot unused)
@@ -146,18 +159,31 @@ __device__ __forceinline__ WorkItem decode_item(const FwdParams& p, int idx) {
   w.head[1] = w.kvh * G + h1;
   w.qb[0] = qb0;
   w.qb[1] = qb1;
-  // key-padding lengths (non-causal only): tiles beyond the batch element's own length are never loaded
-  w.kv_len = (!CAUSAL && p.kv_lens) ? min(max(p.kv_lens[w.b], 1), p.N) : p.N;
+  // key-padding lengths: tiles beyond the batch element's own length are never loaded
+  w.kv_len = p.kv_lens ? min(max(p.kv_lens[w.b], 1), p.NK) : p.NK;
+  w.off = w.kv_len - p.N;
   const int n_kv = (w.kv_len + kBlockN - 1) / kBlockN;
-  w.n[0] = CAUSAL ? qb0 + 1 : n_kv;
-  w.n[1] = (qb1 < NQB) ? (CAUSAL ? qb1 + 1 : n_kv) : 0;
+  // causal: the last row of query block qb sees keys up to qb*128 + 127 + off; a block none of whose rows sees a
+  // key gets no tiles (its rows are written as O = 0, L = -inf by the softmax warps)
+  auto causal_tiles = [&](int qb) { return min(max((qb * kBlockM + kBlockM + w.off + kBlockN - 1) / kBlockN, 0), n_kv); };
+  w.n[0] = CAUSAL ? causal_tiles(qb0) : n_kv;
+  w.n[1] = (qb1 < NQB) ? (CAUSAL ? causal_tiles(qb1) : n_kv) : 0;
   return w;
 }
 
 // Items are dealt to CTAs in a snake (boustrophedon) order so that, with a length-sorted causal list,
-// every CTA receives the same mix of long and short items.
-__device__ __forceinline__ int item_for_round(int round, int cta, int n_cta) {
-  return round * n_cta + ((round & 1) ? (n_cta - 1 - cta) : cta);
+// every CTA receives the same mix of long and short items. Every group of units is dealt in rounds of its own
+// (the last round of a group may be partial) and consecutive groups start the snake from opposite ends: a round
+// that straddled two groups would hand the longest items of the next group to the CTAs that also got the
+// longer items of this one (2 % imbalance with 64 MB groups, 7 % with 32 MB groups of the N = 8192 shape).
+// Returns the item index, or -1 when this CTA has no item in this round.
+template <typename Params>
+__device__ __forceinline__ int item_for_round(const Params& p, int round, int cta, int n_cta) {
+  const int grp = round / p.rounds_per_group;
+  const int r = round - grp * p.rounds_per_group;
+  const int first = grp * p.group_items;
+  const int in_grp = r * n_cta + (((r + grp) & 1) ? (n_cta - 1 - cta) : cta);
+  return (in_grp < min(p.group_items, p.n_items - first)) ? first + in_grp : -1;
 }
 
 #ifdef HK_TRACE
@@ -193,6 +219,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   // (columns [384,448) and [448,512)). S(j+1) = Q K(j+1)^T can then be issued as soon as the softmax has
   // read S(j), instead of after O += P(j) V(j), and a slot's softmax never waits for the tensor pipe.
   constexpr bool kSepP = (D == 64);
+  constexpr int kEmuCnt = (D == 64) ? HK_EMU_CNT_D64 : HK_EMU_CNT_D128;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -253,15 +280,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     int trace_n = 0;
 #endif
     for (int round = 0; ok; ++round) {
-      const int idx = item_for_round(round, blockIdx.x, gridDim.x);
-      if (idx >= p.n_items) {
-        // a snake round may leave this CTA without an item while lower-numbered CTAs still have one
-        if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
-        continue;
-      }
+      if (round >= p.total_rounds) break;
+      const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+      if (idx < 0) continue;  // a partial round leaves some CTAs without an item
       const WorkItem w = decode_item<CAUSAL>(p, idx);
       const int nkv = w.n[slot];
-      if (nkv == 0) continue;
+      if (nkv == 0) {
+        if (CAUSAL && w.qb[slot] * kBlockM < p.N) {
+          // a query block that sees no key at all (more queries than keys): defined output, no products
+          const int qrow = w.qb[slot] * kBlockM + row;
+          if (qrow < p.N) {
+            uint4* dst = reinterpret_cast<uint4*>(p.o + ((static_cast<size_t>(w.b) * p.N + qrow) * p.H + w.head[slot]) * D);
+#pragma unroll
+            for (int v4 = 0; v4 < D / 8; ++v4) dst[v4] = make_uint4(0u, 0u, 0u, 0u);
+            p.lse[(static_cast<size_t>(w.b) * p.H + w.head[slot]) * p.N + qrow] = -INFINITY;
+          }
+        }
+        continue;
+      }
       float m = 0.f, l = 0.f;
       for (int j = 0; j < nkv && ok; ++j) {
         HK_STAMP2(slot, 0);
@@ -277,16 +313,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         for (int cc = 0; cc < 4; ++cc) tmem_ld32(tS + cc * 32, su + cc * 32);
         tmem_wait_ld();
         HK_STAMP2(slot, 2);
-        if (kSepP && j + 1 < nkv) {
-          // S(j) is in registers: the issuer may overwrite it with S(j+1) right away
+        if (kSepP) {
+          // S(j) is in registers: the issuer may overwrite it with the next S of this slot right away
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&s_free[slot]);
         }
-        if (CAUSAL && j == nkv - 1) {
-          // diagonal tile: key (j*128 + col) is visible to query (qb*128 + row) iff col <= row
+        if (CAUSAL && (j + 1) * kBlockN - 1 > min(w.qb[slot] * kBlockM + w.off, w.kv_len - 1)) {
+          // a tile the diagonal (or the end of the keys) runs through - the last one, and the one before it when
+          // off is not a multiple of the tile: key j*128 + i is visible to query row r iff it is <= r + off and
+          // < kv_len. (CTA-uniform condition: the first row of the block sees the fewest keys.)
+          const int lim = min(w.qb[slot] * kBlockM + row + w.off, w.kv_len - 1) - j * kBlockN;
 #pragma unroll
-          for (int i = 0; i < kBlockN; ++i) su[i] = (i > row) ? 0xff800000u : su[i];
+          for (int i = 0; i < kBlockN; ++i) su[i] = (i > lim) ? 0xff800000u : su[i];
         }
         if (!CAUSAL && j == nkv - 1 && (w.kv_len & (kBlockN - 1)) != 0) {
           // partial last tile: keys at or beyond the length are padding (or, beyond N, zeros filled by TMA)
@@ -340,7 +379,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         // the MUFU.
         HK_STAMP2(slot, 3);
         const uint64_t c2 = pack2(c, c);
-        const float nmc = -(m * c);
+        // a causal row that has seen no key yet has m = -inf: subtract nothing, its exponentials are exp2(-inf) = 0
+        const float nmc = (CAUSAL && m == -INFINITY) ? 0.f : -(m * c);
         const uint64_t nmc2 = pack2(nmc, nmc);
         uint64_t lacc0 = pack2(0.f, 0.f), lacc1 = pack2(0.f, 0.f);
 #pragma unroll
@@ -352,11 +392,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             uint64_t p2;
             float p0, p1;
             if ((i % kEmuMod) < kEmuCnt) {
-              float x0, x1;
-              unpack2(x2, x0, x1);
-              p0 = ex2_poly(x0);
-              p1 = ex2_poly(x1);
-              p2 = pack2(p0, p1);
+              p2 = ex2_poly2(x2);
+              unpack2(p2, p0, p1);
             } else {
               float x0, x1;
               unpack2(x2, x0, x1);
@@ -390,7 +427,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if (!ok) break;
       ++o_cnt;
       tc_fence_after();
-      const float inv_l = 1.0f / l;
+      const float inv_l = (CAUSAL && l == 0.f) ? 0.f : 1.0f / l;  // l = 0: a row that sees no key gets O = 0, L = -inf
       const int qrow = w.qb[slot] * kBlockM + row;
       const int head = w.head[slot];
       __nv_bfloat16* orow = p.o + ((static_cast<size_t>(w.b) * p.N + qrow) * p.H + head) * D;
@@ -413,7 +450,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
         }
       }
-      if (row_exists) p.lse[(static_cast<size_t>(w.b) * p.H + head) * p.N + qrow] = m * p.scale + __logf(l);
+      if (row_exists)
+        p.lse[(static_cast<size_t>(w.b) * p.H + head) * p.N + qrow] =
+            (CAUSAL && l == 0.f) ? -INFINITY : m * p.scale + __logf(l);
       // order this slot's TMEM reads before the next item's PV (published through p_full)
       tc_fence_before();
     }
@@ -444,11 +483,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         return true;
       };
       for (int round = 0; ok; ++round) {
-        const int idx = item_for_round(round, blockIdx.x, gridDim.x);
-        if (idx >= p.n_items) {
-          if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
-          continue;
-        }
+        if (round >= p.total_rounds) break;
+        const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+        if (idx < 0) continue;
         const WorkItem w = decode_item<CAUSAL>(p, idx);
         for (int s = 0; s < 2 && ok; ++s) {
           if (w.n[s] == 0) continue;
@@ -462,14 +499,76 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                         w.b);
         }
         const int nmax = max(w.n[0], w.n[1]);
-        if (ok) ok = push_kv(&tmap_k, w.b, w.kvh, 0);
+        if (ok && nmax > 0) ok = push_kv(&tmap_k, w.b, w.kvh, 0);
         for (int j = 0; j < nmax && ok; ++j) {
           ok = push_kv(&tmap_v, w.b, w.kvh, j);
           if (ok && j + 1 < nmax) ok = push_kv(&tmap_k, w.b, w.kvh, j + 1);
         }
       }
-    } else if (warp == 9 && lane == 0) {
-      // ---------------- UMMA issuer
+    } else if (kSepP && (warp == 9 || warp == 10) && lane == 0) {
+      // ---------------- D = 64: two UMMA issuers. P has TMEM columns of its own, so S(j+1) = Q K(j+1)^T and
+      // O += P(j) V(j) of a slot do not order each other: warp 9 issues every Q K^T, warp 10 every P V, each with
+      // its own three waits and three commits per KV tile. (One thread issuing both spends ~600 clocks per group of
+      // MMAs on waits, fences and commits, 3 400 per KV tile for 1 456 clocks of MMA work.)
+      constexpr uint32_t idesc_qk = make_idesc_bf16(kBlockM, kBlockN, false);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(kBlockM, D, true);
+      constexpr uint32_t desc_hi = smem_desc_hi(1024);
+      constexpr uint32_t tile16 = kTile >> 4;
+      const uint32_t q_lo0 = smem_desc_lo(smem_u32(sQ), 16);
+      const uint32_t k_lo0 = smem_desc_lo(smem_u32(sKV), 16);
+      const uint32_t v_lo0 = smem_desc_lo(smem_u32(sKV), kSub);
+      const bool is_qk = (warp == 9);
+      uint32_t pos = is_qk ? 0u : 1u;   // ring position of this role's next tile: K tiles even, V tiles odd
+      uint32_t q_par[2] = {0, 0}, cnt[2] = {0, 0};  // cnt: products issued so far per slot
+      bool ok = true;
+      for (int round = 0; ok; ++round) {
+        if (round >= p.total_rounds) break;
+        const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+        if (idx < 0) continue;
+        const WorkItem w = decode_item<CAUSAL>(p, idx);
+        const int nmax = max(w.n[0], w.n[1]);
+        for (int j = 0; j < nmax && ok; ++j) {
+          const int st = static_cast<int>(pos % kStages);
+          const uint32_t par = (pos / kStages) & 1u;
+          pos += 2;
+          ok = mbar_wait(&kv_full[st], par, abortp, kWaitLimitCycles);
+          for (int s = 0; s < 2 && ok; ++s) {
+            if (j >= w.n[s]) continue;
+            if (is_qk) {
+              if (j == 0) {
+                ok = mbar_wait(&q_full[s], q_par[s], abortp, kWaitLimitCycles);
+                q_par[s] ^= 1;
+                if (!ok) break;
+              }
+              // S of this slot is free once the softmax has read the previous one (nothing to wait for the first time)
+              ok = mbar_wait(&s_free[s], (cnt[s] & 1) ^ 1, abortp, kWaitLimitCycles);
+              if (!ok) break;
+              ++cnt[s];
+              tc_fence_after();
+              const uint32_t a = q_lo0 + s * tile16, b = k_lo0 + st * tile16, d = tmem + s * kBlockN;
+#pragma unroll
+              for (int k = 0; k < D / 16; ++k)
+                umma_ss_lohi(d, a + k * 2, b + k * 2, desc_hi, idesc_qk, k > 0 ? 1u : 0u);
+              umma_commit(&s_full[s]);
+              if (j + 1 == w.n[s]) umma_commit(&q_empty[s]);
+            } else {
+              ok = mbar_wait(&p_full[s], cnt[s] & 1, abortp, kWaitLimitCycles);
+              if (!ok) break;
+              ++cnt[s];
+              tc_fence_after();
+              const uint32_t b = v_lo0 + st * tile16, d = tmem + 2 * kBlockN + s * D, a = tmem + 384 + s * 64;
+#pragma unroll
+              for (int k = 0; k < kBlockN / 16; ++k)
+                umma_ts_lohi(d, a + k * 8, b + k * 128, desc_hi, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+              umma_commit(&p_free[s]);
+              if (j + 1 == w.n[s]) umma_commit(&o_full[s]);
+            }
+          }
+          if (ok) umma_commit(&kv_empty[st]);
+        }
+      }
+    } else if (!kSepP && warp == 9 && lane == 0) {
+      // ---------------- UMMA issuer (D = 128)
       // One thread issues for both slots, strictly alternating slot 0 / slot 1. The alternation is what
       // keeps the two softmax warpgroups half a period apart, so that one slot's exponentials run under
       // the other slot's MMAs. (Two independent issuers, one per slot, were measured: the slots drift
@@ -485,7 +584,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const uint32_t k_lo0 = smem_desc_lo(smem_u32(sKV), 16);     // ring stage 0 as a K tile (K-major)
       const uint32_t v_lo0 = smem_desc_lo(smem_u32(sKV), kSub);   // ring stage 0 as a V tile (MN-major)
       uint32_t q_par[2] = {0, 0}, p_par[2] = {0, 0};  // phase parities of q_full / p_full per slot
-      uint32_t sf_par[2] = {0, 0};                    // ... and of s_free (D = 64 only)
       int ring_st = 0;                                // next ring stage to consume
       uint32_t ring_par = 0;                          // its phase parity
       int pending_v = -1, pending_k = -1;  // ring stages whose release is deferred (see the main loop)
@@ -534,23 +632,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // the waits for the next K/V tiles and the ring releases all sit in the middle of a slot's chunk
       // (after its PV, before its QK), where the pipe still has the PV MMAs queued.
       for (int round = 0; ok; ++round) {
-        const int idx = item_for_round(round, blockIdx.x, gridDim.x);
-        if (idx >= p.n_items) {
-          if (round * static_cast<int>(gridDim.x) >= p.n_items) break;
-          continue;
-        }
+        if (round >= p.total_rounds) break;
+        const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+        if (idx < 0) continue;
         const WorkItem w = decode_item<CAUSAL>(p, idx);
         const int n0 = w.n[0], n1 = w.n[1];
         const int nmax = max(n0, n1);
+        if (nmax == 0) continue;  // causal with more queries than keys: neither block sees a key
         // ---- first K tile: S = Q K0^T for both slots
-        ok = mbar_wait(&kv_full[ring_st], ring_par, abortp, kWaitLimitCycles) &&
-             mbar_wait(&q_full[0], q_par[0], abortp, kWaitLimitCycles);
+        ok = mbar_wait(&kv_full[ring_st], ring_par, abortp, kWaitLimitCycles);
         if (!ok) break;
-        q_par[0] ^= 1;
-        tc_fence_after();
-        issue_qk(0, ring_st);
-        umma_commit(&s_full[0]);
-        if (n0 == 1) umma_commit(&q_empty[0]);
+        if (n0 > 0) {
+          ok = mbar_wait(&q_full[0], q_par[0], abortp, kWaitLimitCycles);
+          if (!ok) break;
+          q_par[0] ^= 1;
+          tc_fence_after();
+          issue_qk(0, ring_st);
+          umma_commit(&s_full[0]);
+          if (n0 == 1) umma_commit(&q_empty[0]);
+        }
         if (n1 > 0) {
           ok = mbar_wait(&q_full[1], q_par[1], abortp, kWaitLimitCycles);
           if (!ok) break;
@@ -562,63 +662,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
         umma_commit(&kv_empty[ring_st]);
         ring_next();
-        if constexpr (kSepP) {
-          // D = 64: S(j+1) is issued before O += P(j) V(j); see kSepP above. (An issuer that polls the four
-          // conditions and issues whichever is ready first was measured slower than this fixed order.)
-          for (int j = 0; j < nmax && ok; ++j) {
-            const int st_v = ring_st;
-            const uint32_t par_v = ring_par;
-            ring_next();
-            const bool has_next = (j + 1 < nmax);
-            const int st_k = ring_st;
-            const uint32_t par_k = ring_par;
-            if (has_next) {
-              ring_next();
-              ok = mbar_wait(&kv_full[st_k], par_k, abortp, kWaitLimitCycles);
-              if (ok && j + 1 < n0) {
-                ok = mbar_wait(&s_free[0], sf_par[0], abortp, kWaitLimitCycles);
-                sf_par[0] ^= 1;
-                if (!ok) break;
-                tc_fence_after();
-                issue_qk(0, st_k);
-                umma_commit(&s_full[0]);
-                if (j + 2 == n0) umma_commit(&q_empty[0]);
-              }
-              if (ok && j + 1 < n1) {
-                ok = mbar_wait(&s_free[1], sf_par[1], abortp, kWaitLimitCycles);
-                sf_par[1] ^= 1;
-                if (!ok) break;
-                tc_fence_after();
-                issue_qk(1, st_k);
-                umma_commit(&s_full[1]);
-                if (j + 2 == n1) umma_commit(&q_empty[1]);
-              }
-              if (!ok) break;
-              umma_commit(&kv_empty[st_k]);
-            }
-            ok = mbar_wait(&kv_full[st_v], par_v, abortp, kWaitLimitCycles);
-            if (ok && j < n0) {
-              ok = mbar_wait(&p_full[0], p_par[0], abortp, kWaitLimitCycles);
-              if (!ok) break;
-              p_par[0] ^= 1;
-              tc_fence_after();
-              issue_pv(0, st_v, j > 0);
-              umma_commit(&p_free[0]);
-              if (j + 1 == n0) umma_commit(&o_full[0]);
-            }
-            if (ok && j < n1) {
-              ok = mbar_wait(&p_full[1], p_par[1], abortp, kWaitLimitCycles);
-              if (!ok) break;
-              p_par[1] ^= 1;
-              tc_fence_after();
-              issue_pv(1, st_v, j > 0);
-              umma_commit(&p_free[1]);
-              if (j + 1 == n1) umma_commit(&o_full[1]);
-            }
-            if (!ok) break;
-            umma_commit(&kv_empty[st_v]);
-          }
-        } else {
+        {
           // stages of V(0) and K(1)
           int st_v = ring_st;
           ok = mbar_wait(&kv_full[st_v], ring_par, abortp, kWaitLimitCycles);

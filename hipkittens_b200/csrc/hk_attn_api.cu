@@ -277,13 +277,25 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
   return HK_OK;
 }
 
+// Sets the fields that say how a kernel's `n_items` work items are dealt to `grid` CTAs: one group (everything)
+// unless causal, where a group is `group_units` units of `per_unit` items each.
+void set_rounds(hk::BwdParams& p, int per_unit, int grid, bool causal) {
+  p.group_items = causal ? p.group_units * per_unit : p.n_items;
+  const int n_groups = (p.n_items + p.group_items - 1) / p.group_items;
+  p.rounds_per_group = (p.group_items + grid - 1) / grid;
+  p.total_rounds = p.rounds_per_group * n_groups;
+}
+
 template <int D, bool CAUSAL>
 int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
-               hk::BwdParams p, int B, int N, int H, int H_KV, int sm_count, cudaStream_t stream) {
-  const int nb = (N + hk::kBlockM - 1) / hk::kBlockM;
-  if (static_cast<long long>(B) * H * nb > 0x3fffffffll) return HK_EINVAL;  // work items are indexed with int
-  p.n_items = B * H_KV * nb;
+               hk::BwdParams p, int B, int N, int NK, int H, int H_KV, int sm_count, cudaStream_t stream) {
+  const int nbq = (N + hk::kBlockM - 1) / hk::kBlockM;   // query tiles
+  const int nbk = (NK + hk::kBlockN - 1) / hk::kBlockN;  // key blocks
+  if (static_cast<long long>(B) * H * nbq > 0x3fffffffll || static_cast<long long>(B) * H_KV * nbk > 0x3fffffffll)
+    return HK_EINVAL;  // work items are indexed with int
+  p.n_items = B * H_KV * nbk;
   int grid = p.n_items < sm_count ? p.n_items : sm_count;
+  set_rounds(p, nbk, grid, CAUSAL);
 #ifdef HK_TRACE
   long long* const trace_buf = p.trace;
   p.trace = g_trace_bwd_kernel == 0 ? trace_buf : nullptr;
@@ -292,8 +304,9 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
   Lay::template dkdv<D>()<<<grid, Lay::kThreads, hk::BwdSmem<D>::kDynBytes, stream>>>(tq, tk, tv, tdo, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   HK_CUDA(cudaGetLastError());
-  p.n_items = B * H * nb;
+  p.n_items = B * H * nbq;
   grid = p.n_items < sm_count ? p.n_items : sm_count;
+  set_rounds(p, (H / H_KV) * nbq, grid, CAUSAL);
 #ifdef HK_TRACE
   p.trace = g_trace_bwd_kernel == 1 ? trace_buf : nullptr;
 #endif
@@ -331,9 +344,16 @@ int hk_attn_fwd_varlen(const void* q, const void* k, const void* v, void* o, flo
                        int H_KV, int D, const long long* q_strides, const long long* k_strides,
                        const long long* v_strides, const int32_t* kv_lens, int causal, float softmax_scale,
                        int device, void* cuda_stream) {
-  if (kv_lens && causal) return HK_EUNSUPPORTED;
+  return hk_attn_fwd_cross(q, k, v, o, lse, B, N, N, H, H_KV, D, q_strides, k_strides, v_strides, kv_lens, causal,
+                           softmax_scale, device, cuda_stream);
+}
+
+int hk_attn_fwd_cross(const void* q, const void* k, const void* v, void* o, float* lse, int B, int N, int NK, int H,
+                      int H_KV, int D, const long long* q_strides, const long long* k_strides,
+                      const long long* v_strides, const int32_t* kv_lens, int causal, float softmax_scale,
+                      int device, void* cuda_stream) {
   if (!q || !k || !v || !o || !lse || !q_strides || !k_strides || !v_strides) return HK_EINVAL;
-  if (B <= 0 || N <= 0 || H <= 0 || H_KV <= 0) return HK_EINVAL;
+  if (B <= 0 || N <= 0 || NK <= 0 || H <= 0 || H_KV <= 0) return HK_EINVAL;
   if (D != 64 && D != 128) return HK_EUNSUPPORTED;
   if (H % H_KV != 0) return HK_EINVAL;
   for (int i = 0; i < 3; ++i) {
@@ -350,8 +370,8 @@ int hk_attn_fwd_varlen(const void* q, const void* k, const void* v, void* o, flo
 
   CUtensorMap tq, tk, tv;
   if ((rc = make_bnhd_map(&tq, q, B, N, H, D, q_strides)) != HK_OK) return rc;
-  if ((rc = make_bnhd_map(&tk, k, B, N, H_KV, D, k_strides)) != HK_OK) return rc;
-  if ((rc = make_bnhd_map(&tv, v, B, N, H_KV, D, v_strides)) != HK_OK) return rc;
+  if ((rc = make_bnhd_map(&tk, k, B, NK, H_KV, D, k_strides)) != HK_OK) return rc;
+  if ((rc = make_bnhd_map(&tv, v, B, NK, H_KV, D, v_strides)) != HK_OK) return rc;
 
   const int G = H / H_KV;
   const int nqb = (N + hk::kBlockM - 1) / hk::kBlockM;
@@ -360,14 +380,16 @@ int hk_attn_fwd_varlen(const void* q, const void* k, const void* v, void* o, flo
   p.lse = lse;
   p.B = B;
   p.N = N;
+  p.NK = NK;
   p.H = H;
   p.H_KV = H_KV;
   p.pair_heads = (G % 2 == 0) ? 1 : 0;
   {
-    // causal sweep groups: as many (batch, kv-head) units as keep K and V of the group within ~64 MB (half of L2; 32 MB was measured 3 % slower, the whole tensor re-reads K/V 2.6 times)
-    const long long kv_bytes = 4ll * N * D;  // K and V of one unit, bf16
+    // causal sweep groups: as many (batch, kv-head) units as keep K and V of the group within HK_GROUP_MB (the
+    // whole tensor at once re-reads K/V 2.6 times at N = 8192)
+    const long long kv_bytes = 4ll * NK * D;  // K and V of one unit, bf16
 #ifndef HK_GROUP_MB
-#define HK_GROUP_MB 64
+#define HK_GROUP_MB 32
 #endif
     long long u = (static_cast<long long>(HK_GROUP_MB) << 20) / kv_bytes;
     p.group_units = int(u < 1 ? 1 : (u > B * H_KV ? B * H_KV : u));
@@ -382,6 +404,14 @@ int hk_attn_fwd_varlen(const void* q, const void* k, const void* v, void* o, flo
   p.trace = g_trace_buf;
 #endif
   const int grid = p.n_items < st->sm_count ? p.n_items : st->sm_count;
+  {
+    // rounds in which the items are dealt to the CTAs: one group (everything) unless causal
+    const int per_unit = p.n_items / (B * H_KV);
+    p.group_items = causal ? p.group_units * per_unit : p.n_items;
+    const int n_groups = (p.n_items + p.group_items - 1) / p.group_items;
+    p.rounds_per_group = (p.group_items + grid - 1) / grid;
+    p.total_rounds = p.rounds_per_group * n_groups;
+  }
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (D == 128) return causal ? launch_fwd<128, true>(tq, tk, tv, p, grid, stream)
                               : launch_fwd<128, false>(tq, tk, tv, p, grid, stream);
@@ -424,9 +454,16 @@ int hk_attn_bwd_varlen(const void* q, const void* k, const void* v, const void* 
                        const float* delta, void* dq, void* dk, void* dv, int B, int N, int H, int H_KV, int D,
                        const int32_t* kv_lens, int causal, float softmax_scale, int dq_layout, int device,
                        void* cuda_stream) {
-  if (kv_lens && causal) return HK_EUNSUPPORTED;
+  return hk_attn_bwd_cross(q, k, v, d_o, lse, delta, dq, dk, dv, B, N, N, H, H_KV, D, kv_lens, causal, softmax_scale,
+                           dq_layout, device, cuda_stream);
+}
+
+int hk_attn_bwd_cross(const void* q, const void* k, const void* v, const void* d_o, const float* lse,
+                      const float* delta, void* dq, void* dk, void* dv, int B, int N, int NK, int H, int H_KV, int D,
+                      const int32_t* kv_lens, int causal, float softmax_scale, int dq_layout, int device,
+                      void* cuda_stream) {
   if (!q || !k || !v || !d_o || !lse || !delta || !dq || !dk || !dv) return HK_EINVAL;
-  if (B <= 0 || N <= 0 || H <= 0 || H_KV <= 0) return HK_EINVAL;
+  if (B <= 0 || N <= 0 || NK <= 0 || H <= 0 || H_KV <= 0) return HK_EINVAL;
   if (D != 64 && D != 128) return HK_EUNSUPPORTED;
   if (H % H_KV != 0) return HK_EINVAL;
   if (dq_layout != HK_DQ_BNHD && dq_layout != HK_DQ_BHND) return HK_EINVAL;
@@ -439,11 +476,11 @@ int hk_attn_bwd_varlen(const void* q, const void* k, const void* v, const void* 
   if (rc != HK_OK) return rc;
 
   const long long qs[3] = {(long long)N * H * D, (long long)H * D, D};
-  const long long ks[3] = {(long long)N * H_KV * D, (long long)H_KV * D, D};
+  const long long ks[3] = {(long long)NK * H_KV * D, (long long)H_KV * D, D};
   CUtensorMap tq, tk, tv, tdo;
   if ((rc = make_bnhd_map(&tq, q, B, N, H, D, qs)) != HK_OK) return rc;
-  if ((rc = make_bnhd_map(&tk, k, B, N, H_KV, D, ks)) != HK_OK) return rc;
-  if ((rc = make_bnhd_map(&tv, v, B, N, H_KV, D, ks)) != HK_OK) return rc;
+  if ((rc = make_bnhd_map(&tk, k, B, NK, H_KV, D, ks)) != HK_OK) return rc;
+  if ((rc = make_bnhd_map(&tv, v, B, NK, H_KV, D, ks)) != HK_OK) return rc;
   if ((rc = make_bnhd_map(&tdo, d_o, B, N, H, D, qs)) != HK_OK) return rc;
 
   hk::BwdParams p;
@@ -457,13 +494,14 @@ int hk_attn_bwd_varlen(const void* q, const void* k, const void* v, const void* 
   p.dq_stride_h = dq_layout == HK_DQ_BNHD ? D : (long long)N * D;
   p.B = B;
   p.N = N;
+  p.NK = NK;
   p.H = H;
   p.H_KV = H_KV;
   p.n_items = 0;
   {
     // causal sweep groups: units whose Q, dO, K and V together stay within ~64 MB of L2
     const int G = H / H_KV;
-    const long long unit_bytes = (4ll * G + 4ll) * N * D;
+    const long long unit_bytes = 4ll * G * N * D + 4ll * NK * D;
     long long u = (64ll << 20) / unit_bytes;
     p.group_units = int(u < 1 ? 1 : (u > B * H_KV ? B * H_KV : u));
   }
@@ -475,10 +513,10 @@ int hk_attn_bwd_varlen(const void* q, const void* k, const void* v, const void* 
   p.trace = g_trace_buf;
 #endif
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  if (D == 128) return causal ? launch_bwd<128, true>(tq, tk, tv, tdo, p, B, N, H, H_KV, st->sm_count, stream)
-                              : launch_bwd<128, false>(tq, tk, tv, tdo, p, B, N, H, H_KV, st->sm_count, stream);
-  return causal ? launch_bwd<64, true>(tq, tk, tv, tdo, p, B, N, H, H_KV, st->sm_count, stream)
-                : launch_bwd<64, false>(tq, tk, tv, tdo, p, B, N, H, H_KV, st->sm_count, stream);
+  if (D == 128) return causal ? launch_bwd<128, true>(tq, tk, tv, tdo, p, B, N, NK, H, H_KV, st->sm_count, stream)
+                              : launch_bwd<128, false>(tq, tk, tv, tdo, p, B, N, NK, H, H_KV, st->sm_count, stream);
+  return causal ? launch_bwd<64, true>(tq, tk, tv, tdo, p, B, N, NK, H, H_KV, st->sm_count, stream)
+                : launch_bwd<64, false>(tq, tk, tv, tdo, p, B, N, NK, H, H_KV, st->sm_count, stream);
 }
 
 int hk_attn_dq_shuffle(const void* dq_bhnd, void* dq_bnhd, int B, int N, int H, int D, int device,

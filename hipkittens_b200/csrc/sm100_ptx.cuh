@@ -320,12 +320,13 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 // 2^x for two values on the FMA and integer pipes instead of the MUFU: round x to the nearest integer n
 // with the 1.5*2^23 trick, evaluate a cubic in f = x - n on [-0.5, 0.5] (p(0) = 1 exactly, relative error
-// <= 1.02e-4), and add n to the exponent field. Inputs are clamped at -125 so the exponent stays normal.
+// <= 1.02e-4), and add n to the exponent field. Inputs are clamped at -127, where the sum of the exponent fields is
+// zero and the result exactly 0.0f: a masked score (-inf) must give p = 0, as the MUFU does.
 __device__ __forceinline__ uint64_t ex2_poly2(uint64_t x2) {
   float x0, x1;
   unpack2(x2, x0, x1);
-  x0 = fmaxf(x0, -125.0f);
-  x1 = fmaxf(x1, -125.0f);
+  x0 = fmaxf(x0, -127.0f);
+  x1 = fmaxf(x1, -127.0f);
   const uint64_t xc = pack2(x0, x1);
   const uint64_t xr = add2(xc, pack2(12582912.0f, 12582912.0f));
   const uint64_t nf = add2(xr, pack2(-12582912.0f, -12582912.0f));
@@ -344,7 +345,7 @@ __device__ __forceinline__ uint64_t ex2_poly2(uint64_t x2) {
 
 // Scalar form of the same polynomial exp2 (8 instructions, constants as immediates).
 __device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -125.0f);
+  x = fmaxf(x, -127.0f);
   const float xr = x + 12582912.0f;
   const float f = x - (xr - 12582912.0f);
   float p = fmaf(f, 0.05500893294811249f, 0.24221095442771912f);

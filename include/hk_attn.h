@@ -55,12 +55,28 @@ int hk_attn_fwd_strided(const void* q, const void* k, const void* v, void* o, fl
 /* Same forward with key padding: kv_lens is a DEVICE array int32 [B] (or NULL); batch element b attends to keys
  * [0, kv_lens[b]) only, as the reference's PyTorch path does with key_padding_mask
  * (training/llama/llama/models/attentions/base.py:97-103, used by training/bert through attention_mask). Lengths are
- * clamped to [1, N]; all N query rows are still computed. Non-causal only (HK_EUNSUPPORTED with causal != 0); strides
- * as in hk_attn_fwd_strided. KV tiles beyond a batch element's length are neither loaded nor multiplied. */
+ * clamped to [1, N]; all N query rows are still computed. KV tiles beyond a batch element's length are neither loaded
+ * nor multiplied. Strides as in hk_attn_fwd_strided. With causal != 0 the mask is aligned to the kept keys as in
+ * hk_attn_fwd_cross below (Nk = N). */
 int hk_attn_fwd_varlen(const void* q, const void* k, const void* v, void* o, float* lse,
                        int B, int N, int H, int H_KV, int D,
                        const long long* q_strides, const long long* k_strides, const long long* v_strides,
                        const int32_t* kv_lens, int causal, float softmax_scale, int device, void* cuda_stream);
+
+/* The general forward: Nq query rows against Nk keys per batch element (Nq != Nk allowed). This is what the
+ * reference's math path computes for CrossAttention(q, kv) (base.py:78-120) and what inference with a cache calls
+ * (training/llama/llama/models/mha.py:164-168: inner_cross_attn(q, kv) with kv longer than q).
+ *   q, o : bf16 [B, Nq, H, D]    k, v : bf16 [B, Nk, H_KV, D]    lse : fp32 [B, H, 1, Nq]
+ *   kv_lens : DEVICE int32 [B] or NULL; kept keys per batch element, clamped to [1, Nk] (NULL = Nk)
+ *   causal != 0: query row r sees key c iff c <= r + (kv_len_b - Nq) (and c < kv_len_b), the reference's alignment of
+ *   the mask to the last query and the last kept key (base.py:104-116). A row that sees no key at all (possible
+ *   when kv_len_b < Nq) gets O = 0 and L = -inf; the reference's -10000 fill would instead spread such a row
+ *   uniformly over masked keys, an artefact that is not reproduced.
+ * Strides as in hk_attn_fwd_strided (q_strides for [B, Nq, H], k/v_strides for [B, Nk, H_KV]). */
+int hk_attn_fwd_cross(const void* q, const void* k, const void* v, void* o, float* lse,
+                      int B, int Nq, int Nk, int H, int H_KV, int D,
+                      const long long* q_strides, const long long* k_strides, const long long* v_strides,
+                      const int32_t* kv_lens, int causal, float softmax_scale, int device, void* cuda_stream);
 
 /* Paged-KV decode: one query token per sequence attends to its whole context. No counterpart exists in
  * the reference (its nearest relative is the contiguous cache update training/llama/llama/models/mha.py:16-42).
@@ -115,11 +131,22 @@ int hk_attn_bwd(const void* q, const void* k, const void* v, const void* d_o, co
 /* hk_attn_bwd for right-padded batches: batch element b attends to its first kv_lens[b] keys only, the backward of
  * hk_attn_fwd_varlen (the reference's key_padding_mask, training/llama/llama/models/attentions/base.py:97-103; its
  * kernels have no counterpart). kv_lens: device int32 [B], values clamped to [1, N]; null = no padding. dK and dV
- * rows of padded keys come back as zeros. Non-causal only (HK_EUNSUPPORTED with causal != 0). */
+ * rows of padded keys come back as zeros. With causal != 0 the mask is aligned to the kept keys as in
+ * hk_attn_bwd_cross below (Nk = N). */
 int hk_attn_bwd_varlen(const void* q, const void* k, const void* v, const void* d_o, const float* lse,
                        const float* delta, void* dq, void* dk, void* dv, int B, int N, int H, int H_KV, int D,
                        const int32_t* kv_lens, int causal, float softmax_scale, int dq_layout, int device,
                        void* cuda_stream);
+
+/* The general backward, of hk_attn_fwd_cross: Nq query rows against Nk keys (the reference's math path for
+ * CrossAttention(q, kv), base.py:78-120, differentiated; its kernels need Nq = Nk).
+ *   q, d_o, dq : bf16 [B,Nq,H,D] (dq as dq_layout says)    k, v, dk, dv : bf16 [B,Nk,H_KV,D]
+ *   lse, delta : fp32 [B,H,1,Nq], lse as hk_attn_fwd_cross wrote it (-inf for a row that sees no key)
+ *   kv_lens and causal as in hk_attn_fwd_cross. Keys nobody sees get dK = dV = 0, rows that see no key dQ = 0. */
+int hk_attn_bwd_cross(const void* q, const void* k, const void* v, const void* d_o, const float* lse,
+                      const float* delta, void* dq, void* dk, void* dv, int B, int Nq, int Nk, int H, int H_KV, int D,
+                      const int32_t* kv_lens, int causal, float softmax_scale, int dq_layout, int device,
+                      void* cuda_stream);
 
 /* dq_bnhd[b,n,h,:] = dq_bhnd[b,h,n,:]. Replaces dispatch_dq_shuffle (attn_bkwd_prep.cpp:199-223,236-239); only
  * needed after hk_attn_bwd with HK_DQ_BHND. D a multiple of 8; the two buffers must not alias. */

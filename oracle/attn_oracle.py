@@ -73,8 +73,9 @@ def _unit(q_g: torch.Tensor, k_g: torch.Tensor, v_g: torch.Tensor, scale: float,
         col = torch.arange(s).view(1, s)
         scores = scores.masked_fill((col > row + (s - n)).unsqueeze(0), float("-inf"))
     lse = torch.logsumexp(scores, dim=-1)  # [G, N]
-    # base.py:117,119  softmax then contraction with v
-    attn = torch.exp(scores - lse.unsqueeze(-1))
+    # base.py:117,119  softmax then contraction with v. A row that sees no key (causal with fewer kept keys than
+    # queries) has lse = -inf and is defined as O = 0; the reference's -10000 fill would spread it over masked keys.
+    attn = torch.exp(scores - lse.masked_fill(torch.isinf(lse), 0.0).unsqueeze(-1))
     out = torch.einsum("gts,sd->tgd", attn, v_g)
     return out, lse
 
@@ -91,6 +92,8 @@ def attn_fwd_oracle(
 
     ``kv_lens`` [B] restricts batch element b to its first kv_lens[b] keys: the reference's
     ``key_padding_mask`` (``base.py:97-103``, True = keep), with masked logits at -inf instead of -10000.
+    With ``causal`` the mask is ``col > row + sk - Sq`` with sk the number of kept keys (``base.py:104-116``),
+    whether or not S equals N.
 
     Returns O [B,N,H,D] bf16 and L [B,H,1,N] fp32. Work is chunked per (batch, kv-head) so that the
     largest benchmark shapes fit in host memory.
@@ -106,7 +109,6 @@ def attn_fwd_oracle(
         for kh in range(hkv):
             qg = q[bi, :, kh * g:(kh + 1) * g, :].float()
             klen = k.shape[1] if kv_lens is None else int(kv_lens[bi])
-            assert kv_lens is None or not causal
             o_u, l_u = _unit(qg, k[bi, :klen, kh, :].float(), v[bi, :klen, kh, :].float(), scale, causal)
             out[bi, :, kh * g:(kh + 1) * g, :] = o_u.to(torch.bfloat16)
             lse[bi, kh * g:(kh + 1) * g, 0, :] = l_u
@@ -125,8 +127,8 @@ def attn_bwd_oracle(
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """Gradients of O = softmax(scale q k^T) v with respect to q, k, v for the upstream gradient d_o.
 
-    q, d_o [B,N,H,D], k, v [B,N,H_KV,D] (values used as given, math in `dtype`). Returns dq [B,N,H,D],
-    dk, dv [B,N,H_KV,D] and delta [B,H,1,N] = rowsum(d_o * O), all in `dtype` (no bf16 rounding: the
+    q, d_o [B,N,H,D], k, v [B,Nk,H_KV,D] (values used as given, math in `dtype`). Returns dq [B,N,H,D],
+    dk, dv [B,Nk,H_KV,D] and delta [B,H,1,N] = rowsum(d_o * O), all in `dtype` (no bf16 rounding: the
     tolerance of the comparison covers the kernels' bf16 outputs). O here is the unrounded attention
     output; the kernels compute delta from the bf16-rounded O of the forward pass
     (kernels/attn/gqa_backwards/attn_bkwd_prep.cpp:176-185). ``kv_lens`` [B] masks keys at or beyond a batch
@@ -134,28 +136,32 @@ def attn_bwd_oracle(
     """
     b, n, h, d = q.shape
     hkv = k.shape[2]
+    nk = k.shape[1]
     assert h % hkv == 0 and k.shape == v.shape and d_o.shape == q.shape
     g = h // hkv
     scale = softmax_scale if softmax_scale else 1.0 / math.sqrt(d)
     dq = torch.empty((b, n, h, d), dtype=dtype)
-    dk = torch.empty((b, n, hkv, d), dtype=dtype)
-    dv = torch.empty((b, n, hkv, d), dtype=dtype)
+    dk = torch.empty((b, nk, hkv, d), dtype=dtype)
+    dv = torch.empty((b, nk, hkv, d), dtype=dtype)
     delta = torch.empty((b, h, 1, n), dtype=dtype)
     row = torch.arange(n).view(n, 1)
-    col = torch.arange(n).view(1, n)
+    col = torch.arange(nk).view(1, nk)
     for bi in range(b):
+        klen = nk if kv_lens is None else int(kv_lens[bi])
         for kh in range(hkv):
             qg = q[bi, :, kh * g:(kh + 1) * g, :].to(dtype)      # [N, G, D]
             dog = d_o[bi, :, kh * g:(kh + 1) * g, :].to(dtype)
-            ku = k[bi, :, kh, :].to(dtype)                       # [N, D]
+            ku = k[bi, :, kh, :].to(dtype)                       # [Nk, D]
             vu = v[bi, :, kh, :].to(dtype)
             scores = torch.einsum("tgd,sd->gts", qg, ku * scale)
             if causal:
-                scores = scores.masked_fill((col > row).unsqueeze(0), float("-inf"))
+                # base.py:104-116: col > row + sk - Sq is masked, sk = kept keys
+                scores = scores.masked_fill((col > row + (klen - n)).unsqueeze(0), float("-inf"))
             if kv_lens is not None:
-                assert not causal
-                scores = scores.masked_fill((col >= int(kv_lens[bi])).unsqueeze(0), float("-inf"))
-            p = torch.softmax(scores, dim=-1)                    # [G, N, N]
+                scores = scores.masked_fill((col >= klen).unsqueeze(0), float("-inf"))
+            # a row that sees no key is defined as O = 0 (see attn_fwd_oracle): all its probabilities are zero
+            lse = torch.logsumexp(scores, dim=-1, keepdim=True)
+            p = torch.exp(scores - lse.masked_fill(torch.isinf(lse), 0.0))  # [G, N, Nk]
             o = torch.einsum("gts,sd->tgd", p, vu)
             dl = (dog * o).sum(-1)                               # [N, G]
             dp = torch.einsum("tgd,sd->gts", dog, vu)

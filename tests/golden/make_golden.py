@@ -187,7 +187,70 @@ def lse_pin_main() -> None:
               float((rowsum - 1).abs().max()))
 
 
+# (name, B, Sq, Sk, H, H_KV, D, causal, seed, kv_lens or None)
+CROSS = [
+    # a query block shorter than the keys, causal, with key padding: what inference with a cache calls
+    # (mha.py:164-168); every row sees at least one key (kept keys >= queries)
+    ("b3_q100_k256_h4_kv2_d64_causal_keypad", 3, 100, 256, 4, 2, 64, True, 11, [256, 130, 100]),
+    # plain cross attention, neither length a multiple of the tile
+    ("b2_q72_k320_h2_kv1_d128_nc", 2, 72, 320, 2, 1, 128, False, 12, None),
+    # causal self-attention on a right-padded batch: with 200 kept keys of 256 the reference's mask
+    # col > row + 200 - 256 leaves rows 0..55 of that batch element without any key
+    ("b2_n256_h2_kv1_d128_causal_keypad", 2, 256, 256, 2, 1, 128, True, 13, [256, 200]),
+    # more queries than keys, causal, no padding: the first Sq - Sk rows see nothing
+    ("b1_q300_k130_h2_kv2_d64_causal", 1, 300, 130, 2, 2, 64, True, 14, None),
+]
+
+
+def cross_main() -> None:
+    """Fixtures for Sq != Sk and for causal together with key padding, through the reference's
+    ``CrossAttention(causal=...)(q, kv, key_padding_mask=...)`` (base.py:78-120) on fp32 copies, forward and autograd
+    gradients. Where the reference's mask leaves a query row without any key its -10000 fill makes the row attend
+    uniformly to masked keys; ``row_valid`` marks the rows that see at least one key, the upstream gradient is zero
+    on the other rows (so that they contribute nothing to dK and dV in the reference either), and only valid rows of
+    O are to be compared."""
+    ref_root = reference_root()
+    sys.path.insert(0, os.path.join(ref_root, "training", "llama"))
+    from llama.models.attentions.base import CrossAttention  # noqa: E402
+
+    for name, b, sq, sk, h, hkv, d, causal, seed, lens in CROSS:
+        gen = torch.Generator().manual_seed(seed)
+        q = torch.randn((b, sq, h, d), generator=gen).to(torch.bfloat16)
+        k = torch.randn((b, sk, hkv, d), generator=gen).to(torch.bfloat16)
+        v = torch.randn((b, sk, hkv, d), generator=gen).to(torch.bfloat16)
+        d_o = torch.randn((b, sq, h, d), generator=gen).to(torch.bfloat16)
+        kept = torch.tensor(lens if lens is not None else [sk] * b)
+        keep = (torch.arange(sk).view(1, sk) < kept.view(b, 1)) if lens is not None else None
+        row_valid = (torch.arange(sq).view(1, sq) + (kept.view(b, 1) - sq) >= 0) if causal else torch.ones(b, sq, dtype=torch.bool)
+        d_o = d_o * row_valid.view(b, sq, 1, 1).to(torch.bfloat16)
+        attn = CrossAttention(causal=causal)
+        qf = q.float().requires_grad_(True)
+        kvf = torch.stack([k.float(), v.float()], dim=2).requires_grad_(True)
+        o32 = attn(qf, kvf, key_padding_mask=keep)
+        o32.backward(d_o.float())
+        kk = k.double().repeat_interleave(h // hkv, dim=2)
+        scores = torch.einsum("bthd,bshd->bhts", q.double(), kk * (1.0 / math.sqrt(d)))
+        col = torch.arange(sk).view(1, 1, 1, sk)
+        scores = scores.masked_fill(col >= kept.view(b, 1, 1, 1), float("-inf"))
+        if causal:
+            row = torch.arange(sq).view(1, 1, sq, 1)
+            scores = scores.masked_fill(col > row + (kept.view(b, 1, 1, 1) - sq), float("-inf"))
+        out = {"q": bf16_bits(q), "k": bf16_bits(k), "v": bf16_bits(v), "d_o": bf16_bits(d_o),
+               "o_ref_fp32": o32.detach().numpy().astype(np.float32), "row_valid": row_valid.numpy(),
+               "dq_ref_fp32": qf.grad.numpy().astype(np.float32),
+               "dk_ref_fp32": kvf.grad[:, :, 0].contiguous().numpy().astype(np.float32),
+               "dv_ref_fp32": kvf.grad[:, :, 1].contiguous().numpy().astype(np.float32),
+               "lse_def_fp64": torch.logsumexp(scores, dim=-1).numpy(),
+               "shape": np.array([b, sq, sk, h, hkv, d, int(causal), seed], dtype=np.int64)}
+        if lens is not None:
+            out["kv_lens"] = np.array(lens, dtype=np.int32)
+        path = os.path.join(HERE, f"cross_{name}.npz")
+        np.savez_compressed(path, **out)
+        print("wrote", path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
     main()
     rotary_main()
     lse_pin_main()
+    cross_main()

@@ -61,6 +61,38 @@ def assert_grad_parity(got, ref, name):
         assert l2 <= L2TOL, f"{name}: relative L2 error {l2}"
 
 
+def _gpu_fp32_unit_grads(q, k, v, d_o, causal):
+    """fp32 autograd restatement on the GPU of one (batch, kv-head) unit: q, d_o [N,G,D], k, v [N,D]. A checker for
+    full-size shapes (the CPU oracle on a whole tensor would take minutes); it shares nothing with the kernels or
+    with the oracle's hand-written derivative."""
+    import math
+
+    n = q.shape[0]
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    s = torch.einsum("tgd,sd->gts", qf, kf) / math.sqrt(q.shape[-1])
+    if causal:
+        s = s.masked_fill(torch.triu(torch.ones(n, n, dtype=torch.bool, device=q.device), 1), float("-inf"))
+    o = torch.einsum("gts,sd->tgd", torch.softmax(s, -1), vf)
+    o.backward(d_o.float())
+    return qf.grad, kf.grad, vf.grad
+
+
+def _assert_every_unit_matches_fp32(q, k, v, d_o, dq, dk, dv, causal):
+    """Every (batch, kv-head) unit of a full-size backward against the fp32 restatement above, with the build's
+    gradient tolerance per unit."""
+    b, n, h, d = q.shape
+    hkv = k.shape[2]
+    g = h // hkv
+    for bi in range(b):
+        for kh in range(hkv):
+            hs = slice(kh * g, (kh + 1) * g)
+            rq, rk, rv = _gpu_fp32_unit_grads(q[bi, :, hs], k[bi, :, kh], v[bi, :, kh], d_o[bi, :, hs], causal)
+            assert_grad_parity(dq[bi, :, hs], rq, f"dq unit ({bi},{kh})")
+            assert_grad_parity(dk[bi, :, kh], rk, f"dk unit ({bi},{kh})")
+            assert_grad_parity(dv[bi, :, kh], rv, f"dv unit ({bi},{kh})")
+            del rq, rk, rv
+
+
 SHAPES = [
     # B, N, H, H_KV, D, causal
     (1, 256, 8, 2, 64, False),     # BASELINE config 1
@@ -267,9 +299,85 @@ def test_key_padding_lengths(dev):
         v2[b, int(lens[b]):] = -3e4  # finite: a padded key inside a loaded tile still meets p = 0 in the products
     dq2, dk2, dv2, _, _ = run_bwd(q, k2, v2, d_o, False, dev, kv_lens=lens.to(dev))
     assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)
-    with pytest.raises(hk.HkError):
-        hk.attn_bwd(q.to(dev), k.to(dev), v.to(dev), d_o.to(dev), torch.zeros(4, 8, 1, 512, device=dev),
-                    torch.zeros(4, 8, 1, 512, device=dev), causal=True, kv_lens=lens.to(dev))
+
+
+CROSS = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "cross_*.npz")))
+
+
+@pytest.mark.parametrize("path", CROSS, ids=[os.path.basename(p) for p in CROSS])
+def test_unequal_lengths_and_causal_padding_against_reference_gradients(dev, path):
+    """hk_attn_bwd_cross against gradients autograd produced through the reference's CrossAttention with Sq != Sk
+    and with causal + key_padding_mask (base.py:104-116). The fixtures' dO is zero on rows that see no key; dq of
+    those rows is zero here and excluded from the comparison with the reference."""
+    from test_oracle import load_cross
+
+    z, q, k, v, d_o, kv_lens, causal, valid = load_cross(path)
+    dq, dk, dv, _, _ = run_bwd(q, k, v, d_o, causal, dev, kv_lens=kv_lens.to(dev) if kv_lens is not None else None)
+    rq = torch.from_numpy(z["dq_ref_fp32"]) * valid.view(*valid.shape, 1, 1)
+    assert_grad_parity(dq, rq, "dq")
+    assert_grad_parity(dk, torch.from_numpy(z["dk_ref_fp32"]), "dk")
+    assert_grad_parity(dv, torch.from_numpy(z["dv_ref_fp32"]), "dv")
+    if not bool(valid.all()):
+        assert float(dq[~valid].float().abs().max()) == 0.0
+
+
+CROSS_SHAPES = [
+    # B, Nq, Nk, H, H_KV, D, causal, kv_lens
+    (2, 128, 1024, 8, 2, 128, True, None),
+    (1, 100, 1000, 4, 4, 64, True, None),
+    (2, 300, 700, 6, 2, 128, True, [700, 301]),
+    (3, 256, 256, 4, 2, 64, True, [256, 129, 1]),
+    (1, 520, 130, 2, 1, 128, True, None),
+    (2, 1, 777, 8, 1, 128, True, [777, 5]),
+    (2, 200, 456, 4, 2, 64, False, [456, 77]),
+    (1, 640, 384, 3, 3, 128, False, None),
+    (1, 384, 640, 3, 3, 64, True, None),
+]
+
+
+@pytest.mark.parametrize("b,nq,nk,h,hkv,d,causal,lens", CROSS_SHAPES)
+def test_unequal_lengths_parity(dev, b, nq, nk, h, hkv, d, causal, lens):
+    gen = torch.Generator().manual_seed(4321 + nq + nk)
+    q = torch.randn((b, nq, h, d), generator=gen).to(torch.bfloat16)
+    k = torch.randn((b, nk, hkv, d), generator=gen).to(torch.bfloat16)
+    v = torch.randn((b, nk, hkv, d), generator=gen).to(torch.bfloat16)
+    d_o = torch.randn((b, nq, h, d), generator=gen).to(torch.bfloat16)
+    kv_lens = torch.tensor(lens, dtype=torch.int32) if lens is not None else None
+    dq, dk, dv, _, _ = run_bwd(q, k, v, d_o, causal, dev, kv_lens=kv_lens.to(dev) if kv_lens is not None else None)
+    rq, rk, rv, _ = attn_bwd_oracle(q, k, v, d_o, causal=causal, kv_lens=kv_lens)
+    assert_grad_parity(dq, rq, "dq")
+    assert_grad_parity(dk, rk, "dk")
+    assert_grad_parity(dv, rv, "dv")
+
+
+def test_module_backward_with_causal_key_padding_and_longer_kv(dev):
+    """HipCrossAttention(causal=True)(q, kv, key_padding_mask=...) with Sq < Sk through loss.backward(): the call
+    inference and padded training make (mha.py:164-168, base.py:104-116)."""
+    from hipkittens_b200.attention import HipCrossAttention
+
+    b, sq, sk, h, hkv, d = 2, 96, 320, 4, 2, 128
+    gen = torch.Generator().manual_seed(99)
+    q = torch.randn((b, sq, h, d), generator=gen).to(torch.bfloat16)
+    kv = torch.randn((b, sk, 2, hkv, d), generator=gen).to(torch.bfloat16)
+    d_o = torch.randn((b, sq, h, d), generator=gen).to(torch.bfloat16)
+    lens = torch.tensor([320, 150], dtype=torch.int32)
+    mask = torch.arange(sk).view(1, sk) < lens.view(b, 1)
+    qd = q.to(dev).requires_grad_(True)
+    kvd = kv.to(dev).requires_grad_(True)
+    out = HipCrossAttention(causal=True)(qd, kvd, key_padding_mask=mask.to(dev))
+    out.backward(d_o.to(dev))
+    o_ref, _ = attn_fwd_oracle_for_bwd(q, kv[:, :, 0], kv[:, :, 1], True, lens)
+    assert float((out.detach().float().cpu() - o_ref.float()).abs().max()) <= 2e-2
+    rq, rk, rv, _ = attn_bwd_oracle(q, kv[:, :, 0], kv[:, :, 1], d_o, causal=True, kv_lens=lens)
+    assert_grad_parity(qd.grad.cpu(), rq, "dq")
+    assert_grad_parity(kvd.grad[:, :, 0].cpu(), rk, "dk")
+    assert_grad_parity(kvd.grad[:, :, 1].cpu(), rv, "dv")
+
+
+def attn_fwd_oracle_for_bwd(q, k, v, causal, lens):
+    from oracle.attn_oracle import attn_fwd_oracle
+
+    return attn_fwd_oracle(q, k, v, causal, kv_lens=lens)
 
 
 def test_padded_rows_do_not_leak(dev):
@@ -286,7 +394,8 @@ def test_padded_rows_do_not_leak(dev):
 
 def test_full_size_identities_config2(dev):
     """BASELINE config 2 (B16 N2048 H64 H_KV8 D128), too large for the oracle as a whole: size-independent
-    identities over every (batch, kv head) unit plus oracle parity on one unit.
+    identities over every (batch, kv head) unit, every unit against an fp32 autograd restatement on the GPU, plus
+    oracle parity on one unit.
       <q, dq> == <k, dk> per unit (the output is invariant under q -> a q, k -> k / a);
       sum_s dv[s] == sum over the group's heads and rows of dO (softmax rows sum to one)."""
     b, n, h, hkv, d = 16, 2048, 64, 8, 128
@@ -308,6 +417,8 @@ def test_full_size_identities_config2(dev):
     dv_sum = dv.float().sum(1)                                                   # [B, H_KV, D]
     do_sum = d_o.float().view(b, n, hkv, g, d).sum((1, 3))
     assert float((dv_sum - do_sum).abs().max()) <= 2e-2 * float(do_sum.abs().max())
+    # every unit against the fp32 autograd restatement evaluated on the GPU
+    _assert_every_unit_matches_fp32(q, k, v, d_o, dq, dk, dv, causal=False)
     # one unit against the oracle
     bi, kh = 5, 3
     hs = slice(kh * g, (kh + 1) * g)
@@ -344,6 +455,8 @@ def test_full_size_identities_config3_causal(dev):
     dv_sum = dv.float().sum(1)
     do_sum = d_o.float().view(b, n, hkv, g, d).sum((1, 3))
     assert float((dv_sum - do_sum).abs().max()) <= 2e-2 * float(do_sum.abs().max())
+    # every unit against the fp32 autograd restatement evaluated on the GPU
+    _assert_every_unit_matches_fp32(q, k, v, d_o, dq, dk, dv, causal=True)
     # causality makes the first 256 query rows independent of everything behind them: dq of those rows equals the dq of
     # the 256-token problem (dk and dv of the first keys also collect from later queries, so only dq is compared)
     bi, kh, m = 2, 5, 256

@@ -182,8 +182,71 @@ def test_key_padding_lengths(dev):
         v2[b, int(lens[b]):] = -3e4  # finite: a padded key inside a loaded tile still meets p = 0 in the product
     o2, l2 = run_fwd(q, k2, v2, False, dev, kv_lens=lens.to(dev))
     assert torch.equal(o, o2) and torch.equal(l, l2)
-    with pytest.raises(RuntimeError):
-        hk.attn_fwd(q.to(dev), k.to(dev), v.to(dev), causal=True, kv_lens=lens.to(dev))
+
+
+CROSS = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "cross_*.npz")))
+
+
+@pytest.mark.parametrize("path", CROSS, ids=[os.path.basename(p) for p in CROSS])
+def test_unequal_lengths_and_causal_padding_against_reference_module(dev, path):
+    """hk_attn_fwd_cross against outputs of the reference's CrossAttention(causal=...)(q, kv, key_padding_mask=...)
+    with Sq != Sk (base.py:104-116 aligns the causal mask to the last query and the last kept key). Rows that see no
+    key are O = 0, L = -inf here and are not compared with the reference (its -10000 fill is an artefact)."""
+    from test_oracle import load_cross
+
+    z, q, k, v, _d_o, kv_lens, causal, valid = load_cross(path)
+    o, l = run_fwd(q, k, v, causal, dev, kv_lens=kv_lens.to(dev) if kv_lens is not None else None)
+    assert not torch.isnan(o.float()).any() and not torch.isnan(l).any()
+    o_ref = torch.from_numpy(z["o_ref_fp32"])
+    assert float((o.float() - o_ref)[valid].abs().max()) <= TOL_O
+    l_ref = torch.from_numpy(z["lse_def_fp64"]).float()
+    vh = valid.unsqueeze(1).expand_as(l_ref)
+    assert float((l[:, :, 0, :] - l_ref)[vh].abs().max()) <= TOL_L
+    if not bool(valid.all()):
+        assert float(o[~valid].float().abs().max()) == 0.0
+        assert bool((l[:, :, 0, :][~vh] == float("-inf")).all())
+
+
+CROSS_SHAPES = [
+    # B, Nq, Nk, H, H_KV, D, causal, kv_lens
+    (2, 128, 1024, 8, 2, 128, True, None),          # a 128-token chunk against a longer cache, offset 896
+    (1, 100, 1000, 4, 4, 64, True, None),           # neither a multiple of the tile: the diagonal crosses two tiles
+    (2, 300, 700, 6, 2, 128, True, [700, 301]),     # causal + padding, offsets 400 and 1
+    (3, 256, 256, 4, 2, 64, True, [256, 129, 1]),   # self-attention shape, kept keys < queries: rows without keys
+    (1, 520, 130, 2, 1, 128, True, None),           # more queries than keys: whole query blocks see nothing
+    (2, 1, 777, 8, 1, 128, True, [777, 5]),         # a single query token against a cache (decode through the prefill kernel)
+    (2, 200, 456, 4, 2, 64, False, [456, 77]),      # non-causal cross attention with padding
+    (1, 640, 384, 3, 3, 128, False, None),          # odd head count (q-block pairing), Nk < Nq
+    (1, 384, 640, 3, 3, 64, True, None),            # q-block pairs whose two blocks have different tile counts
+]
+
+
+@pytest.mark.parametrize("b,nq,nk,h,hkv,d,causal,lens", CROSS_SHAPES)
+def test_unequal_lengths_parity(dev, b, nq, nk, h, hkv, d, causal, lens):
+    gen = torch.Generator().manual_seed(1234 + nq + nk)
+    q = torch.randn((b, nq, h, d), generator=gen).to(torch.bfloat16)
+    k = torch.randn((b, nk, hkv, d), generator=gen).to(torch.bfloat16)
+    v = torch.randn((b, nk, hkv, d), generator=gen).to(torch.bfloat16)
+    kv_lens = torch.tensor(lens, dtype=torch.int32) if lens is not None else None
+    o, l = run_fwd(q, k, v, causal, dev, kv_lens=kv_lens.to(dev) if kv_lens is not None else None)
+    o_ref, l_ref = attn_fwd_oracle(q, k, v, causal, kv_lens=kv_lens)
+    assert not torch.isnan(o.float()).any() and not torch.isnan(l).any()
+    assert float((o.float() - o_ref.float()).abs().max()) <= TOL_O
+    finite = torch.isfinite(l_ref)
+    assert torch.equal(torch.isfinite(l), finite)            # rows without keys: L = -inf on both sides
+    assert float((l - l_ref)[finite].abs().max()) <= TOL_L
+    assert float(o[~finite[:, :, 0, :].transpose(1, 2)].float().abs().max() if not bool(finite.all()) else 0.0) == 0.0
+
+
+def test_chunk_against_cache_equals_rows_of_the_full_causal_forward(dev):
+    """Size-independent property of the bottom-right aligned mask: the last T query rows of a causal self-attention
+    over N tokens are exactly a T-row chunk attending causally to all N keys (chunked prefill)."""
+    q, k, v = make_prefill_inputs(2, 1024, 8, 2, 128, seed=77)
+    o_full, l_full = run_fwd(q, k, v, True, dev)
+    for t in (128, 200, 1):
+        o_c, l_c = run_fwd(q[:, -t:].contiguous(), k, v, True, dev)
+        assert torch.equal(o_c, o_full[:, -t:]) or float((o_c.float() - o_full[:, -t:].float()).abs().max()) <= 8e-3
+        assert float((l_c - l_full[:, :, :, -t:]).abs().max()) <= 1e-4
 
 
 def test_long_sequence_n16384(dev):

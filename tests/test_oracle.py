@@ -75,6 +75,43 @@ def test_lse_is_what_the_reference_backward_harness_consumes(path):
         assert float(np.abs(z[name] - ref).max()) <= 2e-5 * float(np.abs(ref).max())
 
 
+CROSS = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "cross_*.npz")))
+
+
+def load_cross(path):
+    """A cross_*.npz fixture (tests/golden/make_golden.py, cross_main): tensors and the case's parameters."""
+    z = np.load(path)
+    b, sq, sk, h, hkv, d, causal, _seed = [int(x) for x in z["shape"]]
+    q = _bf16(z["q"]).reshape(b, sq, h, d)
+    k = _bf16(z["k"]).reshape(b, sk, hkv, d)
+    v = _bf16(z["v"]).reshape(b, sk, hkv, d)
+    d_o = _bf16(z["d_o"]).reshape(b, sq, h, d)
+    kv_lens = torch.from_numpy(z["kv_lens"]) if "kv_lens" in z.files else None
+    return z, q, k, v, d_o, kv_lens, bool(causal), torch.from_numpy(z["row_valid"])
+
+
+def test_cross_fixtures_present():
+    assert len(CROSS) >= 4
+
+
+@pytest.mark.parametrize("path", CROSS, ids=[os.path.basename(p) for p in CROSS])
+def test_oracle_matches_reference_module_with_unequal_lengths_and_causal_padding(path):
+    """Sq != Sk, and causal together with key padding, against the reference's CrossAttention (base.py:104-116: the
+    causal mask is aligned to the last query and the last kept key). Rows the mask leaves without any key are O = 0,
+    L = -inf here and are excluded from the comparison (the reference's -10000 fill spreads them over masked keys)."""
+    z, q, k, v, _d_o, kv_lens, causal, valid = load_cross(path)
+    o, lse = attn_fwd_oracle(q, k, v, causal=causal, kv_lens=kv_lens)
+    o_ref = torch.from_numpy(z["o_ref_fp32"])
+    err = (o.float() - o_ref).abs() - o_ref.abs() * 2.0 ** -8
+    assert float(err[valid].max()) <= 1e-5
+    l_ref = torch.from_numpy(z["lse_def_fp64"]).float()                  # [B,H,Sq]
+    vh = valid.unsqueeze(1).expand_as(l_ref)
+    assert float((lse[:, :, 0, :] - l_ref)[vh].abs().max()) <= 2e-5
+    if not bool(valid.all()):
+        assert float(o[~valid].float().abs().max()) == 0.0
+        assert bool(torch.isinf(lse[:, :, 0, :][~vh]).all()) and bool((lse[:, :, 0, :][~vh] < 0).all())
+
+
 def test_generators_reproduce_golden_inputs():
     z = np.load([p for p in GOLDEN if "c1_" in p][0])
     b, n, h, hkv, d, _c, seed = [int(x) for x in z["shape"]]

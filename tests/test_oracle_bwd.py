@@ -38,6 +38,30 @@ def test_oracle_matches_reference_module_gradients(path):
         assert float((got - ref).abs().max()) <= 2e-5 * max(1.0, float(ref.abs().max())), name
 
 
+CROSS = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "cross_*.npz")))
+
+
+@pytest.mark.parametrize("path", CROSS, ids=[os.path.basename(p) for p in CROSS])
+def test_oracle_matches_reference_gradients_with_unequal_lengths_and_causal_padding(path):
+    """Sq != Sk and causal + key padding: gradients autograd produced through the reference's CrossAttention
+    (base.py:104-116 mask alignment). The fixtures' upstream gradient is zero on rows that see no key, so those rows
+    contribute nothing on either side; their dq is zero here (the reference's is not: it differentiates its uniform
+    attention over masked keys) and is excluded."""
+    from test_oracle import load_cross
+
+    z, q, k, v, d_o, kv_lens, causal, valid = load_cross(path)
+    dq, dk, dv, _delta = attn_bwd_oracle(q, k, v, d_o, causal=causal, kv_lens=kv_lens)
+    for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
+        ref = torch.from_numpy(z[name + "_ref_fp32"])
+        assert got.shape == ref.shape
+        diff = (got - ref).abs()
+        if name == "dq":
+            diff = diff[valid]
+        assert float(diff.max()) <= 2e-5 * float(ref.abs().max()), name
+    if not bool(valid.all()):
+        assert float(dq[~valid].abs().max()) == 0.0
+
+
 def test_oracle_matches_autograd_in_fp64():
     q, k, v = make_prefill_inputs(2, 128, 6, 2, 64, seed=31)
     d_o = torch.randn((2, 128, 6, 64), generator=torch.Generator().manual_seed(32)).to(torch.bfloat16)
