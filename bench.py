@@ -111,7 +111,7 @@ class ClockSampler:
         0x80: "hw_power_brake_slowdown",
     }
 
-    def __init__(self, device_index: int, period_s: float = 0.01):
+    def __init__(self, device_index: int, period_s: float = 0.004):
         self.period = period_s
         self.samples = []
         self.tag = None   # name of the timed region in progress (None outside timed regions)
@@ -647,6 +647,9 @@ def main() -> int:
                                           "on the data path"},
                 "roofline": prefill_roofline(args.workload, kind, ach, peaks, peaks_src, flops_per_launch),
             })
+            if strong and line["roofline"]["traffic"] is not None:
+                # the capture is of the whole workload on one GPU; a rank's launch moves its share of the units
+                line["roofline"]["traffic"] = line["roofline"]["traffic"] / world
             if e2e:
                 line["e2e"] = {"value": total_units / (e2e_ms_max / e2e["steps"] * 1e-3) / 1e12, "unit": "TFLOP/s",
                                "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],

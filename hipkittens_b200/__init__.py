@@ -34,7 +34,9 @@ from ._native import (  # noqa: F401
     paged_decode,
     paged_decode_workspace_bytes,
     paged_kv_append,
+    paged_kv_append_rotary,
     rotary,
+    rotary_bnhd,
 )
 
 __all__ = [
@@ -55,6 +57,8 @@ __all__ = [
     "load_tk_kernel_rotary",
     "paged_decode",
     "paged_kv_append",
+    "paged_kv_append_rotary",
     "paged_decode_workspace_bytes",
     "rotary",
+    "rotary_bnhd",
 ]

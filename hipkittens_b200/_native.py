@@ -31,6 +31,8 @@ EXPORTED_SYMBOLS = (
     "hk_attn_bwd_cross",
     "hk_attn_dq_shuffle",
     "hk_rotary",
+    "hk_rotary_bnhd",
+    "hk_paged_kv_append_rotary",
     "hk_attn_paged_decode_workspace_bytes",
     "hk_attn_paged_decode",
     "hk_attn_paged_decode_static",
@@ -94,6 +96,10 @@ def capi() -> ctypes.CDLL:
     lib.hk_attn_dq_shuffle.restype = ci
     lib.hk_rotary.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]
     lib.hk_rotary.restype = ci
+    lib.hk_rotary_bnhd.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, vp]
+    lib.hk_rotary_bnhd.restype = ci
+    lib.hk_paged_kv_append_rotary.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, ci, ci, ci, vp]
+    lib.hk_paged_kv_append_rotary.restype = ci
     lib.hk_attn_paged_decode_workspace_bytes.argtypes = [ci, ci, ci, ci, ci]
     lib.hk_attn_paged_decode_workspace_bytes.restype = ctypes.c_size_t
     lib.hk_attn_paged_decode.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cf, vp,
@@ -349,6 +355,27 @@ def rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, out: Optional[
     return out
 
 
+def rotary_bnhd(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, out: Optional[torch.Tensor] = None,
+                pos_offset: int = 0, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """Rotary embedding of x [B,N,H,D] bf16 (the attention entries' layout) with cos, sin [>= N + pos_offset, R/2]
+    bf16; row n of the sequence uses table row n + pos_offset. `out` may be `x` itself."""
+    for name, t in (("x", x), ("cos", cos), ("sin", sin)):
+        if not isinstance(t, torch.Tensor) or not t.is_contiguous() or t.device.type != "cuda" or t.dtype != torch.bfloat16:
+            raise RuntimeError(f"{name} must be a contiguous bf16 CUDA tensor")
+    if x.dim() != 4 or cos.dim() != 2 or cos.shape != sin.shape or cos.shape[0] < x.shape[1] + pos_offset or pos_offset < 0:
+        raise RuntimeError("x must be [B,N,H,D] and cos/sin [>= N + pos_offset, R/2]")
+    b, n, h, d = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    if out.shape != x.shape or out.dtype != x.dtype or not out.is_contiguous():
+        raise RuntimeError("out must be a contiguous bf16 tensor of x's shape")
+    _require_same_device(x, cos=cos, sin=sin, out=out)
+    s = stream if stream is not None else torch.cuda.current_stream(x.device)
+    _check(capi().hk_rotary_bnhd(x.data_ptr(), out.data_ptr(), sin.data_ptr(), cos.data_ptr(), b, n, h, d,
+                                 2 * cos.shape[1], int(pos_offset), x.device.index, s.cuda_stream), "hk_rotary_bnhd")
+    return out
+
+
 def paged_decode_workspace_bytes(s: int, h: int, d: int, max_pages: int, page_size: int = 16) -> int:
     return int(capi().hk_attn_paged_decode_workspace_bytes(s, h, d, max_pages, page_size))
 
@@ -437,6 +464,49 @@ def paged_kv_append(
                                    block_table.data_ptr(), start_pos.data_ptr(), s_n, t_n, hkv, d, page,
                                    block_table.shape[1], p_n, k_new.device.index, st.cuda_stream)
     _check(rc, "hk_paged_kv_append")
+
+
+def paged_kv_append_rotary(
+    k_new: torch.Tensor,
+    v_new: torch.Tensor,
+    k_pages: torch.Tensor,
+    v_pages: torch.Tensor,
+    block_table: torch.Tensor,
+    start_pos: torch.Tensor,
+    cos: torch.Tensor,
+    sin: torch.Tensor,
+    stream: Optional[torch.cuda.Stream] = None,
+) -> None:
+    """`paged_kv_append` with the rotary embedding of K applied on the way: token t of sequence s is rotated with row
+    start_pos[s] + t of cos / sin [rows, R/2] bf16 (V is copied). The pages end up bit-identical to `rotary_bnhd`
+    followed by `paged_kv_append` (the reference's order, mha.py:217-220 then 16-42)."""
+    for name, t in (("k_new", k_new), ("v_new", v_new), ("k_pages", k_pages), ("v_pages", v_pages)):
+        _require_cuda_bf16(name, t, 4)
+        if t.dtype != torch.bfloat16:
+            raise RuntimeError(f"{name} must be torch.bfloat16")
+    for name, t in (("cos", cos), ("sin", sin)):
+        if not t.is_contiguous() or t.dtype != torch.bfloat16 or t.dim() != 2:
+            raise RuntimeError(f"{name} must be a contiguous bf16 tensor [rows, R/2]")
+    if cos.shape != sin.shape:
+        raise RuntimeError("cos and sin must have the same shape")
+    if block_table.dtype != torch.int32 or start_pos.dtype != torch.int32:
+        raise RuntimeError("block_table and start_pos must be torch.int32")
+    if not (block_table.is_contiguous() and start_pos.is_contiguous()):
+        raise RuntimeError("Tensor must be contiguous")
+    s_n, t_n, hkv, d = k_new.shape
+    p_n, page, hkv2, d2 = k_pages.shape
+    if v_new.shape != k_new.shape or v_pages.shape != k_pages.shape or (hkv2, d2) != (hkv, d):
+        raise RuntimeError("k_new/v_new must be [S,T,H_KV,D] and k_pages/v_pages [P,page,H_KV,D]")
+    if block_table.dim() != 2 or block_table.shape[0] != s_n or start_pos.shape != (s_n,):
+        raise RuntimeError("block_table must be [S, max_pages] and start_pos [S]")
+    _require_same_device(k_new, v_new=v_new, k_pages=k_pages, v_pages=v_pages, block_table=block_table,
+                         start_pos=start_pos, cos=cos, sin=sin)
+    st = stream if stream is not None else torch.cuda.current_stream(k_new.device)
+    rc = capi().hk_paged_kv_append_rotary(k_new.data_ptr(), v_new.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(),
+                                          block_table.data_ptr(), start_pos.data_ptr(), sin.data_ptr(), cos.data_ptr(),
+                                          s_n, t_n, hkv, d, 2 * cos.shape[1], cos.shape[0], page, block_table.shape[1],
+                                          p_n, k_new.device.index, st.cuda_stream)
+    _check(rc, "hk_paged_kv_append_rotary")
 
 
 def device_status(device: int = 0) -> int:

@@ -539,10 +539,10 @@ int hk_attn_dq_shuffle(const void* dq_bhnd, void* dq_bnhd, int B, int N, int H, 
   return HK_OK;
 }
 
-int hk_rotary(const void* x, void* o, const void* sin, const void* cos, int B, int H, int N, int D, int rotary_dim,
-              int device, void* cuda_stream) {
+static int rotary_launch(const void* x, void* o, const void* sin, const void* cos, long long rows, int N, int D,
+                         int rotary_dim, int n_div, int pos0, int device, void* cuda_stream) {
   if (!x || !o || !sin || !cos) return HK_EINVAL;
-  if (B <= 0 || H <= 0 || N <= 0 || D <= 0) return HK_EINVAL;
+  if (rows <= 0 || N <= 0 || D <= 0 || pos0 < 0) return HK_EINVAL;
   if (rotary_dim <= 0) rotary_dim = D;
   if (D % 8 != 0 || rotary_dim % 16 != 0 || rotary_dim > D) return HK_EUNSUPPORTED;
   if (!aligned16(x) || !aligned16(o) || !aligned16(sin) || !aligned16(cos)) return HK_EINVAL;
@@ -555,10 +555,12 @@ int hk_rotary(const void* x, void* o, const void* sin, const void* cos, int B, i
   p.o = static_cast<__nv_bfloat16*>(o);
   p.cos = static_cast<const __nv_bfloat16*>(cos);
   p.sin = static_cast<const __nv_bfloat16*>(sin);
-  p.rows = static_cast<long long>(B) * H * N;
+  p.rows = rows;
   p.N = N;
   p.D = D;
   p.R = rotary_dim;
+  p.n_div = n_div;
+  p.pos0 = pos0;
   const long long units = p.rows * (rotary_dim / 16 + (D - rotary_dim) / 8);
   const long long blocks = (units + 255) / 256;
   if (blocks > 0x7fffffffll) return HK_EINVAL;
@@ -566,6 +568,19 @@ int hk_rotary(const void* x, void* o, const void* sin, const void* cos, int B, i
   g_launches.fetch_add(1, std::memory_order_relaxed);
   HK_CUDA(cudaGetLastError());
   return HK_OK;
+}
+
+int hk_rotary(const void* x, void* o, const void* sin, const void* cos, int B, int H, int N, int D, int rotary_dim,
+              int device, void* cuda_stream) {
+  if (B <= 0 || H <= 0) return HK_EINVAL;
+  return rotary_launch(x, o, sin, cos, static_cast<long long>(B) * H * N, N, D, rotary_dim, 1, 0, device, cuda_stream);
+}
+
+int hk_rotary_bnhd(const void* x, void* o, const void* sin, const void* cos, int B, int N, int H, int D,
+                   int rotary_dim, int pos_offset, int device, void* cuda_stream) {
+  if (B <= 0 || H <= 0) return HK_EINVAL;
+  return rotary_launch(x, o, sin, cos, static_cast<long long>(B) * N * H, N, D, rotary_dim, H, pos_offset, device,
+                       cuda_stream);
 }
 
 size_t hk_attn_paged_decode_workspace_bytes(int S, int H, int D, int max_pages_per_seq, int page_size) {
@@ -643,6 +658,52 @@ int hk_paged_kv_append(const void* k_new, const void* v_new, void* k_pages, void
   const long long max_blocks = static_cast<long long>(st->sm_count) * 16;  // 16 x 128 threads fill an SM
   const unsigned blocks = static_cast<unsigned>(groups < max_blocks ? groups : max_blocks);
   hk::paged_kv_append_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(cuda_stream)>>>(p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  HK_CUDA(cudaGetLastError());
+  return HK_OK;
+}
+
+int hk_paged_kv_append_rotary(const void* k_new, const void* v_new, void* k_pages, void* v_pages,
+                              const int32_t* block_table, const int32_t* start_pos, const void* sin, const void* cos,
+                              int S, int T, int H_KV, int D, int rotary_dim, int cos_rows, int page_size,
+                              int max_pages_per_seq, int num_pages, int device, void* cuda_stream) {
+  if (!k_new || !v_new || !k_pages || !v_pages || !block_table || !start_pos || !sin || !cos) return HK_EINVAL;
+  if (S <= 0 || T <= 0 || H_KV <= 0 || D <= 0 || max_pages_per_seq <= 0 || num_pages <= 0 || cos_rows <= 0)
+    return HK_EINVAL;
+  if (page_size != hk::kPageTokens) return HK_EUNSUPPORTED;
+  if (rotary_dim <= 0) rotary_dim = D;
+  if (D % 8 != 0 || rotary_dim % 16 != 0 || rotary_dim > D) return HK_EUNSUPPORTED;
+  if (T > 65535 || S > 65535) return HK_EINVAL;
+  if (!aligned16(k_new) || !aligned16(v_new) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(sin) ||
+      !aligned16(cos))
+    return HK_EINVAL;
+  DeviceState* st = nullptr;
+  DeviceScope scope;
+  int rc = scope.enter(device, &st);
+  if (rc != HK_OK) return rc;
+  hk::AppendRotaryParams q;
+  q.a.k_new = static_cast<const __nv_bfloat16*>(k_new);
+  q.a.v_new = static_cast<const __nv_bfloat16*>(v_new);
+  q.a.k_pages = static_cast<__nv_bfloat16*>(k_pages);
+  q.a.v_pages = static_cast<__nv_bfloat16*>(v_pages);
+  q.a.block_table = block_table;
+  q.a.start_pos = start_pos;
+  q.a.S = S;
+  q.a.T = T;
+  q.a.row_vec16 = H_KV * D * 2 / 16;
+  q.a.max_pages = max_pages_per_seq;
+  q.a.num_pages = num_pages;
+  q.a.status = st->status;
+  q.cos = static_cast<const __nv_bfloat16*>(cos);
+  q.sin = static_cast<const __nv_bfloat16*>(sin);
+  q.cos_rows = cos_rows;
+  q.H_KV = H_KV;
+  q.D = D;
+  q.R = rotary_dim;
+  const long long tokens = static_cast<long long>(S) * T;
+  const long long max_blocks = static_cast<long long>(st->sm_count) * 16;  // 16 x 128 threads fill an SM
+  const unsigned blocks = static_cast<unsigned>(tokens < max_blocks ? tokens : max_blocks);
+  hk::paged_kv_append_rotary_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(cuda_stream)>>>(q);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   HK_CUDA(cudaGetLastError());
   return HK_OK;

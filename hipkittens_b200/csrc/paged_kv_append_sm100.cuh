@@ -12,6 +12,7 @@
 #include <stdint.h>
 
 #include "paged_decode_sm100.cuh"
+#include "rotary_sm100.cuh"
 
 namespace hk {
 
@@ -70,6 +71,74 @@ __global__ void __launch_bounds__(128) paged_kv_append_kernel(const AppendParams
         if (dst[u] < 0) continue;
         reinterpret_cast<uint4*>(p.k_pages)[dst[u] + i] = kv[u];
         reinterpret_cast<uint4*>(p.v_pages)[dst[u] + i] = vv[u];
+      }
+    }
+  }
+}
+
+// The same append with the rotary embedding of K applied on the way (the reference rotates q and k with a separate
+// kernel before the cache update, training/llama/llama/models/mha.py:217-220 then 16-42; fused here, K is read once
+// and written once, rotated, instead of being rewritten by a pre-pass first). Token t of sequence s has position
+// start_pos[s] + t, which selects its row of cos / sin [cos_rows, R/2]; arithmetic is rotary_kernel's (every product
+// and sum rounded to bf16), so the pages hold bit-for-bit what the pre-pass followed by the plain append would.
+struct AppendRotaryParams {
+  AppendParams a;
+  const __nv_bfloat16* cos;   // [cos_rows, R/2]
+  const __nv_bfloat16* sin;
+  int cos_rows, H_KV, D, R;
+};
+
+__global__ void __launch_bounds__(128) paged_kv_append_rotary_kernel(const AppendRotaryParams q) {
+  const AppendParams& p = q.a;
+  const long long total = static_cast<long long>(p.S) * p.T;
+  const int half = q.R / 2;
+  const int pair_units = q.R / 16;                      // 8 rotated pairs each
+  const int units_per_head = pair_units + (q.D - q.R) / 8;
+  const int k_units = q.H_KV * units_per_head;
+  for (long long tok = blockIdx.x; tok < total; tok += gridDim.x) {
+    const int s = static_cast<int>(tok / p.T), t = static_cast<int>(tok - static_cast<long long>(s) * p.T);
+    const int pos = p.start_pos[s] + t;
+    const int page_slot = pos / kPageTokens;
+    if (pos < 0 || page_slot >= p.max_pages || pos >= q.cos_rows) {
+      if (threadIdx.x == 0) atomicCAS(p.status, 0, kStatusBadPage);  // outside the block table or the cos / sin table
+      continue;
+    }
+    const int id = p.block_table[size_t(s) * p.max_pages + page_slot];
+    if (id < 0 || id >= p.num_pages) {  // never write through an id outside the pool
+      if (threadIdx.x == 0) atomicCAS(p.status, 0, kStatusBadPage);
+      continue;
+    }
+    const long long dst = (static_cast<long long>(id) * kPageTokens + pos % kPageTokens) * p.row_vec16;
+    const long long src = tok * p.row_vec16;
+    // V: plain copy
+    for (int i = threadIdx.x; i < p.row_vec16; i += blockDim.x)
+      reinterpret_cast<uint4*>(p.v_pages)[dst + i] = reinterpret_cast<const uint4*>(p.v_new)[src + i];
+    // K: rotated pairs, then the dimensions beyond the rotary dimension
+    const __nv_bfloat16* krow = p.k_new + src * 8;
+    __nv_bfloat16* kdst = p.k_pages + dst * 8;
+    for (int i = threadIdx.x; i < k_units; i += blockDim.x) {
+      const int head = i / units_per_head, u = i - head * units_per_head;
+      const __nv_bfloat16* xr = krow + head * q.D;
+      __nv_bfloat16* orow = kdst + head * q.D;
+      if (u < pair_units) {
+        const uint4 x1 = *reinterpret_cast<const uint4*>(xr + u * 8);
+        const uint4 x2 = *reinterpret_cast<const uint4*>(xr + half + u * 8);
+        const uint4 c = __ldg(reinterpret_cast<const uint4*>(q.cos + static_cast<size_t>(pos) * half + u * 8));
+        const uint4 sn = __ldg(reinterpret_cast<const uint4*>(q.sin + static_cast<size_t>(pos) * half + u * 8));
+        uint4 lo, hi;
+        lo.x = rot_lo(x1.x, x2.x, c.x, sn.x);
+        lo.y = rot_lo(x1.y, x2.y, c.y, sn.y);
+        lo.z = rot_lo(x1.z, x2.z, c.z, sn.z);
+        lo.w = rot_lo(x1.w, x2.w, c.w, sn.w);
+        hi.x = rot_hi(x1.x, x2.x, c.x, sn.x);
+        hi.y = rot_hi(x1.y, x2.y, c.y, sn.y);
+        hi.z = rot_hi(x1.z, x2.z, c.z, sn.z);
+        hi.w = rot_hi(x1.w, x2.w, c.w, sn.w);
+        *reinterpret_cast<uint4*>(orow + u * 8) = lo;
+        *reinterpret_cast<uint4*>(orow + half + u * 8) = hi;
+      } else {
+        const int off = q.R + (u - pair_units) * 8;
+        *reinterpret_cast<uint4*>(orow + off) = *reinterpret_cast<const uint4*>(xr + off);
       }
     }
   }

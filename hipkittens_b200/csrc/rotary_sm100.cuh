@@ -10,6 +10,9 @@
 // separately (__hmul2 / __hsub2 / __hadd2 there; the explicitly rounded, never-fused intrinsics here), so the result is
 // bit-identical to that expression.
 //
+// The same kernel serves x [B, N, H, D], the layout the attention kernels read (RotaryParams::n_div = H), so that q
+// and k can be rotated where they lie, without the transposes the [B, H, N, D] form needs around it.
+//
 // Pure streaming: 16-byte loads and stores, one thread per 8 rotated pairs. HBM-bound: 2 x B*H*N*D*2 bytes per call;
 // cos / sin (N * R bytes each) stay in L2.
 #pragma once
@@ -27,6 +30,8 @@ struct RotaryParams {
   const __nv_bfloat16* sin;  // [N, R/2]
   long long rows;
   int N, D, R;
+  int n_div;   // the position of row r is (r / n_div) % N + pos0: 1 for [B,H,N,D], H for [B,N,H,D]
+  int pos0;    // position of sequence index 0 (a chunk that continues a cached prefix starts at its offset)
 };
 
 __device__ __forceinline__ uint32_t rot_lo(uint32_t x1, uint32_t x2, uint32_t c, uint32_t s) {
@@ -58,7 +63,7 @@ __global__ void __launch_bounds__(256) rotary_kernel(const RotaryParams p) {
   const __nv_bfloat16* xr = p.x + row * p.D;
   __nv_bfloat16* orow = p.o + row * p.D;
   if (u < pair_units) {
-    const int n = static_cast<int>(row % p.N);
+    const int n = static_cast<int>((row / p.n_div) % p.N) + p.pos0;
     const int half = p.R / 2;
     const uint4 x1 = *reinterpret_cast<const uint4*>(xr + u * 8);
     const uint4 x2 = *reinterpret_cast<const uint4*>(xr + half + u * 8);

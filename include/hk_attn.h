@@ -164,6 +164,14 @@ int hk_attn_dq_shuffle(const void* dq_bhnd, void* dq_bnhd, int B, int N, int H, 
 int hk_rotary(const void* x, void* o, const void* sin, const void* cos, int B, int H, int N, int D, int rotary_dim,
               int device, void* cuda_stream);
 
+/* hk_rotary for x, o in the layout the attention entries read, bf16 [B, N, H, D], so that q and k are rotated where
+ * they lie (the reference's kernel wants [B, H, N, D], kernels/rotary/kernel.cpp:44-98, and its call site rotates
+ * before attention, training/llama/llama/models/mha.py:217-220). Row n of the sequence takes row n + pos_offset of
+ * sin / cos [>= N + pos_offset, rotary_dim / 2]: a chunk that continues a cached prefix passes the prefix length.
+ * Same arithmetic as hk_rotary (bit-identical results); x and o may be the same buffer. */
+int hk_rotary_bnhd(const void* x, void* o, const void* sin, const void* cos, int B, int N, int H, int D,
+                   int rotary_dim, int pos_offset, int device, void* cuda_stream);
+
 /* Appends T new tokens per sequence to the paged KV cache read by hk_attn_paged_decode.
  * Paged counterpart of the reference's contiguous cache update, kv_cache[b, offset : offset + T] = kv
  * (training/llama/llama/models/mha.py:16-42, _update_kv_cache).
@@ -177,6 +185,17 @@ int hk_paged_kv_append(const void* k_new, const void* v_new, void* k_pages, void
                        const int32_t* block_table, const int32_t* start_pos,
                        int S, int T, int H_KV, int D, int page_size, int max_pages_per_seq, int num_pages,
                        int device, void* cuda_stream);
+
+/* hk_paged_kv_append with the rotary embedding of K fused in: k_new is rotated on its way into the pages (V is
+ * copied), token t of sequence s with row start_pos[s] + t of sin / cos [cos_rows, rotary_dim / 2]. The reference
+ * rotates k with its rotary kernel and then updates the cache (mha.py:217-220, then 16-42); the pages end up
+ * bit-identical to hk_rotary_bnhd followed by hk_paged_kv_append, with one read and one write of K instead of two.
+ * rotary_dim <= 0 selects D; D a multiple of 8, rotary_dim a multiple of 16. A position at or beyond cos_rows is
+ * skipped and reported like a position beyond the block table (HK_EBADPAGE). */
+int hk_paged_kv_append_rotary(const void* k_new, const void* v_new, void* k_pages, void* v_pages,
+                              const int32_t* block_table, const int32_t* start_pos, const void* sin, const void* cos,
+                              int S, int T, int H_KV, int D, int rotary_dim, int cos_rows, int page_size,
+                              int max_pages_per_seq, int num_pages, int device, void* cuda_stream);
 
 /* Paged-KV decode for callers that cannot allocate device memory. No counterpart in the reference.
  *
