@@ -53,6 +53,8 @@ WORKLOADS = {
     "paged_kv_append_s16_t2048_kv8_d128": ("append", 16, 2048, 64, 8, 128, False),
     # reduced copies of the above for ncu captures (same kernels and tile shapes, inputs still beyond L2)
     "profile_gqa_fwd_b4_n2048_h64_kv8_d128": ("fwd", 4, 2048, 64, 8, 128, False),
+    "profile_gqa_causal_fwd_b2_n8192_h64_kv8_d128": ("fwd", 2, 8192, 64, 8, 128, True),
+    "profile_mha_fwd_b8_n4096_h16_d64": ("fwd", 8, 4096, 16, 16, 64, False),
     "profile_paged_decode_s14_ctx512_8192_h64_kv8_d128": ("decode", 14, 0, 64, 8, 128, False),
     "profile_gqa_bwd_b4_n2048_h64_kv8_d128": ("bwd", 4, 2048, 64, 8, 128, False),
 }
@@ -64,12 +66,12 @@ DEFAULT_WORKLOAD = "gqa_fwd_b16_n2048_h64_kv8_d128"
 # summarised under profiles/ (None = not captured for that workload).
 NCU_TRAFFIC_BYTES = {
     # 4 x the B=4 capture (260.2 MB per launch; traffic grows with the (batch, kv-head) units)
-    "gqa_fwd_b16_n2048_h64_kv8_d128": 4 * 260.2e6,
-    # metric captures of the full workloads (profiles/attn_fwd_kernel_causal_d128_and_mha_d64.md)
-    "gqa_causal_fwd_b4_n8192_h64_kv8_d128": 1.109e9 + 0.520e9,
-    "mha_fwd_b16_n4096_h16_d64": 0.404e9 + 0.118e9,
+    "gqa_fwd_b16_n2048_h64_kv8_d128": 4 * 259.5e6,
+    # 2 x the B=2 / B=8 captures (profiles/attn_fwd_kernel_causal_d128_and_mha_d64.md)
+    "gqa_causal_fwd_b4_n8192_h64_kv8_d128": 2 * (335.9e6 + 229.7e6),
+    "mha_fwd_b16_n4096_h16_d64": 2 * (201.4e6 + 48.4e6),
     # backward, 4 x the B=4 capture of the two main kernels (profiles/attn_bwd_kernels_gqa_bwd_d128.md) + the prep kernel
-    "gqa_bwd_b16_n2048_h64_kv8_d128": 4 * (358.2e6 + 413.1e6) + 1.082e9,
+    "gqa_bwd_b16_n2048_h64_kv8_d128": 4 * (358.7e6 + 412.7e6) + 1.082e9,
     # rate x duration of the section capture (profiles/rotary_kernel_and_paged_kv_append_kernel.md)
     "rotary_b16_h16_n2048_d128": 216.6e6,
     "paged_kv_append_s16_t2048_kv8_d128": 222.6e6,
