@@ -307,110 +307,225 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         ++s_cnt;
         tc_fence_after();
         HK_STAMP(slot, 1);
-        uint32_t su[kBlockN];  // one row of S, fp32 bit patterns
+        if constexpr (kSepP) {
+          uint32_t su[kBlockN];  // one row of S, fp32 bit patterns
 #define HK_S(i) __uint_as_float(su[(i)])
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) tmem_ld32(tS + cc * 32, su + cc * 32);
-        tmem_wait_ld();
-        HK_STAMP2(slot, 2);
-        if (kSepP) {
-          // S(j) is in registers: the issuer may overwrite it with the next S of this slot right away
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&s_free[slot]);
-        }
-        if (CAUSAL && (j + 1) * kBlockN - 1 > min(w.qb[slot] * kBlockM + w.off, w.kv_len - 1)) {
-          // a tile the diagonal (or the end of the keys) runs through - the last one, and the one before it when
-          // off is not a multiple of the tile: key j*128 + i is visible to query row r iff it is <= r + off and
-          // < kv_len. (CTA-uniform condition: the first row of the block sees the fewest keys.)
-          const int lim = min(w.qb[slot] * kBlockM + row + w.off, w.kv_len - 1) - j * kBlockN;
+          for (int cc = 0; cc < 4; ++cc) tmem_ld32(tS + cc * 32, su + cc * 32);
+          tmem_wait_ld();
+          HK_STAMP2(slot, 2);
+          if (kSepP) {
+            // S(j) is in registers: the issuer may overwrite it with the next S of this slot right away
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_free[slot]);
+          }
+          if (CAUSAL && (j + 1) * kBlockN - 1 > min(w.qb[slot] * kBlockM + w.off, w.kv_len - 1)) {
+            // a tile the diagonal (or the end of the keys) runs through - the last one, and the one before it when
+            // off is not a multiple of the tile: key j*128 + i is visible to query row r iff it is <= r + off and
+            // < kv_len. (CTA-uniform condition: the first row of the block sees the fewest keys.)
+            const int lim = min(w.qb[slot] * kBlockM + row + w.off, w.kv_len - 1) - j * kBlockN;
 #pragma unroll
-          for (int i = 0; i < kBlockN; ++i) su[i] = (i > lim) ? 0xff800000u : su[i];
-        }
-        if (!CAUSAL && j == nkv - 1 && (w.kv_len & (kBlockN - 1)) != 0) {
-          // partial last tile: keys at or beyond the length are padding (or, beyond N, zeros filled by TMA)
-          const int rem = w.kv_len - j * kBlockN;
+            for (int i = 0; i < kBlockN; ++i) su[i] = (i > lim) ? 0xff800000u : su[i];
+          }
+          if (!CAUSAL && j == nkv - 1 && (w.kv_len & (kBlockN - 1)) != 0) {
+            // partial last tile: keys at or beyond the length are padding (or, beyond N, zeros filled by TMA)
+            const int rem = w.kv_len - j * kBlockN;
 #pragma unroll
-          for (int i = 0; i < kBlockN; ++i) su[i] = (i >= rem) ? 0xff800000u : su[i];
-        }
-        float bm0 = fmaxf(HK_S(0), HK_S(1)), bm1 = fmaxf(HK_S(2), HK_S(3));
-        float bm2 = fmaxf(HK_S(4), HK_S(5)), bm3 = fmaxf(HK_S(6), HK_S(7));
+            for (int i = 0; i < kBlockN; ++i) su[i] = (i >= rem) ? 0xff800000u : su[i];
+          }
+          float bm0 = fmaxf(HK_S(0), HK_S(1)), bm1 = fmaxf(HK_S(2), HK_S(3));
+          float bm2 = fmaxf(HK_S(4), HK_S(5)), bm3 = fmaxf(HK_S(6), HK_S(7));
 #pragma unroll
-        for (int i = 8; i < kBlockN; i += 8) {
-          bm0 = max3(bm0, HK_S(i), HK_S(i + 1));
-          bm1 = max3(bm1, HK_S(i + 2), HK_S(i + 3));
-          bm2 = max3(bm2, HK_S(i + 4), HK_S(i + 5));
-          bm3 = max3(bm3, HK_S(i + 6), HK_S(i + 7));
-        }
-        const float bm = fmaxf(fmaxf(bm0, bm2), fmaxf(bm1, bm3));
-        if (kSepP && pv_cnt > 0) {
-          // S(j) may be ready before O += P(j-1) V(j-1) has finished: wait for that product before
-          // rescaling O or overwriting P
-          ok = mbar_wait(&p_free[slot], (pv_cnt - 1) & 1, abortp, kWaitLimitCycles);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-        }
-        ++pv_cnt;
-        if (j == 0) {
-          m = bm;
+          for (int i = 8; i < kBlockN; i += 8) {
+            bm0 = max3(bm0, HK_S(i), HK_S(i + 1));
+            bm1 = max3(bm1, HK_S(i + 2), HK_S(i + 3));
+            bm2 = max3(bm2, HK_S(i + 4), HK_S(i + 5));
+            bm3 = max3(bm3, HK_S(i + 6), HK_S(i + 7));
+          }
+          const float bm = fmaxf(fmaxf(bm0, bm2), fmaxf(bm1, bm3));
+          if (kSepP && pv_cnt > 0) {
+            // S(j) may be ready before O += P(j-1) V(j-1) has finished: wait for that product before
+            // rescaling O or overwriting P
+            ok = mbar_wait(&p_free[slot], (pv_cnt - 1) & 1, abortp, kWaitLimitCycles);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          ++pv_cnt;
+          if (j == 0) {
+            m = bm;
+          } else {
+            const float m_new = fmaxf(m, bm);
+            const bool grow = (m_new - m) * c > kRescaleThresholdLog2;
+            if (__any_sync(0xffffffffu, grow)) {
+              // The previous PV of this slot has completed (the commit that released this S tile
+              // was issued after it), so O is stable and nothing writes it until we publish P.
+              const float alpha = ex2_approx((m - m_new) * c);
+              l *= alpha;
+              m = m_new;
+#pragma unroll
+              for (int cc = 0; cc < D / 32; ++cc) {
+                uint32_t o[32];
+                tmem_ld32(tO + cc * 32, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                tmem_st32(tO + cc * 32, o);
+              }
+            }
+          }
+          // p = exp2(s*c - m*c), two columns per instruction where the hardware has packed fp32 forms.
+          // Of every kEmuMod column pairs, kEmuCnt compute exp2 on the FMA pipe (polynomial), the rest on
+          // the MUFU.
+          HK_STAMP2(slot, 3);
+          const uint64_t c2 = pack2(c, c);
+          // a causal row that has seen no key yet has m = -inf: subtract nothing, its exponentials are exp2(-inf) = 0
+          const float nmc = (CAUSAL && m == -INFINITY) ? 0.f : -(m * c);
+          const uint64_t nmc2 = pack2(nmc, nmc);
+          uint64_t lacc0 = pack2(0.f, 0.f), lacc1 = pack2(0.f, 0.f);
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const uint64_t x2 = fma2(pack2(HK_S(cc * 32 + 2 * i), HK_S(cc * 32 + 2 * i + 1)), c2, nmc2);
+              uint64_t p2;
+              float p0, p1;
+              if ((i % kEmuMod) < kEmuCnt) {
+                p2 = ex2_poly2(x2);
+                unpack2(p2, p0, p1);
+              } else {
+                float x0, x1;
+                unpack2(x2, x0, x1);
+                p0 = ex2_approx(x0);
+                p1 = ex2_approx(x1);
+                p2 = pack2(p0, p1);
+              }
+              if (i & 1) lacc1 = add2(lacc1, p2); else lacc0 = add2(lacc0, p2);
+              pk[i] = pack_bf16x2(p0, p1);
+            }
+            tmem_st16(tP + cc * 16, pk);
+          }
+          {
+            float a0, a1, b0, b1;
+            unpack2(lacc0, a0, a1);
+            unpack2(lacc1, b0, b1);
+            l += (a0 + a1) + (b0 + b1);
+          }
+#undef HK_S
         } else {
-          const float m_new = fmaxf(m, bm);
-          const bool grow = (m_new - m) * c > kRescaleThresholdLog2;
-          if (__any_sync(0xffffffffu, grow)) {
-            // The previous PV of this slot has completed (the commit that released this S tile
-            // was issued after it), so O is stable and nothing writes it until we publish P.
-            const float alpha = ex2_approx((m - m_new) * c);
-            l *= alpha;
-            m = m_new;
+          // ---- D = 128. Any reference value m within ~100 powers of two of a row's true maximum gives the same O
+          // and L: p = exp2(s*c - m*c) neither overflows nor loses the row's largest terms, P keeps its relative
+          // precision in bf16, and L = m*scale + ln(l) does not care which m it was. So after the first tile of an
+          // item the row maximum is not computed at all (it costs ~240 clocks of the chain S -> softmax -> P V that
+          // bounds this kernel): the exponentials are taken against the m the row already has and P is held in
+          // registers until the row sums are known. Only if one of them is huge or not finite is the tile redone
+          // the exact way, with its maximum and the rescaling of O; S is still intact in TMEM then, because nothing
+          // has been stored over it.
+          uint32_t su[kBlockN];  // one row of S, fp32 bit patterns
+#define HK_S(i) __uint_as_float(su[(i)])
+          auto load_scores = [&]() {
 #pragma unroll
-            for (int cc = 0; cc < D / 32; ++cc) {
-              uint32_t o[32];
-              tmem_ld32(tO + cc * 32, o);
-              tmem_wait_ld();
+            for (int cc = 0; cc < 4; ++cc) tmem_ld32(tS + cc * 32, su + cc * 32);
+            tmem_wait_ld();
+            if (CAUSAL && (j + 1) * kBlockN - 1 > min(w.qb[slot] * kBlockM + w.off, w.kv_len - 1)) {
+              // a tile the diagonal (or the end of the keys) runs through - the last one, and the one before it
+              // when off is not a multiple of the tile: key j*128 + i is visible to query row r iff it is
+              // <= r + off and < kv_len. (CTA-uniform condition: the first row of the block sees the fewest keys.)
+              const int lim = min(w.qb[slot] * kBlockM + row + w.off, w.kv_len - 1) - j * kBlockN;
 #pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              tmem_st32(tO + cc * 32, o);
+              for (int i = 0; i < kBlockN; ++i) su[i] = (i > lim) ? 0xff800000u : su[i];
             }
-          }
-        }
-        // p = exp2(s*c - m*c), two columns per instruction where the hardware has packed fp32 forms.
-        // Of every kEmuMod column pairs, kEmuCnt compute exp2 on the FMA pipe (polynomial), the rest on
-        // the MUFU.
-        HK_STAMP2(slot, 3);
-        const uint64_t c2 = pack2(c, c);
-        // a causal row that has seen no key yet has m = -inf: subtract nothing, its exponentials are exp2(-inf) = 0
-        const float nmc = (CAUSAL && m == -INFINITY) ? 0.f : -(m * c);
-        const uint64_t nmc2 = pack2(nmc, nmc);
-        uint64_t lacc0 = pack2(0.f, 0.f), lacc1 = pack2(0.f, 0.f);
+            if (!CAUSAL && j == nkv - 1 && (w.kv_len & (kBlockN - 1)) != 0) {
+              // partial last tile: keys at or beyond the length are padding (or, beyond N, zeros filled by TMA)
+              const int rem = w.kv_len - j * kBlockN;
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const uint64_t x2 = fma2(pack2(HK_S(cc * 32 + 2 * i), HK_S(cc * 32 + 2 * i + 1)), c2, nmc2);
-            uint64_t p2;
-            float p0, p1;
-            if ((i % kEmuMod) < kEmuCnt) {
-              p2 = ex2_poly2(x2);
-              unpack2(p2, p0, p1);
-            } else {
-              float x0, x1;
-              unpack2(x2, x0, x1);
-              p0 = ex2_approx(x0);
-              p1 = ex2_approx(x1);
-              p2 = pack2(p0, p1);
+              for (int i = 0; i < kBlockN; ++i) su[i] = (i >= rem) ? 0xff800000u : su[i];
             }
-            if (i & 1) lacc1 = add2(lacc1, p2); else lacc0 = add2(lacc0, p2);
-            pk[i] = pack_bf16x2(p0, p1);
+          };
+          load_scores();
+          HK_STAMP2(slot, 2);
+          // the first tile fixes m; so does any tile of a row that has not seen a key yet (only possible with more
+          // queries than kept keys, off < 0)
+          bool exact = j == 0 || (CAUSAL && w.off < 0 && __any_sync(0xffffffffu, m == -INFINITY));
+          uint32_t pk[kBlockN / 2];
+          float l_tile;
+          for (;;) {
+            if (exact) {
+              float bm0 = fmaxf(HK_S(0), HK_S(1)), bm1 = fmaxf(HK_S(2), HK_S(3));
+              float bm2 = fmaxf(HK_S(4), HK_S(5)), bm3 = fmaxf(HK_S(6), HK_S(7));
+#pragma unroll
+              for (int i = 8; i < kBlockN; i += 8) {
+                bm0 = max3(bm0, HK_S(i), HK_S(i + 1));
+                bm1 = max3(bm1, HK_S(i + 2), HK_S(i + 3));
+                bm2 = max3(bm2, HK_S(i + 4), HK_S(i + 5));
+                bm3 = max3(bm3, HK_S(i + 6), HK_S(i + 7));
+              }
+              const float bm = fmaxf(fmaxf(bm0, bm2), fmaxf(bm1, bm3));
+              if (j == 0) {
+                m = bm;
+              } else {
+                const float m_new = fmaxf(m, bm);
+                const bool grow = (m_new - m) * c > kRescaleThresholdLog2;
+                if (__any_sync(0xffffffffu, grow)) {
+                  // The previous PV of this slot has completed (the commit that released this S tile was issued
+                  // after it), so O is stable and nothing writes it until we publish P.
+                  const float alpha = (m == -INFINITY) ? 0.f : ex2_approx((m - m_new) * c);
+                  l *= alpha;
+                  m = m_new;
+#pragma unroll
+                  for (int cc = 0; cc < D / 32; ++cc) {
+                    uint32_t o[32];
+                    tmem_ld32(tO + cc * 32, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st32(tO + cc * 32, o);
+                  }
+                }
+              }
+            }
+            // p = exp2(s*c - m*c), two columns per instruction where the hardware has packed fp32 forms
+            HK_STAMP2(slot, 3);
+            const uint64_t c2 = pack2(c, c);
+            // a causal row that has seen no key yet has m = -inf: subtract nothing, its exponentials are exp2(-inf) = 0
+            const float nmc = (CAUSAL && m == -INFINITY) ? 0.f : -(m * c);
+            const uint64_t nmc2 = pack2(nmc, nmc);
+            uint64_t lacc0 = pack2(0.f, 0.f), lacc1 = pack2(0.f, 0.f);
+#pragma unroll
+            for (int i = 0; i < kBlockN / 2; ++i) {
+              const uint64_t x2 = fma2(pack2(HK_S(2 * i), HK_S(2 * i + 1)), c2, nmc2);
+              uint64_t p2;
+              float p0, p1;
+              if ((i % kEmuMod) < kEmuCnt) {
+                p2 = ex2_poly2(x2);
+                unpack2(p2, p0, p1);
+              } else {
+                float x0, x1;
+                unpack2(x2, x0, x1);
+                p0 = ex2_approx(x0);
+                p1 = ex2_approx(x1);
+                p2 = pack2(p0, p1);
+              }
+              if (i & 1) lacc1 = add2(lacc1, p2); else lacc0 = add2(lacc0, p2);
+              pk[i] = pack_bf16x2(p0, p1);
+            }
+            {
+              float a0, a1, b0, b1;
+              unpack2(lacc0, a0, a1);
+              unpack2(lacc1, b0, b1);
+              l_tile = (a0 + a1) + (b0 + b1);
+            }
+            // exp2 saturates to +inf, so a score too far above m shows in the row sum (as does a NaN)
+            if (exact || !__any_sync(0xffffffffu, !(l_tile < 1e30f))) break;
+            load_scores();
+            exact = true;
           }
-          tmem_st16(tP + cc * 16, pk);
-        }
-        {
-          float a0, a1, b0, b1;
-          unpack2(lacc0, a0, a1);
-          unpack2(lacc1, b0, b1);
-          l += (a0 + a1) + (b0 + b1);
+          l += l_tile;
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) tmem_st16(tP + cc * 16, pk + cc * 16);
+#undef HK_S
         }
         HK_STAMP2(slot, 4);
         tmem_wait_st();
@@ -418,7 +533,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[slot]);
         HK_STAMP(slot, 5);
-#undef HK_S
       }
       if (!ok) break;
       // ---- epilogue of this slot: O / l -> bf16, L = m*scale + ln(l)

@@ -296,6 +296,27 @@ def test_adversarial_numerics(dev):
     o_ref, l_ref = attn_fwd_oracle(qb, k, v, False)
     assert float((o.float() - o_ref.float()).abs().max()) <= TOL_O
     assert float(((l - l_ref).abs() / l_ref.abs().clamp_min(1)).max()) <= 1e-5
+    # (f) logits that jump by hundreds of powers of two after the first tiles: with D = 128 the kernel takes its
+    # exponentials against the maximum it already has and must notice the overflow and redo the tile exactly; the
+    # jump sits in a full tile, in the partial last tile, and (causal) in a diagonal tile
+    for n, causal, jump_at in ((512, False, 300), (450, False, 400), (640, True, 520)):
+        qf, kf, vf = make_prefill_inputs(2, n, 4, 2, 128, seed=17 + n)
+        kj = kf.clone()
+        kj[:, jump_at:] = (kf[:, jump_at:].float() * 60).to(torch.bfloat16)
+        qj = (qf.float() * 4).to(torch.bfloat16)
+        o, l = run_fwd(qj, kj, vf, causal, dev)
+        o_ref, l_ref = attn_fwd_oracle(qj, kj, vf, causal)
+        assert torch.isfinite(o.float()).all() and torch.isfinite(l).all()
+        assert float((o.float() - o_ref.float()).abs().max()) <= TOL_O
+        assert float(((l - l_ref).abs() / l_ref.abs().clamp_min(1)).max()) <= 1e-5
+    # (g) logits that FALL by hundreds of powers of two after the first tile: later tiles underflow to zero, as they
+    # should (their true weight is below fp32 resolution)
+    kd = kf.clone()
+    kd[:, :128] = (kf[:, :128].float() * 60).to(torch.bfloat16)
+    o, l = run_fwd(qj, kd, vf, False, dev)
+    o_ref, l_ref = attn_fwd_oracle(qj, kd, vf, False)
+    assert float((o.float() - o_ref.float()).abs().max()) <= TOL_O
+    assert float(((l - l_ref).abs() / l_ref.abs().clamp_min(1)).max()) <= 1e-5
 
 
 def test_bitwise_deterministic_and_gqa_equals_mha(dev):
