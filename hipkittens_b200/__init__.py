@@ -33,6 +33,7 @@ from ._native import (  # noqa: F401
     load_tk_kernel_rotary,
     paged_decode,
     paged_decode_workspace_bytes,
+    attn_fwd_paged,
     paged_kv_append,
     paged_kv_append_rotary,
     rotary,
@@ -56,6 +57,7 @@ __all__ = [
     "load_tk_kernel_fwd",
     "load_tk_kernel_rotary",
     "paged_decode",
+    "attn_fwd_paged",
     "paged_kv_append",
     "paged_kv_append_rotary",
     "paged_decode_workspace_bytes",

@@ -25,6 +25,7 @@ EXPORTED_SYMBOLS = (
     "hk_attn_fwd_strided",
     "hk_attn_fwd_varlen",
     "hk_attn_fwd_cross",
+    "hk_attn_fwd_paged",
     "hk_attn_bwd_prep",
     "hk_attn_bwd",
     "hk_attn_bwd_varlen",
@@ -84,6 +85,8 @@ def capi() -> ctypes.CDLL:
     lib.hk_attn_fwd_varlen.restype = ci
     lib.hk_attn_fwd_cross.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ll3, ll3, ll3, vp, ci, cf, ci, vp]
     lib.hk_attn_fwd_cross.restype = ci
+    lib.hk_attn_fwd_paged.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, ci, ci, cf, ci, vp]
+    lib.hk_attn_fwd_paged.restype = ci
     lib.hk_attn_bwd_prep.argtypes = [vp, vp, vp, ci, ci, ci, ci, ci, vp]
     lib.hk_attn_bwd_prep.restype = ci
     lib.hk_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, cf, ci, ci, vp]
@@ -429,6 +432,54 @@ def paged_decode(
                                      s_n, h, hkv, d, page, max_pages, p_n, float(softmax_scale or 0.0),
                                      workspace.data_ptr(), workspace.numel(), q.device.index, st.cuda_stream)
     _check(rc, "hk_attn_paged_decode")
+    return out, lse
+
+
+def attn_fwd_paged(
+    q: torch.Tensor,
+    k_pages: torch.Tensor,
+    v_pages: torch.Tensor,
+    block_table: torch.Tensor,
+    ctx_lens: torch.Tensor,
+    causal: bool = True,
+    softmax_scale: Optional[float] = None,
+    out: Optional[torch.Tensor] = None,
+    lse: Optional[torch.Tensor] = None,
+    stream: Optional[torch.cuda.Stream] = None,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Chunked prefill against the paged KV cache: q [S,T,H,D] bf16 (the last T tokens of each context when `causal`),
+    pages [P,16,H_KV,D] bf16, block_table [S,max_pages] int32, ctx_lens [S] int32 -> O [S,T,H,D] bf16,
+    L [S,H,1,T] fp32. The chunk's keys must already be in the cache (`paged_kv_append` first)."""
+    for name, t in (("q", q), ("k_pages", k_pages), ("v_pages", v_pages)):
+        _require_cuda_bf16(name, t, 4)
+        if t.dtype != torch.bfloat16:
+            raise RuntimeError(f"{name} must be torch.bfloat16")
+    if block_table.dtype != torch.int32 or ctx_lens.dtype != torch.int32:
+        raise RuntimeError("block_table and ctx_lens must be torch.int32")
+    if not (block_table.is_contiguous() and ctx_lens.is_contiguous()):
+        raise RuntimeError("Tensor must be contiguous")
+    s_n, t_n, h, d = q.shape
+    p_n, page, hkv, d2 = k_pages.shape
+    if d2 != d or v_pages.shape != k_pages.shape:
+        raise RuntimeError("q must be [S,T,H,D] and k_pages/v_pages [P,page,H_KV,D]")
+    if block_table.dim() != 2 or block_table.shape[0] != s_n or ctx_lens.shape != (s_n,):
+        raise RuntimeError("block_table must be [S, max_pages] and ctx_lens [S]")
+    if out is None:
+        out = torch.empty_like(q)
+    if lse is None:
+        lse = torch.empty((s_n, h, 1, t_n), dtype=torch.float32, device=q.device)
+    if out.shape != q.shape or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise RuntimeError("out must be a contiguous bf16 tensor of q's shape")
+    if lse.shape != (s_n, h, 1, t_n) or lse.dtype != torch.float32 or not lse.is_contiguous():
+        raise RuntimeError("lse must be a contiguous fp32 tensor [S, H, 1, T]")
+    _require_same_device(q, k_pages=k_pages, v_pages=v_pages, block_table=block_table, ctx_lens=ctx_lens, out=out,
+                         lse=lse)
+    st = stream if stream is not None else torch.cuda.current_stream(q.device)
+    rc = capi().hk_attn_fwd_paged(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+                                  ctx_lens.data_ptr(), out.data_ptr(), lse.data_ptr(), s_n, t_n, h, hkv, d, page,
+                                  block_table.shape[1], p_n, int(bool(causal)), float(softmax_scale or 0.0),
+                                  q.device.index, st.cuda_stream)
+    _check(rc, "hk_attn_fwd_paged")
     return out, lse
 
 

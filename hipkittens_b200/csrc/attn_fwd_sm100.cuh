@@ -56,7 +56,7 @@ constexpr int kEmuMod = HK_EMU_MOD;
 constexpr uint64_t kWaitLimitCycles = 8000ull * 1000 * 1000;  // SM cycles, > 4 s: far beyond any legitimate wait
 
 // Device status codes written to FwdParams::status (0 = OK).
-enum : int { kStatusOk = 0, kStatusTimeout = 1 };
+enum : int { kStatusOk = 0, kStatusTimeout = 1, kStatusFwdBadPage = 2 };  // 2 = the decode kernels' kStatusBadPage
 
 struct FwdParams {
   __nv_bfloat16* o;     // [B,N,H,D]
@@ -72,6 +72,11 @@ struct FwdParams {
   float scale;          // softmax scale
   float scale_log2;     // scale * log2(e)
   const int* kv_lens;   // optional device [B]: batch b attends to keys [0, kv_lens[b]) only; null = NK
+  // Paged K/V (null block_table = contiguous): key j of batch element b is row j % 16 of page
+  // block_table[b * max_pages + j / 16] of a pool [num_pages, 16, H_KV, D]; the K and V tensor maps then describe
+  // the pools as [num_pages * 16 rows, H_KV, D] with a 16-row box, and NK = max_pages * 16.
+  const int* block_table;
+  int max_pages, num_pages;
   int* status;          // device word: first non-zero status wins
 #ifdef HK_TRACE
   long long* trace;     // [3 roles][4096] clock stamps of CTA 0 (debug builds only)
@@ -582,14 +587,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       int ring_st = 0;        // next ring stage to fill
       uint32_t ring_par = 0;  // its phase parity
       bool ok = true;
-      auto push_kv = [&](const CUtensorMap* tm, int b, int kvh, int tile) -> bool {
+      auto push_kv = [&](const CUtensorMap* tm, int b, int kvh, int tile, int kv_len) -> bool {
         const int st = ring_st;
         if (!mbar_wait(&kv_empty[st], ring_par ^ 1, abortp, kWaitLimitCycles)) return false;
         mbar_expect_tx(&kv_full[st], kTile);
         uint8_t* dst = sKV + st * kTile;
+        if (p.block_table == nullptr) {
 #pragma unroll
-        for (int ch = 0; ch < kChunks; ++ch)
-          tma_load_4d(dst + ch * kSub, tm, &kv_full[st], ch * 64, kvh, tile * kBlockN, b);
+          for (int ch = 0; ch < kChunks; ++ch)
+            tma_load_4d(dst + ch * kSub, tm, &kv_full[st], ch * 64, kvh, tile * kBlockN, b);
+        } else {
+          // paged: the tile's 128 keys are 8 pages of 16, each fetched with its own 16-row box. Pages beyond the
+          // context repeat its last page, so that every row of the tile holds cache contents (those keys are masked;
+          // their V rows meet p = 0). An id outside the pool is reported and replaced, never dereferenced.
+          const int total_pages = (kv_len + 15) >> 4;
+          const int* row = p.block_table + static_cast<size_t>(b) * p.max_pages;
+          int ids[kBlockN / 16];
+#pragma unroll
+          for (int pg = 0; pg < kBlockN / 16; ++pg)
+            ids[pg] = __ldg(row + min(tile * (kBlockN / 16) + pg, total_pages - 1));
+#pragma unroll
+          for (int pg = 0; pg < kBlockN / 16; ++pg) {
+            int id = ids[pg];
+            if (id < 0 || id >= p.num_pages) {
+              atomicCAS(p.status, kStatusOk, kStatusFwdBadPage);
+              id = 0;
+            }
+#pragma unroll
+            for (int ch = 0; ch < kChunks; ++ch)
+              tma_load_4d(dst + ch * kSub + pg * (16 * 128), tm, &kv_full[st], ch * 64, kvh, id * 16, 0);
+          }
+        }
         if (++ring_st == kStages) {
           ring_st = 0;
           ring_par ^= 1;
@@ -613,10 +641,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                         w.b);
         }
         const int nmax = max(w.n[0], w.n[1]);
-        if (ok && nmax > 0) ok = push_kv(&tmap_k, w.b, w.kvh, 0);
+        if (ok && nmax > 0) ok = push_kv(&tmap_k, w.b, w.kvh, 0, w.kv_len);
         for (int j = 0; j < nmax && ok; ++j) {
-          ok = push_kv(&tmap_v, w.b, w.kvh, j);
-          if (ok && j + 1 < nmax) ok = push_kv(&tmap_k, w.b, w.kvh, j + 1);
+          ok = push_kv(&tmap_v, w.b, w.kvh, j, w.kv_len);
+          if (ok && j + 1 < nmax) ok = push_kv(&tmap_k, w.b, w.kvh, j + 1, w.kv_len);
         }
       }
     } else if (kSepP && (warp == 9 || warp == 10) && lane == 0) {

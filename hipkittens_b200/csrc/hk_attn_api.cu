@@ -234,7 +234,8 @@ int status_to_code(int word) {
 // 128-byte swizzle (rows of the box are 128 B, the layout tcgen05 descriptors expect).
 // `st` = element strides of the batch, sequence and head dimensions (the D dimension is contiguous); every
 // stride must be a multiple of 8 elements (16 bytes), which TMA requires.
-int make_bnhd_map(CUtensorMap* map, const void* base, int B, int N, int heads, int D, const long long* st) {
+int make_bnhd_map(CUtensorMap* map, const void* base, int B, int N, int heads, int D, const long long* st,
+                  int box_rows = hk::kBlockM) {
   EncodeTiledFn enc = get_encode();
   if (!enc) {
     snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled not available from the driver");
@@ -242,7 +243,7 @@ int make_bnhd_map(CUtensorMap* map, const void* base, int B, int N, int heads, i
   }
   cuuint64_t dims[4] = {cuuint64_t(D), cuuint64_t(heads), cuuint64_t(N), cuuint64_t(B)};
   cuuint64_t strides[3] = {cuuint64_t(st[2]) * 2, cuuint64_t(st[1]) * 2, cuuint64_t(st[0]) * 2};
-  cuuint32_t box[4] = {64, 1, cuuint32_t(hk::kBlockM), 1};
+  cuuint32_t box[4] = {64, 1, cuuint32_t(box_rows), 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -348,21 +349,12 @@ int hk_attn_fwd_varlen(const void* q, const void* k, const void* v, void* o, flo
                            softmax_scale, device, cuda_stream);
 }
 
-int hk_attn_fwd_cross(const void* q, const void* k, const void* v, void* o, float* lse, int B, int N, int NK, int H,
+// Shared tail of the forward entries. Contiguous K/V: k, v are [B, NK, H_KV, D] with strides; paged K/V
+// (block_table != null): k, v are the page pools [num_pages, 16, H_KV, D] and NK = max_pages * 16.
+static int fwd_launch(const void* q, const void* k, const void* v, void* o, float* lse, int B, int N, int NK, int H,
                       int H_KV, int D, const long long* q_strides, const long long* k_strides,
-                      const long long* v_strides, const int32_t* kv_lens, int causal, float softmax_scale,
-                      int device, void* cuda_stream) {
-  if (!q || !k || !v || !o || !lse || !q_strides || !k_strides || !v_strides) return HK_EINVAL;
-  if (B <= 0 || N <= 0 || NK <= 0 || H <= 0 || H_KV <= 0) return HK_EINVAL;
-  if (D != 64 && D != 128) return HK_EUNSUPPORTED;
-  if (H % H_KV != 0) return HK_EINVAL;
-  for (int i = 0; i < 3; ++i) {
-    const long long s3[3] = {q_strides[i], k_strides[i], v_strides[i]};
-    for (long long st_i : s3)
-      if (st_i <= 0 || st_i % 8 != 0 || st_i >= (1ll << 39)) return HK_EINVAL;
-  }
-  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || (reinterpret_cast<uintptr_t>(lse) & 3))
-    return HK_EINVAL;
+                      const long long* v_strides, const int32_t* kv_lens, const int32_t* block_table, int max_pages,
+                      int num_pages, int causal, float softmax_scale, int device, void* cuda_stream) {
   DeviceState* st = nullptr;
   DeviceScope scope;
   int rc = scope.enter(device, &st);
@@ -370,8 +362,15 @@ int hk_attn_fwd_cross(const void* q, const void* k, const void* v, void* o, floa
 
   CUtensorMap tq, tk, tv;
   if ((rc = make_bnhd_map(&tq, q, B, N, H, D, q_strides)) != HK_OK) return rc;
-  if ((rc = make_bnhd_map(&tk, k, B, NK, H_KV, D, k_strides)) != HK_OK) return rc;
-  if ((rc = make_bnhd_map(&tv, v, B, NK, H_KV, D, v_strides)) != HK_OK) return rc;
+  if (block_table) {
+    // the pools as [num_pages * 16 rows, H_KV, D], fetched one page (16 rows) at a time
+    const long long ps[3] = {(long long)num_pages * 16 * H_KV * D, (long long)H_KV * D, D};
+    if ((rc = make_bnhd_map(&tk, k, 1, num_pages * 16, H_KV, D, ps, 16)) != HK_OK) return rc;
+    if ((rc = make_bnhd_map(&tv, v, 1, num_pages * 16, H_KV, D, ps, 16)) != HK_OK) return rc;
+  } else {
+    if ((rc = make_bnhd_map(&tk, k, B, NK, H_KV, D, k_strides)) != HK_OK) return rc;
+    if ((rc = make_bnhd_map(&tv, v, B, NK, H_KV, D, v_strides)) != HK_OK) return rc;
+  }
 
   const int G = H / H_KV;
   const int nqb = (N + hk::kBlockM - 1) / hk::kBlockM;
@@ -399,6 +398,9 @@ int hk_attn_fwd_cross(const void* q, const void* k, const void* v, void* o, floa
   p.scale = softmax_scale > 0.f ? softmax_scale : 1.0f / std::sqrt(float(D));
   p.scale_log2 = p.scale * 1.4426950408889634f;
   p.kv_lens = kv_lens;
+  p.block_table = block_table;
+  p.max_pages = max_pages;
+  p.num_pages = num_pages;
   p.status = st->status;
 #ifdef HK_TRACE
   p.trace = g_trace_buf;
@@ -417,6 +419,43 @@ int hk_attn_fwd_cross(const void* q, const void* k, const void* v, void* o, floa
                               : launch_fwd<128, false>(tq, tk, tv, p, grid, stream);
   return causal ? launch_fwd<64, true>(tq, tk, tv, p, grid, stream)
                 : launch_fwd<64, false>(tq, tk, tv, p, grid, stream);
+}
+
+int hk_attn_fwd_cross(const void* q, const void* k, const void* v, void* o, float* lse, int B, int N, int NK, int H,
+                      int H_KV, int D, const long long* q_strides, const long long* k_strides,
+                      const long long* v_strides, const int32_t* kv_lens, int causal, float softmax_scale,
+                      int device, void* cuda_stream) {
+  if (!q || !k || !v || !o || !lse || !q_strides || !k_strides || !v_strides) return HK_EINVAL;
+  if (B <= 0 || N <= 0 || NK <= 0 || H <= 0 || H_KV <= 0) return HK_EINVAL;
+  if (D != 64 && D != 128) return HK_EUNSUPPORTED;
+  if (H % H_KV != 0) return HK_EINVAL;
+  for (int i = 0; i < 3; ++i) {
+    const long long s3[3] = {q_strides[i], k_strides[i], v_strides[i]};
+    for (long long st_i : s3)
+      if (st_i <= 0 || st_i % 8 != 0 || st_i >= (1ll << 39)) return HK_EINVAL;
+  }
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || (reinterpret_cast<uintptr_t>(lse) & 3))
+    return HK_EINVAL;
+  return fwd_launch(q, k, v, o, lse, B, N, NK, H, H_KV, D, q_strides, k_strides, v_strides, kv_lens, nullptr, 0, 0,
+                    causal, softmax_scale, device, cuda_stream);
+}
+
+int hk_attn_fwd_paged(const void* q, const void* k_pages, const void* v_pages, const int32_t* block_table,
+                      const int32_t* ctx_lens, void* o, float* lse, int S, int T, int H, int H_KV, int D,
+                      int page_size, int max_pages_per_seq, int num_pages, int causal, float softmax_scale,
+                      int device, void* cuda_stream) {
+  if (!q || !k_pages || !v_pages || !block_table || !ctx_lens || !o || !lse) return HK_EINVAL;
+  if (S <= 0 || T <= 0 || H <= 0 || H_KV <= 0 || max_pages_per_seq <= 0 || num_pages <= 0) return HK_EINVAL;
+  if ((D != 64 && D != 128) || page_size != 16) return HK_EUNSUPPORTED;
+  if (H % H_KV != 0) return HK_EINVAL;
+  if (static_cast<long long>(num_pages) * 16 > 0x7fffffffll || static_cast<long long>(max_pages_per_seq) * 16 > 0x3fffffffll)
+    return HK_EINVAL;
+  if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(o) ||
+      (reinterpret_cast<uintptr_t>(lse) & 3))
+    return HK_EINVAL;
+  const long long qs[3] = {(long long)T * H * D, (long long)H * D, D};
+  return fwd_launch(q, k_pages, v_pages, o, lse, S, T, max_pages_per_seq * 16, H, H_KV, D, qs, qs, qs, ctx_lens,
+                    block_table, max_pages_per_seq, num_pages, causal, softmax_scale, device, cuda_stream);
 }
 
 int hk_attn_bwd_prep(const void* o, const void* d_o, float* delta, int B, int N, int H, int D, int device,

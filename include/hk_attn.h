@@ -78,6 +78,22 @@ int hk_attn_fwd_cross(const void* q, const void* k, const void* v, void* o, floa
                       const long long* q_strides, const long long* k_strides, const long long* v_strides,
                       const int32_t* kv_lens, int causal, float softmax_scale, int device, void* cuda_stream);
 
+/* Chunked prefill against the paged KV cache: T query rows per sequence against that sequence's cached context,
+ * K and V read page by page through the block table (the multi-token sibling of hk_attn_paged_decode; the reference
+ * has neither - its cache is contiguous, training/llama/llama/models/mha.py:16-42,164-168).
+ *   q, o : bf16 [S, T, H, D]     lse : fp32 [S, H, 1, T]
+ *   k_pages, v_pages, block_table as in hk_attn_paged_decode; ctx_lens[s] = keys of sequence s, clamped to
+ *   [1, max_pages_per_seq * 16]. The chunk's own keys are expected to be in the cache already (append first).
+ *   causal != 0: query row r of the chunk sees keys up to r + (ctx_lens[s] - T), i.e. the chunk is the last T
+ *   tokens of the context (the alignment of hk_attn_fwd_cross); a row that sees no key gets O = 0, L = -inf.
+ *   D in {64, 128}, page_size = 16. A block-table entry outside [0, num_pages) is not dereferenced and is reported
+ *   as HK_EBADPAGE by hk_last_device_status. Same kernel as hk_attn_fwd: results are bit-identical to
+ *   hk_attn_fwd_cross on the gathered K and V. Cache rows the context does not cover must hold finite values. */
+int hk_attn_fwd_paged(const void* q, const void* k_pages, const void* v_pages, const int32_t* block_table,
+                      const int32_t* ctx_lens, void* o, float* lse, int S, int T, int H, int H_KV, int D,
+                      int page_size, int max_pages_per_seq, int num_pages, int causal, float softmax_scale,
+                      int device, void* cuda_stream);
+
 /* Paged-KV decode: one query token per sequence attends to its whole context. No counterpart exists in
  * the reference (its nearest relative is the contiguous cache update training/llama/llama/models/mha.py:16-42).
  *   q, o        : bf16 [S, 1, H, D]                 lse : fp32 [S, H, 1, 1]
