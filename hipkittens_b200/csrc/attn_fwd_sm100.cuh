@@ -29,6 +29,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 #include "sm100_ptx.cuh"
 
 namespace hk {
@@ -578,75 +580,85 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   } else {
     // ------------------------------------------------------------------ producer warpgroup
     asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
-    if (warp == 8 && lane == 0) {
-      // ---------------- TMA producer
-      prefetch_tmap(&tmap_q);
-      prefetch_tmap(&tmap_k);
-      prefetch_tmap(&tmap_v);
-      uint32_t q_cnt[2] = {0, 0};
-      int ring_st = 0;        // next ring stage to fill
-      uint32_t ring_par = 0;  // its phase parity
-      bool ok = true;
-      auto push_kv = [&](const CUtensorMap* tm, int b, int kvh, int tile, int kv_len) -> bool {
-        const int st = ring_st;
-        if (!mbar_wait(&kv_empty[st], ring_par ^ 1, abortp, kWaitLimitCycles)) return false;
-        mbar_expect_tx(&kv_full[st], kTile);
-        uint8_t* dst = sKV + st * kTile;
-        if (p.block_table == nullptr) {
+    if (warp == 8) {
+      // ---------------- TMA producer. Contiguous K/V: one thread (lane 0) walks the work list. Paged K/V: the whole
+      // warp does, lane 0 doing the waits and lanes 0-7 each fetching one page of a K/V tile (one thread issuing the
+      // 8 or 16 small boxes of a tile, after 8 dependent block-table reads, could not keep the ring full).
+      auto produce = [&](auto paged_tag) {
+        constexpr bool kPaged = decltype(paged_tag)::value;
+        if (lane == 0) {
+          prefetch_tmap(&tmap_q);
+          prefetch_tmap(&tmap_k);
+          prefetch_tmap(&tmap_v);
+        }
+        uint32_t q_cnt[2] = {0, 0};
+        int ring_st = 0;        // next ring stage to fill
+        uint32_t ring_par = 0;  // its phase parity
+        bool ok = true;
+        auto push_kv = [&](const CUtensorMap* tm, int b, int kvh, int tile, int kv_len) -> bool {
+          const int st = ring_st;
+          bool good = true;
+          if (lane == 0) {
+            good = mbar_wait(&kv_empty[st], ring_par ^ 1, abortp, kWaitLimitCycles);
+            if (good) mbar_expect_tx(&kv_full[st], kTile);
+          }
+          if (kPaged) good = __shfl_sync(0xffffffffu, good, 0);
+          if (!good) return false;
+          uint8_t* dst = sKV + st * kTile;
+          if (!kPaged) {
 #pragma unroll
-          for (int ch = 0; ch < kChunks; ++ch)
-            tma_load_4d(dst + ch * kSub, tm, &kv_full[st], ch * 64, kvh, tile * kBlockN, b);
-        } else {
-          // paged: the tile's 128 keys are 8 pages of 16, each fetched with its own 16-row box. Pages beyond the
-          // context repeat its last page, so that every row of the tile holds cache contents (those keys are masked;
-          // their V rows meet p = 0). An id outside the pool is reported and replaced, never dereferenced.
-          const int total_pages = (kv_len + 15) >> 4;
-          const int* row = p.block_table + static_cast<size_t>(b) * p.max_pages;
-          int ids[kBlockN / 16];
-#pragma unroll
-          for (int pg = 0; pg < kBlockN / 16; ++pg)
-            ids[pg] = __ldg(row + min(tile * (kBlockN / 16) + pg, total_pages - 1));
-#pragma unroll
-          for (int pg = 0; pg < kBlockN / 16; ++pg) {
-            int id = ids[pg];
+            for (int ch = 0; ch < kChunks; ++ch)
+              tma_load_4d(dst + ch * kSub, tm, &kv_full[st], ch * 64, kvh, tile * kBlockN, b);
+          } else if (lane < kBlockN / 16) {
+            // the tile's 128 keys are 8 pages of 16, one lane and one 16-row box each. Pages beyond the context
+            // repeat its last page, so that every row of the tile holds cache contents (those keys are masked; their
+            // V rows meet p = 0). An id outside the pool is reported and replaced, never dereferenced.
+            const int total_pages = (kv_len + 15) >> 4;
+            int id = __ldg(p.block_table + static_cast<size_t>(b) * p.max_pages +
+                           min(tile * (kBlockN / 16) + lane, total_pages - 1));
             if (id < 0 || id >= p.num_pages) {
               atomicCAS(p.status, kStatusOk, kStatusFwdBadPage);
               id = 0;
             }
 #pragma unroll
             for (int ch = 0; ch < kChunks; ++ch)
-              tma_load_4d(dst + ch * kSub + pg * (16 * 128), tm, &kv_full[st], ch * 64, kvh, id * 16, 0);
+              tma_load_4d(dst + ch * kSub + lane * (16 * 128), tm, &kv_full[st], ch * 64, kvh, id * 16, 0);
+          }
+          if (++ring_st == kStages) {
+            ring_st = 0;
+            ring_par ^= 1;
+          }
+          return true;
+        };
+        for (int round = 0; ok; ++round) {
+          if (round >= p.total_rounds) break;
+          const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+          if (idx < 0) continue;
+          const WorkItem w = decode_item<CAUSAL>(p, idx);
+          if (lane == 0) {
+            for (int s = 0; s < 2 && ok; ++s) {
+              if (w.n[s] == 0) continue;
+              ok = mbar_wait(&q_empty[s], (q_cnt[s] & 1) ^ 1, abortp, kWaitLimitCycles);
+              if (!ok) break;
+              ++q_cnt[s];
+              mbar_expect_tx(&q_full[s], kTile);
+#pragma unroll
+              for (int ch = 0; ch < kChunks; ++ch)
+                tma_load_4d(sQ + s * kTile + ch * kSub, &tmap_q, &q_full[s], ch * 64, w.head[s], w.qb[s] * kBlockM,
+                            w.b);
+            }
+          }
+          if (kPaged) ok = __shfl_sync(0xffffffffu, ok, 0);
+          const int nmax = max(w.n[0], w.n[1]);
+          if (ok && nmax > 0) ok = push_kv(&tmap_k, w.b, w.kvh, 0, w.kv_len);
+          for (int j = 0; j < nmax && ok; ++j) {
+            ok = push_kv(&tmap_v, w.b, w.kvh, j, w.kv_len);
+            if (ok && j + 1 < nmax) ok = push_kv(&tmap_k, w.b, w.kvh, j + 1, w.kv_len);
           }
         }
-        if (++ring_st == kStages) {
-          ring_st = 0;
-          ring_par ^= 1;
-        }
-        return true;
       };
-      for (int round = 0; ok; ++round) {
-        if (round >= p.total_rounds) break;
-        const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
-        if (idx < 0) continue;
-        const WorkItem w = decode_item<CAUSAL>(p, idx);
-        for (int s = 0; s < 2 && ok; ++s) {
-          if (w.n[s] == 0) continue;
-          ok = mbar_wait(&q_empty[s], (q_cnt[s] & 1) ^ 1, abortp, kWaitLimitCycles);
-          if (!ok) break;
-          ++q_cnt[s];
-          mbar_expect_tx(&q_full[s], kTile);
-#pragma unroll
-          for (int ch = 0; ch < kChunks; ++ch)
-            tma_load_4d(sQ + s * kTile + ch * kSub, &tmap_q, &q_full[s], ch * 64, w.head[s], w.qb[s] * kBlockM,
-                        w.b);
-        }
-        const int nmax = max(w.n[0], w.n[1]);
-        if (ok && nmax > 0) ok = push_kv(&tmap_k, w.b, w.kvh, 0, w.kv_len);
-        for (int j = 0; j < nmax && ok; ++j) {
-          ok = push_kv(&tmap_v, w.b, w.kvh, j, w.kv_len);
-          if (ok && j + 1 < nmax) ok = push_kv(&tmap_k, w.b, w.kvh, j + 1, w.kv_len);
-        }
-      }
+      if (p.block_table != nullptr) produce(std::true_type{});
+      else if (lane == 0) produce(std::false_type{});
     } else if (kSepP && (warp == 9 || warp == 10) && lane == 0) {
       // ---------------- D = 64: two UMMA issuers. P has TMEM columns of its own, so S(j+1) = Q K(j+1)^T and
       // O += P(j) V(j) of a slot do not order each other: warp 9 issues every Q K^T, warp 10 every P V, each with
