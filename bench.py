@@ -66,9 +66,9 @@ DEFAULT_WORKLOAD = "gqa_fwd_b16_n2048_h64_kv8_d128"
 # summarised under profiles/ (None = not captured for that workload).
 NCU_TRAFFIC_BYTES = {
     # 4 x the B=4 capture (260.2 MB per launch; traffic grows with the (batch, kv-head) units)
-    "gqa_fwd_b16_n2048_h64_kv8_d128": 4 * 259.5e6,
+    "gqa_fwd_b16_n2048_h64_kv8_d128": 4 * 260.0e6,
     # 2 x the B=2 / B=8 captures (profiles/attn_fwd_kernel_causal_d128_and_mha_d64.md)
-    "gqa_causal_fwd_b4_n8192_h64_kv8_d128": 2 * (335.9e6 + 229.7e6),
+    "gqa_causal_fwd_b4_n8192_h64_kv8_d128": 2 * (336.1e6 + 230.3e6),
     "mha_fwd_b16_n4096_h16_d64": 2 * (201.4e6 + 48.4e6),
     # backward, 4 x the B=4 capture of the two main kernels (profiles/attn_bwd_kernels_gqa_bwd_d128.md) + the prep kernel
     "gqa_bwd_b16_n2048_h64_kv8_d128": 4 * (358.7e6 + 412.7e6) + 1.082e9,
