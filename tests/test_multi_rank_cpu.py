@@ -73,7 +73,9 @@ def test_two_rank_sharded_forward_matches_unsharded(b, hkv):
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(2, _free_port(), b, 128, 2 * hkv, hkv, 64, True, ret), nprocs=2, join=True)
-    assert ret["o"] == 0.0 and ret["l"] == 0.0
+    # the oracle on a shard and on the whole tensor runs the same arithmetic per unit; torch's CPU contractions may
+    # split their reductions differently for differently strided views, so allow the last bits to differ
+    assert ret["o"] <= 1e-6 and ret["l"] <= 1e-6
 
 
 def _bwd_worker(rank, world, port, b, n, h, hkv, d, causal, ret):
@@ -107,4 +109,28 @@ def test_two_rank_sharded_backward_matches_unsharded(b, hkv):
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_bwd_worker, args=(2, _free_port(), b, 128, 2 * hkv, hkv, 64, True, ret), nprocs=2, join=True)
-    assert ret["err"] == 0.0
+    assert ret["err"] <= 1e-5  # see the forward test: same arithmetic per unit, last bits may differ
+
+
+def test_both_bench_arms_print_the_same_config_object():
+    """bench.py's GPU arm and its reference arm take `config` from one function, so the two JSON lines describe the
+    same workload key for key; what describes the run (per-GPU batch, sharding) lives beside it, not in it."""
+    import importlib.util
+    import inspect
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py")
+    spec = importlib.util.spec_from_file_location("bench_module", path)
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    cfg = bench.workload_config(bench.DEFAULT_WORKLOAD)
+    assert cfg == {"workload": "gqa_fwd_b16_n2048_h64_kv8_d128", "B": 16, "N": 2048, "H": 64, "H_KV": 8, "D": 128,
+                   "causal": False, "cache": "inputs_exceed_l2"}
+    assert '"config": workload_config(args.workload)' in inspect.getsource(bench.main)
+    assert "workload_config(args.workload)" in inspect.getsource(bench.run_reference_arm)
+    for name in bench.OTHER_WORKLOADS:
+        assert bench.workload_config(name)["workload"] == name
+    # the split of config 2 the N-GPU run makes: whole batch elements per rank, equal shares at 2, 4 and 8 ranks
+    for world in (2, 4, 8):
+        shares = [sum(s.kvh_hi - s.kvh_lo for s in partition_units(16, 8, world, r)) for r in range(world)]
+        assert shares == [128 // world] * world
