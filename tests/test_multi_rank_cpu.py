@@ -73,9 +73,10 @@ def test_two_rank_sharded_forward_matches_unsharded(b, hkv):
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(2, _free_port(), b, 128, 2 * hkv, hkv, 64, True, ret), nprocs=2, join=True)
-    # the oracle on a shard and on the whole tensor runs the same arithmetic per unit; torch's CPU contractions may
-    # split their reductions differently for differently strided views, so allow the last bits to differ
-    assert ret["o"] <= 1e-6 and ret["l"] <= 1e-6
+    # the oracle on a shard and on the whole tensor runs the same arithmetic per unit, but torch's CPU contractions may
+    # split their reductions differently from call to call, and a last-bit difference in fp32 can flip the rounding of
+    # an O element to bf16: allow one bf16 ulp of |O| < 2 (a unit placed wrongly would be off by the size of O itself)
+    assert ret["o"] <= 1e-2 and ret["l"] <= 1e-5
 
 
 def _bwd_worker(rank, world, port, b, n, h, hkv, d, causal, ret):
