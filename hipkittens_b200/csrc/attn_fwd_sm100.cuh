@@ -2,7 +2,8 @@
 //
 // Replaces the reference's attend_ker<D> (kernels/attn/gqa/kernel.cpp:102-574 and
 // kernels/attn/gqa_causal/kernel.cpp:181-691): O = softmax(scale * Q K^T) V and
-// L = logsumexp(scale * Q K^T), Q/O [B,N,H,D], K/V [B,N,H_KV,D], L [B,H,1,N].
+// L = logsumexp(scale * Q K^T), Q/O [B,N,H,D], K/V [B,NK,H_KV,D] (or 16-token pages reached through a block
+// table), L [B,H,1,N]; optional per-batch key lengths; causal masks aligned to the last query and the last kept key.
 //
 // Design (one persistent CTA per SM, 384 threads):
 //   warps 0-3   softmax warpgroup of slot 0   (one thread per query row, TMEM lane = row)
@@ -20,7 +21,8 @@
 //
 // Numerics: Q stays unscaled bf16; p = exp2(s*c - m*c) with c = scale*log2(e) in fp32; the running
 // max m is only refreshed when it grew by more than 8 in log2 units (the reference's lazy rescale,
-// kernels/attn/gqa/kernel.cpp:68,268-281); P is rounded to bf16 (RNE) for the PV product while the
+// kernels/attn/gqa/kernel.cpp:68,268-281) - at D = 128 it is not even looked for after an item's first tile, unless a
+// row sum overflows (see the softmax loop); P is rounded to bf16 (RNE) for the PV product while the
 // row sum uses the fp32 values; L = m*scale + ln(l) (kernel.cpp:569-573 in the natural-log domain).
 #pragma once
 
