@@ -12,7 +12,11 @@
 //   warp  9     UMMA issuer: S = Q K^T (both operands in shared memory) and O += P V (P read from
 //               TMEM, V from shared memory, MN-major), accumulators in TMEM
 //   warp  10    D = 64 only: second UMMA issuer (warp 9 then issues the Q K^T products, warp 10 the P V ones)
-//   warps 10-11 otherwise idle (they complete the producer warpgroup for the register re-allocation)
+//   warp  11    store thread: sends each finished O tile from its shared-memory staging buffer to global memory
+//               with TMA (the softmax warps write their rows there, swizzled, instead of storing 32 scattered rows
+//               per instruction from registers)
+//   (warp 10 at D = 128, and all but one lane of warps 9-11, are idle; they complete the producer warpgroup for
+//   the register re-allocation)
 // A work item is a pair of 128-row query tiles ("slots") that share one KV head, so each K/V tile
 // staged in shared memory feeds two S and two O accumulators. While the tensor pipe works on one
 // slot the other slot's softmax runs, which is what hides the exponentials under the MMAs.
@@ -91,8 +95,10 @@ template <int D>
 struct FwdSmem {
   static constexpr int kTileBytes = kBlockM * D * 2;            // one 128 x D bf16 tile
   static constexpr int kSubTileBytes = kBlockM * 128;           // 128 rows x 64 bf16 (128 B swizzled rows)
-  static constexpr int kStages = (D == 128) ? 5 : 8;
-  static constexpr int kDynBytes = (2 + kStages) * kTileBytes + 1024;  // + slack for 1024-B alignment
+  static constexpr int kStages = (D == 128) ? 4 : 8;            // a fifth stage at D = 128 measured no faster
+  // D = 128: one [128 x 128] staging tile (two 64-column halves) from which O leaves through TMA
+  static constexpr int kOutStageBytes = (D == 128) ? kTileBytes : 0;
+  static constexpr int kDynBytes = (2 + kStages) * kTileBytes + kOutStageBytes + 1024;  // + alignment slack
 };
 
 struct WorkItem {
@@ -217,7 +223,8 @@ __device__ __forceinline__ int item_for_round(const Params& p, int round, int ct
 template <int D, bool CAUSAL>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
+                const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
+                const FwdParams p) {
   using namespace ptx;
   using SM = FwdSmem<D>;
   constexpr int kStages = SM::kStages;
@@ -234,10 +241,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;                 // 2 tiles
   uint8_t* sKV = smem + 2 * kTile;    // kStages tiles, K and V alternate through the ring
+  // D = 128: O leaves through TMA from one [128 x 128] staging tile (two 64-column halves) that the two slots use
+  // in turn. D = 64 stores from registers: its softmax warps are short of issue slots, and the staging instructions
+  // cost them more than the scattered 32-byte stores do.
+  uint8_t* sOut = sKV + kStages * kTile;
+  constexpr bool kTmaOut = (D == 128);
 
   __shared__ uint64_t q_full[2], q_empty[2], s_full[2], p_full[2], o_full[2];
   __shared__ uint64_t s_free[2], p_free[2];  // D = 64 only: S has been read / P has been consumed
   __shared__ uint64_t kv_full[kStages], kv_empty[kStages];
+  // O staging (D = 128): so_turn[slot] - the store thread gives the staging tile to the slot (its previous contents
+  // have been read out); so_full[slot] - the slot's four warps have written their rows into it
+  __shared__ uint64_t so_turn[2], so_full[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ uint32_t abort_flag;
 
@@ -255,6 +270,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       mbar_init(&o_full[s], 1);
       mbar_init(&s_free[s], 4);
       mbar_init(&p_free[s], 1);
+      mbar_init(&so_full[s], 4);
+      mbar_init(&so_turn[s], 1);
     }
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&kv_full[s], 1);
@@ -283,6 +300,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const uint32_t tP = kSepP ? tmem + lane_addr + 384 + slot * 64 : tS;  // bf16 P: 64 packed columns
     const float c = p.scale_log2;
     uint32_t s_cnt = 0, o_cnt = 0, pv_cnt = 0;
+    // Staging buffer of this slot and the number of times it has been used before the current item. With one
+    // buffer for both slots its uses are ordered: item by item, and inside an item the slot with fewer K/V tiles
+    // (which finishes first) before the other; both slots and the store warp derive that order from the item.
     bool ok = true;
 #ifdef HK_TRACE
     const bool trace_on = ((warp & 3) == 0) && lane == 0 && p.trace != nullptr;
@@ -553,25 +573,63 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const float inv_l = (CAUSAL && l == 0.f) ? 0.f : 1.0f / l;  // l = 0: a row that sees no key gets O = 0, L = -inf
       const int qrow = w.qb[slot] * kBlockM + row;
       const int head = w.head[slot];
-      __nv_bfloat16* orow = p.o + ((static_cast<size_t>(w.b) * p.N + qrow) * p.H + head) * D;
       const bool row_exists = qrow < p.N;  // rows of a partial last block beyond N are computed but not stored
+      // O leaves through shared memory: a thread's row goes into the staging tile in the 128-byte-swizzled layout
+      // (conflict-free 16-byte stores) and the store warp sends the tile to global memory as TMA boxes, which write
+      // whole 128-byte lines and clip the rows beyond N. (Storing from registers, each thread its own row, touched
+      // 32 separate lines per instruction and cost almost two tile periods per work item.)
+      if constexpr (!kTmaOut) {
+        // straight from registers, 32 bytes per store where the tensor allows it
+        __nv_bfloat16* orow = p.o + ((static_cast<size_t>(w.b) * p.N + qrow) * p.H + head) * D;
+        const bool wide = (reinterpret_cast<uintptr_t>(p.o) & 31) == 0;  // rows are multiples of 128 bytes apart
 #pragma unroll
-      for (int cc = 0; cc < D / 32; ++cc) {
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t o[32];
+          tmem_ld32(tO + cc * 32, o);
+          tmem_wait_ld();
+          uint32_t r[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            r[i] = pack_bf16x2(__uint_as_float(o[2 * i]) * inv_l, __uint_as_float(o[2 * i + 1]) * inv_l);
+          if (row_exists) {
+            if (wide) {
+              st_global_v8(orow + cc * 32, r);
+              st_global_v8(orow + cc * 32 + 16, r + 8);
+            } else {
+              uint4* dst = reinterpret_cast<uint4*>(orow + cc * 32);
+#pragma unroll
+              for (int v4 = 0; v4 < 4; ++v4) dst[v4] = make_uint4(r[v4 * 4], r[v4 * 4 + 1], r[v4 * 4 + 2], r[v4 * 4 + 3]);
+            }
+          }
+        }
+      } else {
         uint32_t o[32];
-        tmem_ld32(tO + cc * 32, o);
-        tmem_wait_ld();
-        uint4* dst = reinterpret_cast<uint4*>(orow + cc * 32);
-        if (row_exists) {
+        tmem_ld32(tO, o);
+        uint8_t* const so_row = sOut + row * 128;
+        // the staging tile is this slot's once the store thread says so (the tile's previous contents are on their
+        // way; the slots take turns in the order in which their tiles finish)
+        ok = mbar_wait(&so_turn[slot], (o_cnt - 1) & 1, abortp, kWaitLimitCycles);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
 #pragma unroll
-        for (int v4 = 0; v4 < 4; ++v4) {
-          uint4 val;
-          val.x = pack_bf16x2(__uint_as_float(o[v4 * 8 + 0]) * inv_l, __uint_as_float(o[v4 * 8 + 1]) * inv_l);
-          val.y = pack_bf16x2(__uint_as_float(o[v4 * 8 + 2]) * inv_l, __uint_as_float(o[v4 * 8 + 3]) * inv_l);
-          val.z = pack_bf16x2(__uint_as_float(o[v4 * 8 + 4]) * inv_l, __uint_as_float(o[v4 * 8 + 5]) * inv_l);
-          val.w = pack_bf16x2(__uint_as_float(o[v4 * 8 + 6]) * inv_l, __uint_as_float(o[v4 * 8 + 7]) * inv_l);
-          dst[v4] = val;
+        for (int cc = 0; cc < D / 32; ++cc) {  // 32 columns = 64 bytes = four 16-byte units of the row's 128-byte half
+          tmem_wait_ld();
+          uint4 val[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            val[u].x = pack_bf16x2(__uint_as_float(o[u * 8 + 0]) * inv_l, __uint_as_float(o[u * 8 + 1]) * inv_l);
+            val[u].y = pack_bf16x2(__uint_as_float(o[u * 8 + 2]) * inv_l, __uint_as_float(o[u * 8 + 3]) * inv_l);
+            val[u].z = pack_bf16x2(__uint_as_float(o[u * 8 + 4]) * inv_l, __uint_as_float(o[u * 8 + 5]) * inv_l);
+            val[u].w = pack_bf16x2(__uint_as_float(o[u * 8 + 6]) * inv_l, __uint_as_float(o[u * 8 + 7]) * inv_l);
+          }
+          if (cc + 1 < D / 32) tmem_ld32(tO + (cc + 1) * 32, o);
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            *reinterpret_cast<uint4*>(so_row + (cc >> 1) * kSub + ((((cc & 1) * 4 + u) ^ (row & 7)) << 4)) = val[u];
         }
-        }
+        fence_proxy_async();  // this thread's stores, visible to the TMA engine
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&so_full[slot]);
       }
       if (row_exists)
         p.lse[(static_cast<size_t>(w.b) * p.H + head) * p.N + qrow] =
@@ -888,6 +946,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
         flush_releases();
       }
+    } else if (kTmaOut && warp == 11 && lane == 0) {
+      // ---------------- store thread: gives the staging tile to one slot at a time and sends what the slot wrote
+      // there to global memory. Order of the turns: item by item and, inside an item, the slot with fewer K/V tiles
+      // (which finishes first) before the other.
+      prefetch_tmap(&tmap_o);
+      uint32_t full_cnt0 = 0, full_cnt1 = 0;  // tiles sent so far, per slot
+      bool ok = true;
+      for (int round = 0; ok; ++round) {
+        if (round >= p.total_rounds) break;
+        const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+        if (idx < 0) continue;
+        const WorkItem w = decode_item<CAUSAL>(p, idx);
+        const int first = (w.n[1] < w.n[0]) ? 1 : 0;
+        for (int t = 0; t < 2 && ok; ++t) {
+          const int s = t == 0 ? first : 1 - first;
+          // selects, not indexing with s: the item stays in registers
+          const int n_s = s ? w.n[1] : w.n[0], head_s = s ? w.head[1] : w.head[0], qb_s = s ? w.qb[1] : w.qb[0];
+          if (n_s == 0) continue;
+          mbar_arrive(&so_turn[s]);
+          ok = mbar_wait_parked(&so_full[s], (s ? full_cnt1 : full_cnt0) & 1, abortp, kWaitLimitCycles);
+          if (!ok) break;
+          full_cnt0 += s ? 0u : 1u;
+          full_cnt1 += s ? 1u : 0u;
+#pragma unroll
+          for (int ch = 0; ch < kChunks; ++ch)
+            tma_store_4d(&tmap_o, sOut + ch * kSub, ch * 64, head_s, qb_s * kBlockM, w.b);
+          bulk_commit_group();
+          bulk_wait_group_read0();  // the tile may be overwritten
+        }
+      }
+      bulk_wait_group0();  // the last boxes have reached global memory
     }
   }
 

@@ -270,9 +270,9 @@ __global__ void bounded_wait_selftest_kernel(int* status, unsigned long long lim
 }
 
 template <int D, bool CAUSAL>
-int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const hk::FwdParams& p,
-               int grid, cudaStream_t stream) {
-  hk::attn_fwd_kernel<D, CAUSAL><<<grid, hk::kFwdThreads, hk::FwdSmem<D>::kDynBytes, stream>>>(tq, tk, tv, p);
+int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
+               const hk::FwdParams& p, int grid, cudaStream_t stream) {
+  hk::attn_fwd_kernel<D, CAUSAL><<<grid, hk::kFwdThreads, hk::FwdSmem<D>::kDynBytes, stream>>>(tq, tk, tv, to, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   HK_CUDA(cudaGetLastError());
   return HK_OK;
@@ -360,8 +360,13 @@ static int fwd_launch(const void* q, const void* k, const void* v, void* o, floa
   int rc = scope.enter(device, &st);
   if (rc != HK_OK) return rc;
 
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, to;
   if ((rc = make_bnhd_map(&tq, q, B, N, H, D, q_strides)) != HK_OK) return rc;
+  {
+    // O is written by TMA from a swizzled staging tile, a [128 rows x 64 columns] box at a time
+    const long long os[3] = {(long long)N * H * D, (long long)H * D, D};
+    if ((rc = make_bnhd_map(&to, o, B, N, H, D, os)) != HK_OK) return rc;
+  }
   if (block_table) {
     // the pools as [num_pages * 16 rows, H_KV, D], fetched one page (16 rows) at a time
     const long long ps[3] = {(long long)num_pages * 16 * H_KV * D, (long long)H_KV * D, D};
@@ -415,10 +420,10 @@ static int fwd_launch(const void* q, const void* k, const void* v, void* o, floa
     p.total_rounds = p.rounds_per_group * n_groups;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  if (D == 128) return causal ? launch_fwd<128, true>(tq, tk, tv, p, grid, stream)
-                              : launch_fwd<128, false>(tq, tk, tv, p, grid, stream);
-  return causal ? launch_fwd<64, true>(tq, tk, tv, p, grid, stream)
-                : launch_fwd<64, false>(tq, tk, tv, p, grid, stream);
+  if (D == 128) return causal ? launch_fwd<128, true>(tq, tk, tv, to, p, grid, stream)
+                              : launch_fwd<128, false>(tq, tk, tv, to, p, grid, stream);
+  return causal ? launch_fwd<64, true>(tq, tk, tv, to, p, grid, stream)
+                : launch_fwd<64, false>(tq, tk, tv, to, p, grid, stream);
 }
 
 int hk_attn_fwd_cross(const void* q, const void* k, const void* v, void* o, float* lse, int B, int N, int NK, int H,

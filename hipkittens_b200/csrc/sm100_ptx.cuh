@@ -88,6 +88,39 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// One 32-byte store to global memory; `dst` must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* dst, const uint32_t* r) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(dst), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
+// Bounded wait for a role that waits long and is not in a hurry: try_wait is given a suspend-time hint, so the
+// thread is parked by the hardware instead of polling (a polling thread takes issue slots from the warps that share
+// its scheduler). Same return values and abort protocol as mbar_wait.
+__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                 uint64_t limit_cycles) {
+  const long long t0 = clock64();
+  while (true) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(100000u)  // suspend-time hint, nanoseconds
+        : "memory");
+    if (done) return true;
+    if (*abort_flag != 0) return false;
+    if (static_cast<uint64_t>(clock64() - t0) > limit_cycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
@@ -103,6 +136,21 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tmap, ui
         "r"(c2), "r"(c3)
       : "memory");
 }
+
+// 4-D tiled store shared -> global, tracked by the issuing thread's bulk async-group. Rows or columns of the box that
+// lie outside the tensor are not written. The shared-memory source must have been made visible to the async proxy
+// (fence_proxy_async after the ordinary stores that filled it) and must not be rewritten before
+// bulk_wait_group_read0() has returned in the issuing thread.
+__device__ __forceinline__ void tma_store_4d(const void* tmap, const void* smem_src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all of this thread's bulk groups have finished READING their shared-memory sources
+__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all of this thread's bulk groups are complete (their global writes are done)
+__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // Untiled bulk copy global -> shared, completion signalled on an mbarrier as transaction bytes.
 // Both addresses must be 16-byte aligned and `bytes` a multiple of 16.
