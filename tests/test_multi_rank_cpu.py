@@ -75,8 +75,9 @@ def test_two_rank_sharded_forward_matches_unsharded(b, hkv):
     mp.spawn(_worker, args=(2, _free_port(), b, 128, 2 * hkv, hkv, 64, True, ret), nprocs=2, join=True)
     # the oracle on a shard and on the whole tensor runs the same arithmetic per unit, but torch's CPU contractions may
     # split their reductions differently from call to call, and a last-bit difference in fp32 can flip the rounding of
-    # an O element to bf16: allow one bf16 ulp of |O| < 2 (a unit placed wrongly would be off by the size of O itself)
-    assert ret["o"] <= 1e-2 and ret["l"] <= 1e-5
+    # an O element to bf16: allow one bf16 ulp of |O| < 2, and 1e-4 on L, ten times the largest difference seen (a
+    # unit placed wrongly would be off by the size of O and L themselves)
+    assert ret["o"] <= 1e-2 and ret["l"] <= 1e-4
 
 
 def _bwd_worker(rank, world, port, b, n, h, hkv, d, causal, ret):
@@ -110,7 +111,7 @@ def test_two_rank_sharded_backward_matches_unsharded(b, hkv):
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_bwd_worker, args=(2, _free_port(), b, 128, 2 * hkv, hkv, 64, True, ret), nprocs=2, join=True)
-    assert ret["err"] <= 1e-5  # see the forward test: same arithmetic per unit, last bits may differ
+    assert ret["err"] <= 1e-4  # see the forward test: same arithmetic per unit, last bits may differ
 
 
 def test_both_bench_arms_print_the_same_config_object():
