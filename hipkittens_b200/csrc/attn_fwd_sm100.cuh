@@ -12,9 +12,9 @@
 //   warp  9     UMMA issuer: S = Q K^T (both operands in shared memory) and O += P V (P read from
 //               TMEM, V from shared memory, MN-major), accumulators in TMEM
 //   warp  10    D = 64 only: second UMMA issuer (warp 9 then issues the Q K^T products, warp 10 the P V ones)
-//   warp  11    store thread: sends each finished O tile from its shared-memory staging buffer to global memory
-//               with TMA (the softmax warps write their rows there, swizzled, instead of storing 32 scattered rows
-//               per instruction from registers)
+//   warp  11    D = 128: store thread, sends each finished O tile from its shared-memory staging buffer to global
+//               memory with TMA (the softmax warps write their rows there, swizzled, instead of storing 32 scattered
+//               rows per instruction from registers). D = 64 non-causal: Q loader (O is stored from registers there)
 //   (warp 10 at D = 128, and all but one lane of warps 9-11, are idle; they complete the producer warpgroup for
 //   the register re-allocation)
 // A work item is a pair of 128-row query tiles ("slots") that share one KV head, so each K/V tile
@@ -246,6 +246,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   // cost them more than the scattered 32-byte stores do.
   uint8_t* sOut = sKV + kStages * kTile;
   constexpr bool kTmaOut = (D == 128);
+  // D = 64, non-causal: the Q tiles are loaded by a thread of their own (warp 11, which has no stores to send
+  // there). Measured +1.7 % there, but -7 % at D = 64 causal and -2 % at D = 128 with short items, where the
+  // producer thread goes on loading Q itself.
+  constexpr bool kQThread = (D == 64) && !CAUSAL;
 
   __shared__ uint64_t q_full[2], q_empty[2], s_full[2], p_full[2], o_full[2];
   __shared__ uint64_t s_free[2], p_free[2];  // D = 64 only: S has been read / P has been consumed
@@ -647,7 +651,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       auto produce = [&](auto paged_tag) {
         constexpr bool kPaged = decltype(paged_tag)::value;
         if (lane == 0) {
-          prefetch_tmap(&tmap_q);
+          if (!kQThread) prefetch_tmap(&tmap_q);
           prefetch_tmap(&tmap_k);
           prefetch_tmap(&tmap_v);
         }
@@ -695,7 +699,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
           if (idx < 0) continue;
           const WorkItem w = decode_item<CAUSAL>(p, idx);
-          if (lane == 0) {
+          if (!kQThread && lane == 0) {
             for (int s = 0; s < 2 && ok; ++s) {
               if (w.n[s] == 0) continue;
               ok = mbar_wait(&q_empty[s], (q_cnt[s] & 1) ^ 1, abortp, kWaitLimitCycles);
@@ -800,7 +804,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       uint32_t q_par[2] = {0, 0}, p_par[2] = {0, 0};  // phase parities of q_full / p_full per slot
       int ring_st = 0;                                // next ring stage to consume
       uint32_t ring_par = 0;                          // its phase parity
-      int pending_v = -1, pending_k = -1;  // ring stages whose release is deferred (see the main loop)
       bool ok = true;
 #ifdef HK_TRACE
       const bool trace_on = p.trace != nullptr;
@@ -830,21 +833,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           ring_par ^= 1;
         }
       };
-      auto flush_releases = [&]() {
-        if (pending_v >= 0) {
-          umma_commit(&kv_empty[pending_v]);
-          pending_v = -1;
-        }
-        if (pending_k >= 0) {
-          umma_commit(&kv_empty[pending_k]);
-          pending_k = -1;
-        }
-      };
       // The pipe runs only a couple of MMAs behind this thread, so whatever the thread does between the
       // last MMA of one slot and the first MMA of the other is a bubble in the tensor pipe. Between slots
       // there is therefore only the S-ready commit and the wait for the other slot's P; ring bookkeeping,
-      // the waits for the next K/V tiles and the ring releases all sit in the middle of a slot's chunk
-      // (after its PV, before its QK), where the pipe still has the PV MMAs queued.
+      // the waits for the next K/V tiles and the ring releases all sit at the end of a trip, after slot 1's
+      // Q K^T, where this thread has nothing to issue until slot 0's next P arrives.
       for (int round = 0; ok; ++round) {
         if (round >= p.total_rounds) break;
         const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
@@ -896,7 +889,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               HK_STAMP(2, 12);
               tc_fence_after();
               issue_pv(0, st_v, j > 0);
-              flush_releases();  // V(j-1) and K(j): every MMA that read them is issued by now
               if (j + 1 < n0) {
                 issue_qk(0, st_k);
                 umma_commit(&s_full[0]);
@@ -915,18 +907,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
               tc_fence_after();
               issue_pv(1, st_v, j > 0);
             }
-            // next trip's tiles V(j+1), K(j+2): requested long ago, these waits normally pass at once
-            if (j + 1 < nmax) {
-              nst_v = ring_st;
-              ok = mbar_wait(&kv_full[nst_v], ring_par, abortp, kWaitLimitCycles);
-              ring_next();
-              if (ok && j + 2 < nmax) {
-                nst_k = ring_st;
-                ok = mbar_wait(&kv_full[nst_k], ring_par, abortp, kWaitLimitCycles);
-                ring_next();
-              }
-              if (!ok) break;
-            }
             if (j < n1) {
               if (j + 1 < n1) {
                 issue_qk(1, st_k);
@@ -937,14 +917,58 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 umma_commit(&o_full[1]);
               }
             }
-            // V(j) and K(j+1) were last read by the MMAs above; their releases ride behind the next PV
-            pending_v = st_v;
-            if (j + 1 < nmax) pending_k = st_k;
+            // V(j) and K(j+1) were last read by the MMAs above. Their stages are released here, and the next trip's
+            // tiles V(j+1), K(j+2) awaited here, at the end of the trip, where this thread would only be waiting for
+            // the next P of slot 0 anyway. (In the middle of the trip a wait for a tile that is a little late held
+            // up slot 1's Q K^T by some 300 clocks per tile; releases deferred to the next trip shortened the
+            // producer's lead by a third of a period.)
+            umma_commit(&kv_empty[st_v]);
+            if (j + 1 < nmax) {
+              umma_commit(&kv_empty[st_k]);
+              nst_v = ring_st;
+              ok = mbar_wait(&kv_full[nst_v], ring_par, abortp, kWaitLimitCycles);
+              ring_next();
+              if (ok && j + 2 < nmax) {
+                nst_k = ring_st;
+                ok = mbar_wait(&kv_full[nst_k], ring_par, abortp, kWaitLimitCycles);
+                ring_next();
+              }
+              if (!ok) break;
+            }
             st_v = nst_v;
             st_k = nst_k;
           }
         }
-        flush_releases();
+      }
+    } else if (kQThread && warp == 11 && lane == 0) {
+      // ---------------- Q loader (D = 64, non-causal): a thread of its own, so that the K/V producer never waits behind a Q
+      // tile that cannot be replaced yet and requests the next item's first K/V tiles as early as the ring allows
+      prefetch_tmap(&tmap_q);
+      uint32_t q_cnt0 = 0, q_cnt1 = 0;
+      bool ok = true;
+      for (int round = 0; ok; ++round) {
+        if (round >= p.total_rounds) break;
+        const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+        if (idx < 0) continue;
+        const WorkItem w = decode_item<CAUSAL>(p, idx);
+        if (w.n[0] > 0) {
+          ok = mbar_wait(&q_empty[0], (q_cnt0 & 1) ^ 1, abortp, kWaitLimitCycles);
+          if (!ok) break;
+          ++q_cnt0;
+          mbar_expect_tx(&q_full[0], kTile);
+#pragma unroll
+          for (int ch = 0; ch < kChunks; ++ch)
+            tma_load_4d(sQ + ch * kSub, &tmap_q, &q_full[0], ch * 64, w.head[0], w.qb[0] * kBlockM, w.b);
+        }
+        if (w.n[1] > 0) {
+          ok = mbar_wait(&q_empty[1], (q_cnt1 & 1) ^ 1, abortp, kWaitLimitCycles);
+          if (!ok) break;
+          ++q_cnt1;
+          mbar_expect_tx(&q_full[1], kTile);
+#pragma unroll
+          for (int ch = 0; ch < kChunks; ++ch)
+            tma_load_4d(sQ + kTile + ch * kSub, &tmap_q, &q_full[1], ch * 64, w.head[1], w.qb[1] * kBlockM, w.b);
+        }
       }
     } else if (kTmaOut && warp == 11 && lane == 0) {
       // ---------------- store thread: gives the staging tile to one slot at a time and sends what the slot wrote
