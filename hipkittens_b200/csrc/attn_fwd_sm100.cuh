@@ -66,6 +66,32 @@ constexpr uint64_t kWaitLimitCycles = 8000ull * 1000 * 1000;  // SM cycles, > 4 
 // Device status codes written to FwdParams::status (0 = OK).
 enum : int { kStatusOk = 0, kStatusTimeout = 1, kStatusFwdBadPage = 2 };  // 2 = the decode kernels' kStatusBadPage
 
+// Division of a non-negative int below 2^31 by a divisor fixed at launch: a multiply-high and a shift instead of the
+// ~40 dependent instructions of a 32-bit division. The work-item decode below divides ten times per item, on the
+// critical path of the MMA issuer and of the softmax warps between two items (1 600 clocks per item before).
+// mul = ceil(2^(31+L) / d) with L = ceil(log2 d); n / d = umulhi(n, mul) >> (L - 1) for 0 <= n < 2^31 (d = 1: n).
+struct FastDiv {
+  uint32_t d = 1, mul = 0, shift = 0;
+  FastDiv() = default;
+  explicit FastDiv(int divisor) : d(static_cast<uint32_t>(divisor)) {
+    if (d > 1) {
+      uint32_t L = 0;
+      while ((1ull << L) < d) ++L;
+      mul = static_cast<uint32_t>(((1ull << (31 + L)) + d - 1) / d);
+      shift = L - 1;
+    }
+  }
+#ifdef __CUDACC__
+  __device__ __forceinline__ int div(int n) const {
+    return d == 1 ? n : static_cast<int>(__umulhi(static_cast<uint32_t>(n), mul) >> shift);
+  }
+  __device__ __forceinline__ void divmod(int n, int& q, int& r) const {
+    q = div(n);
+    r = n - q * static_cast<int>(d);
+  }
+#endif
+};
+
 struct FwdParams {
   __nv_bfloat16* o;     // [B,N,H,D]
   float* lse;           // [B,H,1,N]
@@ -77,6 +103,12 @@ struct FwdParams {
   int group_items;      // work items of a full group (all items when there is one group)
   int rounds_per_group; // ceil(group_items / CTAs): a group is dealt in rounds of its own
   int total_rounds;     // rounds_per_group * number of groups
+  // Item decode, prepared by set_item_decode(): an item index splits into (unit, q tile or q tile pair, head or head
+  // pair inside the group) by these divisors
+  int G, nqb, units;    // H / H_KV, query tiles per sequence, B * H_KV
+  int inner;            // slot pairs per q position inside a unit: G / 2 (two heads per item) or G (two q tiles)
+  int last_group;       // index of the last causal sweep group (it may hold fewer units)
+  FastDiv fd_rounds, fd_group_items, fd_per_unit, fd_inner, fd_per_q, fd_per_q_last, fd_hkv;
   float scale;          // softmax scale
   float scale_log2;     // scale * log2(e)
   const int* kv_lens;   // optional device [B]: batch b attends to keys [0, kv_lens[b]) only; null = NK
@@ -119,57 +151,38 @@ struct WorkItem {
 template <bool CAUSAL>
 __device__ __forceinline__ WorkItem decode_item(const FwdParams& p, int idx) {
   WorkItem w;
-  const int G = p.H / p.H_KV;
-  const int NQB = (p.N + kBlockM - 1) / kBlockM;  // the last block may be partial
-  const int units = p.B * p.H_KV;
-  int unit, qb0, qb1, h0, h1;
+  const int G = p.G;
+  const int NQB = p.nqb;  // the last block may be partial
+  // an item is (unit, q position, pair inside the group); a q position is a q tile (two heads per item) or a pair
+  // of q tiles (one head per item), of which there are nq per unit
+  const int nq = p.pair_heads ? NQB : (NQB + 1) / 2;
+  int unit, qx, hx;
+  if (CAUSAL) {
+    const int grp = min(p.fd_group_items.div(idx), p.last_group);
+    const int within = idx - grp * p.group_items;
+    int qd, rem;
+    if (grp == p.last_group) p.fd_per_q_last.divmod(within, qd, rem);
+    else p.fd_per_q.divmod(within, qd, rem);
+    qx = nq - 1 - qd;
+    int u;
+    p.fd_inner.divmod(rem, u, hx);
+    unit = grp * p.group_units + u;
+  } else {
+    int rem;
+    p.fd_per_unit.divmod(idx, unit, rem);
+    p.fd_inner.divmod(rem, qx, hx);
+  }
+  int qb0, qb1, h0, h1;
   if (p.pair_heads) {
-    const int hp_n = G / 2;
-    int qb, hp;
-    if (CAUSAL) {
-      const int U = p.group_units;
-      const int grp = min(idx / (U * hp_n * NQB), (units - 1) / U);
-      const int within = idx - grp * (U * hp_n * NQB);
-      const int per_qb = min(U, units - grp * U) * hp_n;
-      qb = NQB - 1 - within / per_qb;
-      const int rem = within % per_qb;
-      unit = grp * U + rem / hp_n;
-      hp = rem % hp_n;
-    } else {
-      const int per_unit = hp_n * NQB;
-      unit = idx / per_unit;
-      const int rem = idx % per_unit;
-      qb = rem / hp_n;
-      hp = rem % hp_n;
-    }
-    qb0 = qb1 = qb;
-    h0 = 2 * hp;
+    qb0 = qb1 = qx;
+    h0 = 2 * hx;
     h1 = h0 + 1;
   } else {
-    const int NQP = (NQB + 1) / 2;
-    int qp, hg;
-    if (CAUSAL) {
-      const int U = p.group_units;
-      const int grp = min(idx / (U * G * NQP), (units - 1) / U);
-      const int within = idx - grp * (U * G * NQP);
-      const int per_qp = min(U, units - grp * U) * G;
-      qp = NQP - 1 - within / per_qp;
-      const int rem = within % per_qp;
-      unit = grp * U + rem / G;
-      hg = rem % G;
-    } else {
-      const int per_unit = G * NQP;
-      unit = idx / per_unit;
-      const int rem = idx % per_unit;
-      qp = rem / G;
-      hg = rem % G;
-    }
-    qb0 = 2 * qp;
-    qb1 = 2 * qp + 1;
-    h0 = h1 = hg;
+    qb0 = 2 * qx;
+    qb1 = 2 * qx + 1;
+    h0 = h1 = hx;
   }
-  w.b = unit / p.H_KV;
-  w.kvh = unit % p.H_KV;
+  p.fd_hkv.divmod(unit, w.b, w.kvh);
   w.head[0] = w.kvh * G + h0;
   w.head[1] = w.kvh * G + h1;
   w.qb[0] = qb0;
@@ -199,6 +212,33 @@ __device__ __forceinline__ int item_for_round(const Params& p, int round, int ct
   const int first = grp * p.group_items;
   const int in_grp = r * n_cta + (((r + grp) & 1) ? (n_cta - 1 - cta) : cta);
   return (in_grp < min(p.group_items, p.n_items - first)) ? first + in_grp : -1;
+}
+
+// The same for the forward, whose parameters carry the divisor of the rounds in multiply-and-shift form.
+__device__ __forceinline__ int item_for_round(const FwdParams& p, int round, int cta, int n_cta) {
+  const int grp = p.fd_rounds.div(round);
+  const int r = round - grp * p.rounds_per_group;
+  const int first = grp * p.group_items;
+  const int in_grp = r * n_cta + (((r + grp) & 1) ? (n_cta - 1 - cta) : cta);
+  return (in_grp < min(p.group_items, p.n_items - first)) ? first + in_grp : -1;
+}
+
+// Host side: fills the fields the item decode reads. Call after B, N, H, H_KV, pair_heads, group_units, group_items
+// and rounds_per_group are set.
+inline void set_item_decode(FwdParams& p) {
+  p.G = p.H / p.H_KV;
+  p.nqb = (p.N + kBlockM - 1) / kBlockM;
+  p.units = p.B * p.H_KV;
+  p.inner = p.pair_heads ? p.G / 2 : p.G;
+  const int nq = p.pair_heads ? p.nqb : (p.nqb + 1) / 2;
+  p.last_group = (p.units - 1) / p.group_units;
+  p.fd_rounds = FastDiv(p.rounds_per_group);
+  p.fd_group_items = FastDiv(p.group_units * p.inner * nq);
+  p.fd_per_unit = FastDiv(p.inner * nq);
+  p.fd_inner = FastDiv(p.inner);
+  p.fd_per_q = FastDiv(p.group_units * p.inner);
+  p.fd_per_q_last = FastDiv((p.units - p.last_group * p.group_units) * p.inner);
+  p.fd_hkv = FastDiv(p.H_KV);
 }
 
 #ifdef HK_TRACE
@@ -699,7 +739,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
           if (idx < 0) continue;
           const WorkItem w = decode_item<CAUSAL>(p, idx);
-          if (!kQThread && lane == 0) {
+          const int nmax = max(w.n[0], w.n[1]);
+          // the first K tile is requested before the Q tiles: the stage it goes to is free two K/V tiles before the
+          // previous item ends, the Q tiles only when that item's last Q K^T has been issued
+          if (nmax > 0) ok = push_kv(&tmap_k, w.b, w.kvh, 0, w.kv_len);
+          if (!kQThread && lane == 0 && ok) {
             for (int s = 0; s < 2 && ok; ++s) {
               if (w.n[s] == 0) continue;
               ok = mbar_wait(&q_empty[s], (q_cnt[s] & 1) ^ 1, abortp, kWaitLimitCycles);
@@ -713,8 +757,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
           }
           if (kPaged) ok = __shfl_sync(0xffffffffu, ok, 0);
-          const int nmax = max(w.n[0], w.n[1]);
-          if (ok && nmax > 0) ok = push_kv(&tmap_k, w.b, w.kvh, 0, w.kv_len);
           for (int j = 0; j < nmax && ok; ++j) {
             ok = push_kv(&tmap_v, w.b, w.kvh, j, w.kv_len);
             if (ok && j + 1 < nmax) ok = push_kv(&tmap_k, w.b, w.kvh, j + 1, w.kv_len);
@@ -838,18 +880,51 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // there is therefore only the S-ready commit and the wait for the other slot's P; ring bookkeeping,
       // the waits for the next K/V tiles and the ring releases all sit at the end of a trip, after slot 1's
       // Q K^T, where this thread has nothing to issue until slot 0's next P arrives.
-      for (int round = 0; ok; ++round) {
-        if (round >= p.total_rounds) break;
-        const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
-        if (idx < 0) continue;
-        const WorkItem w = decode_item<CAUSAL>(p, idx);
+      // The first valid round at or after `from` (rounds in which this CTA has no item are skipped), or total_rounds.
+      auto next_round = [&](int from, int& idx) {
+        for (int r = from; r < p.total_rounds; ++r) {
+          idx = item_for_round(p, r, blockIdx.x, gridDim.x);
+          if (idx >= 0) return r;
+        }
+        idx = -1;
+        return p.total_rounds;
+      };
+      // At the end of an item this thread would wait for slot 1's last P before it could turn to the next item, and
+      // slot 0's softmax warps, done with their epilogue, would wait some 2 500 clocks for their first S. So when
+      // slot 0's last P V has been issued, the next item's first Q K^T of that slot follows it at once - if the next
+      // Q tile and the next item's first K tile have already arrived (tested, never waited for: this thread must
+      // not stall in front of the other slot's products). S of the slot is free by then: its softmax warps have
+      // published the last P, which the P V just issued reads and the new product, behind it in the pipe, overwrites.
+      // Slot 0 only: doing the same for slot 1 brings the two slots' first tiles too close together, their softmaxes
+      // run at the same time, and every shape measured 1-2 % slower.
+      bool pre_issued0 = false;
+      auto try_early_qk0 = [&](int n_next) {
+        if (n_next == 0 || !mbar_test_wait(&kv_full[ring_st], ring_par) || !mbar_test_wait(&q_full[0], q_par[0]))
+          return;
+        q_par[0] ^= 1;
+        tc_fence_after();
+        issue_qk(0, ring_st);
+        umma_commit(&s_full[0]);
+        if (n_next == 1) umma_commit(&q_empty[0]);
+        pre_issued0 = true;
+      };
+      int idx = -1, nidx = -1;
+      int round = next_round(0, idx), nround = 0;
+      WorkItem w, wn;
+      if (idx >= 0) w = decode_item<CAUSAL>(p, idx);
+      for (; ok && round < p.total_rounds; round = nround, w = wn) {
+        // the item after this one, for the early issue of its first products
+        nround = next_round(round + 1, nidx);
+        wn.n[0] = wn.n[1] = 0;
+        if (nidx >= 0) wn = decode_item<CAUSAL>(p, nidx);
         const int n0 = w.n[0], n1 = w.n[1];
         const int nmax = max(n0, n1);
         if (nmax == 0) continue;  // causal with more queries than keys: neither block sees a key
-        // ---- first K tile: S = Q K0^T for both slots
+        // ---- first K tile: S = Q K0^T for both slots (a slot whose product was issued at the end of the previous
+        // item is skipped; the tile's arrival has been seen then, and this wait returns at once)
         ok = mbar_wait(&kv_full[ring_st], ring_par, abortp, kWaitLimitCycles);
         if (!ok) break;
-        if (n0 > 0) {
+        if (n0 > 0 && !pre_issued0) {
           ok = mbar_wait(&q_full[0], q_par[0], abortp, kWaitLimitCycles);
           if (!ok) break;
           q_par[0] ^= 1;
@@ -867,6 +942,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           umma_commit(&s_full[1]);
           if (n1 == 1) umma_commit(&q_empty[1]);
         }
+        pre_issued0 = false;
         umma_commit(&kv_empty[ring_st]);
         ring_next();
         {
@@ -898,6 +974,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 umma_commit(&o_full[0]);
               }
             }
+            // ring_st is the next item's first K tile once no tile of this item is left to be waited for
+            if (j + 1 == nmax) try_early_qk0(wn.n[0]);
             // ---- slot 1
             if (j < n1) {
               ok = mbar_wait(&p_full[1], p_par[1], abortp, kWaitLimitCycles);

@@ -419,6 +419,7 @@ static int fwd_launch(const void* q, const void* k, const void* v, void* o, floa
     p.rounds_per_group = (p.group_items + grid - 1) / grid;
     p.total_rounds = p.rounds_per_group * n_groups;
   }
+  hk::set_item_decode(p);
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (D == 128) return causal ? launch_fwd<128, true>(tq, tk, tv, to, p, grid, stream)
                               : launch_fwd<128, false>(tq, tk, tv, to, p, grid, stream);
