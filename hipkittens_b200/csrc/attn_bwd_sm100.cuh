@@ -58,6 +58,15 @@ struct BwdParams {
   int group_items;      // work items of a full group (all items when there is one group)
   int rounds_per_group; // ceil(group_items / CTAs): a group is dealt in rounds of its own (see item_for_round)
   int total_rounds;     // rounds_per_group * number of groups
+  // Item decode by multiply-and-shift division (see FastDiv), set per kernel by set_bwd_decode()
+  int G;                // H / H_KV
+  int last_group;       // index of the last causal sweep group (it may hold fewer units)
+  FastDiv fd_rounds;    // rounds_per_group
+  FastDiv fd_hkv;       // H_KV
+  FastDiv fd_unit;      // items per unit: key blocks (dK/dV kernel) or G * query tiles (dQ kernel)
+  FastDiv fd_inner;     // dQ kernel: query tiles (non-causal order) or G (causal order)
+  FastDiv fd_group;     // causal: items of a full group
+  FastDiv fd_in_grp, fd_in_grp_last;  // causal: items per key block / query tile in a full group, in the last group
   float scale;
   float scale_log2;
   const int* kv_lens;   // optional device [B]: batch b attends to keys [0, kv_lens[b]) only; null = NK
@@ -251,16 +260,21 @@ __device__ __forceinline__ void bwd_store_part_row(uint32_t taddr, __nv_bfloat16
     if constexpr (kChunk == 32) ptx::tmem_ld32(taddr + cc * 32, o);
     else ptx::tmem_ld16(taddr, o);
     ptx::tmem_wait_ld();
-    uint4* out = reinterpret_cast<uint4*>(dst + cc * kChunk);
     if (!row_exists) continue;  // the TMEM load above is warp-collective, the store is per row
+    uint32_t r[kChunk / 2];
 #pragma unroll
-    for (int v4 = 0; v4 < kChunk / 8; ++v4) {
-      uint4 val;
-      val.x = ptx::pack_bf16x2(__uint_as_float(o[v4 * 8 + 0]) * mul, __uint_as_float(o[v4 * 8 + 1]) * mul);
-      val.y = ptx::pack_bf16x2(__uint_as_float(o[v4 * 8 + 2]) * mul, __uint_as_float(o[v4 * 8 + 3]) * mul);
-      val.z = ptx::pack_bf16x2(__uint_as_float(o[v4 * 8 + 4]) * mul, __uint_as_float(o[v4 * 8 + 5]) * mul);
-      val.w = ptx::pack_bf16x2(__uint_as_float(o[v4 * 8 + 6]) * mul, __uint_as_float(o[v4 * 8 + 7]) * mul);
-      out[v4] = val;
+    for (int i = 0; i < kChunk / 2; ++i)
+      r[i] = ptx::pack_bf16x2(__uint_as_float(o[2 * i]) * mul, __uint_as_float(o[2 * i + 1]) * mul);
+    __nv_bfloat16* out = dst + cc * kChunk;
+    // 32 bytes per store where the row allows it: each thread writes a row of its own, so every store instruction
+    // touches 32 separate lines, and half as many instructions is half the time in the store unit
+    if ((reinterpret_cast<uintptr_t>(out) & 31) == 0) {
+#pragma unroll
+      for (int v8 = 0; v8 < kChunk / 16; ++v8) ptx::st_global_v8(out + v8 * 16, r + v8 * 8);
+    } else {
+#pragma unroll
+      for (int v4 = 0; v4 < kChunk / 8; ++v4)
+        reinterpret_cast<uint4*>(out)[v4] = make_uint4(r[v4 * 4], r[v4 * 4 + 1], r[v4 * 4 + 2], r[v4 * 4 + 3]);
     }
   }
 }
@@ -283,29 +297,25 @@ struct DkdvItem {
 template <bool CAUSAL>
 __device__ __forceinline__ DkdvItem decode_dkdv_item(const BwdParams& p, int idx) {
   DkdvItem w;
-  const int NBK = (p.NK + kBlockN - 1) / kBlockN;  // key blocks; the last may be partial
   const int NBQ = (p.N + kBlockM - 1) / kBlockM;   // query tiles
-  const int units = p.B * p.H_KV;
   int unit;
   if (CAUSAL) {
-    const int U = p.group_units;
-    const int grp = min(idx / (U * NBK), (units - 1) / U);
-    const int within = idx - grp * (U * NBK);
-    const int in_grp = min(U, units - grp * U);
-    w.j = within / in_grp;
-    unit = grp * U + within % in_grp;
+    const int grp = min(p.fd_group.div(idx), p.last_group);
+    const int within = idx - grp * p.group_items;
+    int u;
+    if (grp == p.last_group) p.fd_in_grp_last.divmod(within, w.j, u);
+    else p.fd_in_grp.divmod(within, w.j, u);
+    unit = grp * p.group_units + u;
   } else {
-    unit = idx / NBK;
-    w.j = idx % NBK;
+    p.fd_unit.divmod(idx, unit, w.j);
   }
-  w.b = unit / p.H_KV;
-  w.kvh = unit % p.H_KV;
+  p.fd_hkv.divmod(unit, w.b, w.kvh);
   w.kv_len = p.kv_lens ? min(max(p.kv_lens[w.b], 1), p.NK) : p.NK;
   w.off = w.kv_len - p.N;
   // causal: key c is seen by query rows r >= c - off; the first key of the block, j*128, is the one seen by most
   w.i_min = CAUSAL ? max(w.j * kBlockN - w.off, 0) / kBlockM : 0;
   w.cnt_i = max(NBQ - w.i_min, 0);
-  w.n_iter = (w.j * kBlockN >= w.kv_len) ? 0 : (p.H / p.H_KV) * w.cnt_i;
+  w.n_iter = (w.j * kBlockN >= w.kv_len) ? 0 : p.G * w.cnt_i;
   return w;
 }
 
@@ -377,7 +387,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   volatile uint32_t* abortp = abort_word;
-  const int G = p.H / p.H_KV;
+  const int G = p.G;
   // TMEM columns: X [0,128) takes the two score-shaped products in turn, S^T(n) then dP^T(n), each free again as soon
   // as the element-wise warps hold it in registers; Y [128,256) holds the two bf16 operands, P^T in [128,192) and dS^T
   // in [192,256), free again when dV(n) and dK(n) have consumed them; dK [256,256+D); dV [256+D,256+2D). Nothing
@@ -431,11 +441,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
         continue;
       }
-      for (int n = 0; n < w.n_iter && ok; ++n, ++it) {
+      // i_rel: position of the pair's query tile among the cnt_i tiles of its head (n % cnt_i, without the division)
+      for (int n = 0, i_rel = 0; n < w.n_iter && ok; ++n, ++it, i_rel = (i_rel + 1 == w.cnt_i) ? 0 : i_rel + 1) {
         HK_STAMP(trole, 0);
         // a query tile the diagonal runs through: its first row does not see the block's last key (with an offset
         // that is not a multiple of the tile these are two tiles per head, else the one at the block's own position)
-        const int i_t = w.i_min + n % w.cnt_i;
+        const int i_t = w.i_min + i_rel;
         const bool diag = CAUSAL && (i_t * kBlockM + w.off < w.j * kBlockN + kBlockN - 1);
         const float* sL = sStat + (it & 1) * 256 + part * kBwdPC;
         const float* sDl = sL + 128;
@@ -580,9 +591,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           tma_load_4d(sK + ch * kSub, &tmap_k, bars + KV_FULL, ch * 64, w.kvh, w.j * kBlockN, w.b);
           tma_load_4d(sV + ch * kSub, &tmap_v, bars + KV_FULL, ch * 64, w.kvh, w.j * kBlockN, w.b);
         }
-        for (int n = 0; n < w.n_iter && ok; ++n) {
-          const int head = w.kvh * G + n / w.cnt_i;
-          const int i = w.i_min + n % w.cnt_i;
+        for (int n = 0, g_rel = 0, i_rel = 0; n < w.n_iter && ok; ++n) {
+          const int head = w.kvh * G + g_rel;  // n / cnt_i and n % cnt_i, counted instead of divided
+          const int i = w.i_min + i_rel;
+          if (++i_rel == w.cnt_i) {
+            i_rel = 0;
+            ++g_rel;
+          }
           ok = mbar_wait(bars + QA_EMPTY + qa, qa_par ^ 1, abortp, kWaitLimitCycles);
           if (!ok) break;
           mbar_expect_tx(bars + QA_FULL + qa, kTile);
@@ -810,27 +825,24 @@ template <bool CAUSAL>
 __device__ __forceinline__ DqItem decode_dq_item(const BwdParams& p, int idx) {
   DqItem w;
   const int NB = (p.N + kBlockM - 1) / kBlockM;  // the last tile may be partial
-  const int G = p.H / p.H_KV;
-  const int units = p.B * p.H_KV;
+  const int G = p.G;
   int unit, g;
   if (CAUSAL) {
-    const int U = p.group_units;
-    const int grp = min(idx / (U * G * NB), (units - 1) / U);
-    const int within = idx - grp * (U * G * NB);
-    const int in_grp = min(U, units - grp * U) * G;
-    w.i = NB - 1 - within / in_grp;
-    const int rem = within % in_grp;
-    unit = grp * U + rem / G;
-    g = rem % G;
+    const int grp = min(p.fd_group.div(idx), p.last_group);
+    const int within = idx - grp * p.group_items;
+    int qd, rem;
+    if (grp == p.last_group) p.fd_in_grp_last.divmod(within, qd, rem);
+    else p.fd_in_grp.divmod(within, qd, rem);
+    w.i = NB - 1 - qd;
+    int u;
+    p.fd_inner.divmod(rem, u, g);
+    unit = grp * p.group_units + u;
   } else {
-    const int per_unit = G * NB;
-    unit = idx / per_unit;
-    const int rem = idx % per_unit;
-    g = rem / NB;
-    w.i = rem % NB;
+    int rem;
+    p.fd_unit.divmod(idx, unit, rem);
+    p.fd_inner.divmod(rem, g, w.i);
   }
-  w.b = unit / p.H_KV;
-  w.kvh = unit % p.H_KV;
+  p.fd_hkv.divmod(unit, w.b, w.kvh);
   w.h = w.kvh * G + g;
   w.kv_len = p.kv_lens ? min(max(p.kv_lens[w.b], 1), p.NK) : p.NK;
   w.off = w.kv_len - p.N;

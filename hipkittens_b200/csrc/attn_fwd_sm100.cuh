@@ -207,16 +207,7 @@ __device__ __forceinline__ WorkItem decode_item(const FwdParams& p, int idx) {
 // Returns the item index, or -1 when this CTA has no item in this round.
 template <typename Params>
 __device__ __forceinline__ int item_for_round(const Params& p, int round, int cta, int n_cta) {
-  const int grp = round / p.rounds_per_group;
-  const int r = round - grp * p.rounds_per_group;
-  const int first = grp * p.group_items;
-  const int in_grp = r * n_cta + (((r + grp) & 1) ? (n_cta - 1 - cta) : cta);
-  return (in_grp < min(p.group_items, p.n_items - first)) ? first + in_grp : -1;
-}
-
-// The same for the forward, whose parameters carry the divisor of the rounds in multiply-and-shift form.
-__device__ __forceinline__ int item_for_round(const FwdParams& p, int round, int cta, int n_cta) {
-  const int grp = p.fd_rounds.div(round);
+  const int grp = p.fd_rounds.div(round);  // round / rounds_per_group
   const int r = round - grp * p.rounds_per_group;
   const int first = grp * p.group_items;
   const int in_grp = r * n_cta + (((r + grp) & 1) ? (n_cta - 1 - cta) : cta);

@@ -278,13 +278,25 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
   return HK_OK;
 }
 
-// Sets the fields that say how a kernel's `n_items` work items are dealt to `grid` CTAs: one group (everything)
-// unless causal, where a group is `group_units` units of `per_unit` items each.
-void set_rounds(hk::BwdParams& p, int per_unit, int grid, bool causal) {
+// Sets the fields that say how a kernel's `n_items` work items are dealt to `grid` CTAs - one group (everything)
+// unless causal, where a group is `group_units` units of `per_unit` items each - and the divisors of the item
+// decode: `per_unit` items per (batch, kv-head) unit, `per_pos` of them per key block or query tile (1 in the dK/dV
+// kernel, G in the dQ kernel), `inner` the dQ kernel's second divisor.
+void set_bwd_decode(hk::BwdParams& p, int per_unit, int per_pos, int inner, int grid, bool causal) {
   p.group_items = causal ? p.group_units * per_unit : p.n_items;
   const int n_groups = (p.n_items + p.group_items - 1) / p.group_items;
   p.rounds_per_group = (p.group_items + grid - 1) / grid;
   p.total_rounds = p.rounds_per_group * n_groups;
+  const int units = p.B * p.H_KV;
+  p.G = p.H / p.H_KV;
+  p.last_group = (units - 1) / p.group_units;
+  p.fd_rounds = hk::FastDiv(p.rounds_per_group);
+  p.fd_hkv = hk::FastDiv(p.H_KV);
+  p.fd_unit = hk::FastDiv(per_unit);
+  p.fd_inner = hk::FastDiv(inner);
+  p.fd_group = hk::FastDiv(p.group_units * per_unit);
+  p.fd_in_grp = hk::FastDiv(p.group_units * per_pos);
+  p.fd_in_grp_last = hk::FastDiv((units - p.last_group * p.group_units) * per_pos);
 }
 
 template <int D, bool CAUSAL>
@@ -296,7 +308,7 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
     return HK_EINVAL;  // work items are indexed with int
   p.n_items = B * H_KV * nbk;
   int grid = p.n_items < sm_count ? p.n_items : sm_count;
-  set_rounds(p, nbk, grid, CAUSAL);
+  set_bwd_decode(p, nbk, 1, 1, grid, CAUSAL);
 #ifdef HK_TRACE
   long long* const trace_buf = p.trace;
   p.trace = g_trace_bwd_kernel == 0 ? trace_buf : nullptr;
@@ -307,7 +319,7 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
   HK_CUDA(cudaGetLastError());
   p.n_items = B * H * nbq;
   grid = p.n_items < sm_count ? p.n_items : sm_count;
-  set_rounds(p, (H / H_KV) * nbq, grid, CAUSAL);
+  set_bwd_decode(p, (H / H_KV) * nbq, H / H_KV, CAUSAL ? H / H_KV : nbq, grid, CAUSAL);
 #ifdef HK_TRACE
   p.trace = g_trace_bwd_kernel == 1 ? trace_buf : nullptr;
 #endif
