@@ -44,6 +44,17 @@ namespace hk {
 
 enum : int { kStatusSmemAlign = 3 };  // dynamic shared memory did not start on a 1024-byte boundary
 
+// Of every kBwdEmuMod column pairs of a score row, kBwdEmuCnt take their exponentials from the cubic polynomial on the
+// FMA pipe (ptx::ex2_poly2, relative error 1e-4, far inside the bf16 rounding of P and dS) instead of the MUFU.
+#ifndef HK_BWD_EMU_MOD
+#define HK_BWD_EMU_MOD 4
+#endif
+#ifndef HK_BWD_EMU_CNT
+#define HK_BWD_EMU_CNT 1
+#endif
+constexpr int kBwdEmuMod = HK_BWD_EMU_MOD;
+constexpr int kBwdEmuCnt = HK_BWD_EMU_CNT;
+
 struct BwdParams {
   const float* lse;     // [B,H,1,N] from the forward pass (natural log)
   const float* delta;   // [B,H,1,N] rowsum(dO * O)
@@ -67,6 +78,8 @@ struct BwdParams {
   FastDiv fd_inner;     // dQ kernel: query tiles (non-causal order) or G (causal order)
   FastDiv fd_group;     // causal: items of a full group
   FastDiv fd_in_grp, fd_in_grp_last;  // causal: items per key block / query tile in a full group, in the last group
+  int n_pairs;          // causal dK/dV kernel: pairs of key blocks (j, NBK - 1 - j) over all units
+  FastDiv fd_pairs;     // pairs per unit, (NBK + 1) / 2
   float scale;
   float scale_log2;
   const int* kv_lens;   // optional device [B]: batch b attends to keys [0, kv_lens[b]) only; null = NK
@@ -292,23 +305,31 @@ struct DkdvItem {
 };
 
 // Work order: one (batch, kv head) unit's key blocks are adjacent so that the CTAs running at the same
-// time read the same Q / dO tiles from L2. Causal: units are swept in L2-sized groups, key block 0 (the
-// longest) first inside a group.
+// time read the same Q / dO tiles from L2; an item index is unit * key blocks + key block.
+//
+// Causal: key block j meets G * (NBQ - j) query tiles, 64 times more for the first block than for the last at
+// N = 8192, and a unit has fewer blocks than the GPU has SMs, so no dealing of single blocks to CTAs balances. The
+// blocks are therefore dealt in pairs (j, NBK - 1 - j) of the same unit, which all cost the same: a CTA's round 2r
+// is the first block of its r-th pair and round 2r + 1 the second (none for the middle block of an odd count).
+template <bool CAUSAL>
+__device__ __forceinline__ int dkdv_item_for_round(const BwdParams& p, int round, int cta, int n_cta) {
+  if (!CAUSAL) return item_for_round(p, round, cta, n_cta);
+  const int pair = (round >> 1) * n_cta + cta;
+  if (pair >= p.n_pairs) return -1;
+  int unit, jp;
+  p.fd_pairs.divmod(pair, unit, jp);
+  const int nbk = static_cast<int>(p.fd_unit.d);
+  const int j = (round & 1) ? nbk - 1 - jp : jp;
+  if ((round & 1) && j == jp) return -1;
+  return unit * nbk + j;
+}
+
 template <bool CAUSAL>
 __device__ __forceinline__ DkdvItem decode_dkdv_item(const BwdParams& p, int idx) {
   DkdvItem w;
   const int NBQ = (p.N + kBlockM - 1) / kBlockM;   // query tiles
   int unit;
-  if (CAUSAL) {
-    const int grp = min(p.fd_group.div(idx), p.last_group);
-    const int within = idx - grp * p.group_items;
-    int u;
-    if (grp == p.last_group) p.fd_in_grp_last.divmod(within, w.j, u);
-    else p.fd_in_grp.divmod(within, w.j, u);
-    unit = grp * p.group_units + u;
-  } else {
-    p.fd_unit.divmod(idx, unit, w.j);
-  }
+  p.fd_unit.divmod(idx, unit, w.j);
   p.fd_hkv.divmod(unit, w.b, w.kvh);
   w.kv_len = p.kv_lens ? min(max(p.kv_lens[w.b], 1), p.NK) : p.NK;
   w.off = w.kv_len - p.N;
@@ -422,7 +443,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #endif
     for (int round = 0; ok; ++round) {
       if (round >= p.total_rounds) break;
-      const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+      const int idx = dkdv_item_for_round<CAUSAL>(p, round, blockIdx.x, gridDim.x);
       if (idx < 0) continue;  // a partial round leaves some CTAs without an item
       const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
       const bool pad_row = w.j * kBlockN + row >= w.kv_len;  // this key is padding (or lies beyond NK)
@@ -474,12 +495,24 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             const uint64_t xb = fma2(pack2(__uint_as_float(su[q4 * 4 + 2]), __uint_as_float(su[q4 * 4 + 3])), c2,
                                      pack2(l4.z, l4.w));
             float x0, x1, x2, x3;
-            unpack2(xa, x0, x1);
-            unpack2(xb, x2, x3);
-            su[q4 * 4 + 0] = __float_as_uint(ex2_approx(x0));
-            su[q4 * 4 + 1] = __float_as_uint(ex2_approx(x1));
-            su[q4 * 4 + 2] = __float_as_uint(ex2_approx(x2));
-            su[q4 * 4 + 3] = __float_as_uint(ex2_approx(x3));
+            // all 16 compute warps take their exponentials at the same time, which makes this phase MUFU-bound
+            // (16 results per clock and SM): a share of the column pairs goes through the FMA-pipe polynomial
+            if ((2 * q4) % kBwdEmuMod < kBwdEmuCnt) unpack2(ex2_poly2(xa), x0, x1);
+            else {
+              unpack2(xa, x0, x1);
+              x0 = ex2_approx(x0);
+              x1 = ex2_approx(x1);
+            }
+            if ((2 * q4 + 1) % kBwdEmuMod < kBwdEmuCnt) unpack2(ex2_poly2(xb), x2, x3);
+            else {
+              unpack2(xb, x2, x3);
+              x2 = ex2_approx(x2);
+              x3 = ex2_approx(x3);
+            }
+            su[q4 * 4 + 0] = __float_as_uint(x0);
+            su[q4 * 4 + 1] = __float_as_uint(x1);
+            su[q4 * 4 + 2] = __float_as_uint(x2);
+            su[q4 * 4 + 3] = __float_as_uint(x3);
           }
           if (diag) {
             // key j*128 + row is seen by query i_t*128 + col iff key <= query + off: earlier queries see nothing
@@ -578,7 +611,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       bool ok = true;
       for (int round = 0; ok; ++round) {
         if (round >= p.total_rounds) break;
-        const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+        const int idx = dkdv_item_for_round<CAUSAL>(p, round, blockIdx.x, gridDim.x);
         if (idx < 0) continue;  // a partial round leaves some CTAs without an item
         const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
         if (w.n_iter == 0) continue;  // key block wholly beyond this batch element's length: nothing to do
@@ -640,7 +673,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #endif
       for (int round = 0; ok; ++round) {
         if (round >= p.total_rounds) break;
-        const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+        const int idx = dkdv_item_for_round<CAUSAL>(p, round, blockIdx.x, gridDim.x);
         if (idx < 0) continue;  // a partial round leaves some CTAs without an item
         const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
         if (w.n_iter == 0) continue;  // key block wholly beyond this batch element's length: nothing to do
@@ -701,7 +734,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #endif
       for (int round = 0; ok; ++round) {
         if (round >= p.total_rounds) break;
-        const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+        const int idx = dkdv_item_for_round<CAUSAL>(p, round, blockIdx.x, gridDim.x);
         if (idx < 0) continue;  // a partial round leaves some CTAs without an item
         const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
         if (w.n_iter == 0) continue;  // key block wholly beyond this batch element's length: nothing to do
@@ -771,7 +804,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       };
       for (int round = 0; ok; ++round) {
         if (round >= p.total_rounds) break;
-        const int idx = item_for_round(p, round, blockIdx.x, gridDim.x);
+        const int idx = dkdv_item_for_round<CAUSAL>(p, round, blockIdx.x, gridDim.x);
         if (idx < 0) continue;  // a partial round leaves some CTAs without an item
         const DkdvItem w = decode_dkdv_item<CAUSAL>(p, idx);
         if (w.n_iter == 0) continue;  // key block wholly beyond this batch element's length: nothing to do
@@ -974,9 +1007,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 #pragma unroll
           for (int i = 0; i < kBwdPC / 2; ++i) {
             float x0, x1;
-            unpack2(fma2(pack2(__uint_as_float(su[2 * i]), __uint_as_float(su[2 * i + 1])), c2, nl2), x0, x1);
-            su[2 * i] = __float_as_uint(ex2_approx(x0));
-            su[2 * i + 1] = __float_as_uint(ex2_approx(x1));
+            const uint64_t x2 = fma2(pack2(__uint_as_float(su[2 * i]), __uint_as_float(su[2 * i + 1])), c2, nl2);
+            // a share of the column pairs through the FMA-pipe polynomial, as in the dK/dV kernel
+            if (i % kBwdEmuMod < kBwdEmuCnt) unpack2(ex2_poly2(x2), x0, x1);
+            else {
+              unpack2(x2, x0, x1);
+              x0 = ex2_approx(x0);
+              x1 = ex2_approx(x1);
+            }
+            su[2 * i] = __float_as_uint(x0);
+            su[2 * i + 1] = __float_as_uint(x1);
           }
           if (diag) {
             // key n*128 + col is seen by query i*128 + row iff it is <= query + off and < kv_len (this also zeroes

@@ -309,6 +309,14 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
   p.n_items = B * H_KV * nbk;
   int grid = p.n_items < sm_count ? p.n_items : sm_count;
   set_bwd_decode(p, nbk, 1, 1, grid, CAUSAL);
+  if (CAUSAL) {
+    // key blocks are dealt in pairs (j, nbk - 1 - j) of equal cost, two rounds per pair
+    const int per_unit = (nbk + 1) / 2;
+    p.n_pairs = B * H_KV * per_unit;
+    p.fd_pairs = hk::FastDiv(per_unit);
+    grid = p.n_pairs < sm_count ? p.n_pairs : sm_count;
+    p.total_rounds = 2 * ((p.n_pairs + grid - 1) / grid);
+  }
 #ifdef HK_TRACE
   long long* const trace_buf = p.trace;
   p.trace = g_trace_bwd_kernel == 0 ? trace_buf : nullptr;
