@@ -380,7 +380,8 @@ METRIC = {
 }
 # The other configurations of the benchmark, timed after the headline workload in the default single-GPU run.
 OTHER_WORKLOADS = ["gqa_causal_fwd_b4_n8192_h64_kv8_d128", "mha_fwd_b16_n4096_h16_d64",
-                   "paged_decode_s64_ctx512_8192_h64_kv8_d128", "gqa_bwd_b16_n2048_h64_kv8_d128"]
+                   "paged_decode_s64_ctx512_8192_h64_kv8_d128", "gqa_bwd_b16_n2048_h64_kv8_d128",
+                   "gqa_causal_bwd_b4_n8192_h64_kv8_d128"]
 
 
 def run_other_workloads(hk, _native, dev, stream, local_rank, sampler, barrier, peaks, peaks_src, steps, warmup):
