@@ -349,6 +349,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if (idx < 0) continue;  // a partial round leaves some CTAs without an item
       const WorkItem w = decode_item<CAUSAL>(p, idx);
       const int nkv = w.n[slot];
+      // causal: the last key this thread's row sees, and the first tile the diagonal (or the end of the keys) runs
+      // through - the last one, and the one before it when off is not a multiple of the tile. Key j*128 + i is
+      // visible to query row r iff it is <= r + off and < kv_len; tile j needs masking iff its last key is beyond
+      // what the block's FIRST row sees, (j+1)*128 - 1 > min(qb*128 + off, kv_len - 1) (CTA-uniform). Both are
+      // fixed for the item, so the per-tile test is one comparison.
+      const int row_last_key = min(w.qb[slot] * kBlockM + row + w.off, w.kv_len - 1);
+      const int j_mask = (min(w.qb[slot] * kBlockM + w.off, w.kv_len - 1) + 1) >> 7;
       if (nkv == 0) {
         if (CAUSAL && w.qb[slot] * kBlockM < p.N) {
           // a query block that sees no key at all (more queries than keys): defined output, no products
@@ -384,11 +391,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_free[slot]);
           }
-          if (CAUSAL && (j + 1) * kBlockN - 1 > min(w.qb[slot] * kBlockM + w.off, w.kv_len - 1)) {
-            // a tile the diagonal (or the end of the keys) runs through - the last one, and the one before it when
-            // off is not a multiple of the tile: key j*128 + i is visible to query row r iff it is <= r + off and
-            // < kv_len. (CTA-uniform condition: the first row of the block sees the fewest keys.)
-            const int lim = min(w.qb[slot] * kBlockM + row + w.off, w.kv_len - 1) - j * kBlockN;
+          if (CAUSAL && j >= j_mask) {
+            const int lim = row_last_key - j * kBlockN;
 #pragma unroll
             for (int i = 0; i < kBlockN; ++i) su[i] = (i > lim) ? 0xff800000u : su[i];
           }
@@ -493,11 +497,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
             for (int cc = 0; cc < 4; ++cc) tmem_ld32(tS + cc * 32, su + cc * 32);
             tmem_wait_ld();
-            if (CAUSAL && (j + 1) * kBlockN - 1 > min(w.qb[slot] * kBlockM + w.off, w.kv_len - 1)) {
-              // a tile the diagonal (or the end of the keys) runs through - the last one, and the one before it
-              // when off is not a multiple of the tile: key j*128 + i is visible to query row r iff it is
-              // <= r + off and < kv_len. (CTA-uniform condition: the first row of the block sees the fewest keys.)
-              const int lim = min(w.qb[slot] * kBlockM + row + w.off, w.kv_len - 1) - j * kBlockN;
+            if (CAUSAL && j >= j_mask) {
+              const int lim = row_last_key - j * kBlockN;
 #pragma unroll
               for (int i = 0; i < kBlockN; ++i) su[i] = (i > lim) ? 0xff800000u : su[i];
             }
