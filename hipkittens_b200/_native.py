@@ -40,6 +40,7 @@ EXPORTED_SYMBOLS = (
     "hk_paged_kv_append",
     "hk_last_device_status",
     "hk_selftest_bounded_wait",
+    "hk_selftest_fastdiv",
     "hk_kernel_launch_count",
     "hk_strerror",
     "hk_last_cuda_error",
@@ -117,6 +118,8 @@ def capi() -> ctypes.CDLL:
     lib.hk_last_device_status.restype = ci
     lib.hk_selftest_bounded_wait.argtypes = [ci, ctypes.c_uint]
     lib.hk_selftest_bounded_wait.restype = ci
+    lib.hk_selftest_fastdiv.argtypes = []
+    lib.hk_selftest_fastdiv.restype = ci
     lib.hk_kernel_launch_count.argtypes = []
     lib.hk_kernel_launch_count.restype = ctypes.c_ulonglong
     lib.hk_strerror.argtypes = [ci]

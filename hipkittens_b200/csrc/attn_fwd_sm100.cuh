@@ -81,6 +81,10 @@ struct FastDiv {
       shift = L - 1;
     }
   }
+  // the same arithmetic on the host (the self-test of the C ABI checks it against the division it replaces)
+  int div_host(int n) const {
+    return d == 1 ? n : static_cast<int>(((static_cast<uint64_t>(static_cast<uint32_t>(n)) * mul) >> 32) >> shift);
+  }
 #ifdef __CUDACC__
   __device__ __forceinline__ int div(int n) const {
     return d == 1 ? n : static_cast<int>(__umulhi(static_cast<uint32_t>(n), mul) >> shift);

@@ -786,6 +786,30 @@ int hk_last_device_status(int device) {
   return status_to_code(word);
 }
 
+int hk_selftest_fastdiv(void) {
+  // host only: the multiply-and-shift division of the item decode against the division it replaces, for every
+  // divisor up to 4096, divisors around every power of two, and dividends at the edges of [0, 2^31)
+  auto check = [](int d) {
+    const hk::FastDiv fd(d);
+    const long long top = 0x7fffffffll;
+    const long long probes[] = {0, 1, d - 1ll, d, d + 1ll, 2ll * d - 1, 2ll * d, 1000003ll * d + d - 1, top - d, top - 1, top,
+                                0x3fffffffll, 123456789ll, 2000000011ll};
+    for (long long n : probes) {
+      if (n < 0 || n > top) continue;
+      if (fd.div_host(int(n)) != int(n / d)) return false;
+    }
+    return true;
+  };
+  for (int d = 1; d <= 4096; ++d)
+    if (!check(d)) return HK_EINVAL;
+  for (int k = 1; k < 31; ++k)
+    for (int e = -1; e <= 1; ++e) {
+      const long long d = (1ll << k) + e;
+      if (d >= 1 && d <= 0x7fffffffll && !check(int(d))) return HK_EINVAL;
+    }
+  return HK_OK;
+}
+
 int hk_selftest_bounded_wait(int device, unsigned limit_us) {
   DeviceState* st = nullptr;
   DeviceScope scope;

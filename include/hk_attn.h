@@ -256,6 +256,12 @@ int hk_last_device_status(int device);
  * reference, whose kernels have no bounded waits. */
 int hk_selftest_bounded_wait(int device, unsigned limit_us);
 
+/* Host-only self-test (no GPU needed): the multiply-and-shift division by launch constants with which the kernels
+ * turn a work-item index into (batch, kv head, head, tile) is checked against integer division over divisors
+ * 1..4096, divisors around every power of two and dividends at the edges of [0, 2^31). Returns HK_OK. The reference
+ * decodes its block index with plain divisions (kernels/attn/gqa/kernel.cpp:104-118). */
+int hk_selftest_fastdiv(void);
+
 /* Number of kernels this library has launched in the calling process (all devices). */
 unsigned long long hk_kernel_launch_count(void);
 

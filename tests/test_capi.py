@@ -37,6 +37,12 @@ def test_strerror_texts(native_built):
     assert lib.hk_strerror(-99) == b"unknown error code"
 
 
+def test_item_decode_division_selftest(native_built):
+    """The kernels decode a work-item index with multiply-and-shift divisions by launch constants; the library checks
+    that arithmetic against integer division on the host (no GPU involved)."""
+    assert hk.capi().hk_selftest_fastdiv() == 0
+
+
 def _fwd(lib, q=64, k=64, v=64, o=64, l=64, B=1, N=128, H=2, HKV=1, D=128, causal=0):
     return lib.hk_attn_fwd(q, k, v, o, l, B, N, H, HKV, D, causal, 0.0, 0, None)
 
