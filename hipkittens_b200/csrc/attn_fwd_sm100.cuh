@@ -25,7 +25,7 @@
 //
 // Numerics: Q stays unscaled bf16; p = exp2(s*c - m*c) with c = scale*log2(e) in fp32; the running
 // max m is only refreshed when it grew by more than 8 in log2 units (the reference's lazy rescale,
-// kernels/attn/gqa/kernel.cpp:68,268-281) - at D = 128 it is not even looked for after an item's first tile, unless a
+// kernels/attn/gqa/kernel.cpp:68,268-281) - it is not even looked for after an item's first tile, unless a
 // row sum overflows (see the softmax loop); P is rounded to bf16 (RNE) for the PV product while the
 // row sum uses the fp32 values; L = m*scale + ln(l) (kernel.cpp:569-573 in the natural-log domain).
 #pragma once
@@ -406,34 +406,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
             for (int i = 0; i < kBlockN; ++i) su[i] = (i >= rem) ? 0xff800000u : su[i];
           }
-          float bm0 = fmaxf(HK_S(0), HK_S(1)), bm1 = fmaxf(HK_S(2), HK_S(3));
-          float bm2 = fmaxf(HK_S(4), HK_S(5)), bm3 = fmaxf(HK_S(6), HK_S(7));
+          // the first tile fixes m; later tiles take their exponentials against the m the row has and are redone
+          // with their maximum only if a row sum comes out huge or not finite
+          auto row_max = [&]() {
+            float bm0 = fmaxf(HK_S(0), HK_S(1)), bm1 = fmaxf(HK_S(2), HK_S(3));
+            float bm2 = fmaxf(HK_S(4), HK_S(5)), bm3 = fmaxf(HK_S(6), HK_S(7));
 #pragma unroll
-          for (int i = 8; i < kBlockN; i += 8) {
-            bm0 = max3(bm0, HK_S(i), HK_S(i + 1));
-            bm1 = max3(bm1, HK_S(i + 2), HK_S(i + 3));
-            bm2 = max3(bm2, HK_S(i + 4), HK_S(i + 5));
-            bm3 = max3(bm3, HK_S(i + 6), HK_S(i + 7));
-          }
-          const float bm = fmaxf(fmaxf(bm0, bm2), fmaxf(bm1, bm3));
-          if (kSepP && pv_cnt > 0) {
-            // S(j) may be ready before O += P(j-1) V(j-1) has finished: wait for that product before
-            // rescaling O or overwriting P
-            ok = mbar_wait(&p_free[slot], (pv_cnt - 1) & 1, abortp, kWaitLimitCycles);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
-          }
-          ++pv_cnt;
-          if (j == 0) {
-            m = bm;
-          } else {
+            for (int i = 8; i < kBlockN; i += 8) {
+              bm0 = max3(bm0, HK_S(i), HK_S(i + 1));
+              bm1 = max3(bm1, HK_S(i + 2), HK_S(i + 3));
+              bm2 = max3(bm2, HK_S(i + 4), HK_S(i + 5));
+              bm3 = max3(bm3, HK_S(i + 6), HK_S(i + 7));
+            }
+            return fmaxf(fmaxf(bm0, bm2), fmaxf(bm1, bm3));
+          };
+          auto raise_max = [&](float bm) {
+            if (j == 0) {
+              m = bm;
+              return;
+            }
             const float m_new = fmaxf(m, bm);
             const bool grow = (m_new - m) * c > kRescaleThresholdLog2;
             if (__any_sync(0xffffffffu, grow)) {
-              // The previous PV of this slot has completed (the commit that released this S tile
-              // was issued after it), so O is stable and nothing writes it until we publish P.
-              const float alpha = ex2_approx((m - m_new) * c);
+              const float alpha = (m == -INFINITY) ? 0.f : ex2_approx((m - m_new) * c);
               l *= alpha;
               m = m_new;
 #pragma unroll
@@ -446,45 +441,63 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 tmem_st32(tO + cc * 32, o);
               }
             }
-          }
-          // p = exp2(s*c - m*c), two columns per instruction where the hardware has packed fp32 forms.
-          // Of every kEmuMod column pairs, kEmuCnt compute exp2 on the FMA pipe (polynomial), the rest on
-          // the MUFU.
-          HK_STAMP2(slot, 3);
+          };
           const uint64_t c2 = pack2(c, c);
-          // a causal row that has seen no key yet has m = -inf: subtract nothing, its exponentials are exp2(-inf) = 0
-          const float nmc = (CAUSAL && m == -INFINITY) ? 0.f : -(m * c);
-          const uint64_t nmc2 = pack2(nmc, nmc);
-          uint64_t lacc0 = pack2(0.f, 0.f), lacc1 = pack2(0.f, 0.f);
+          // exponentials of the whole row against m, P stored chunk by chunk; returns the row sum of the tile
+          auto exps_and_store = [&]() -> float {
+            const float nmc = (CAUSAL && m == -INFINITY) ? 0.f : -(m * c);
+            const uint64_t nmc2 = pack2(nmc, nmc);
+            uint64_t lacc0 = pack2(0.f, 0.f), lacc1 = pack2(0.f, 0.f);
 #pragma unroll
-          for (int cc = 0; cc < 4; ++cc) {
-            uint32_t pk[16];
+            for (int cc = 0; cc < 4; ++cc) {
+              uint32_t pk[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const uint64_t x2 = fma2(pack2(HK_S(cc * 32 + 2 * i), HK_S(cc * 32 + 2 * i + 1)), c2, nmc2);
-              uint64_t p2;
-              float p0, p1;
-              if ((i % kEmuMod) < kEmuCnt) {
-                p2 = ex2_poly2(x2);
-                unpack2(p2, p0, p1);
-              } else {
-                float x0, x1;
-                unpack2(x2, x0, x1);
-                p0 = ex2_approx(x0);
-                p1 = ex2_approx(x1);
-                p2 = pack2(p0, p1);
+              for (int i = 0; i < 16; ++i) {
+                const uint64_t x2 = fma2(pack2(HK_S(cc * 32 + 2 * i), HK_S(cc * 32 + 2 * i + 1)), c2, nmc2);
+                uint64_t p2;
+                float p0, p1;
+                if ((i % kEmuMod) < kEmuCnt) {
+                  p2 = ex2_poly2(x2);
+                  unpack2(p2, p0, p1);
+                } else {
+                  float x0, x1;
+                  unpack2(x2, x0, x1);
+                  p0 = ex2_approx(x0);
+                  p1 = ex2_approx(x1);
+                  p2 = pack2(p0, p1);
+                }
+                if (i & 1) lacc1 = add2(lacc1, p2); else lacc0 = add2(lacc0, p2);
+                pk[i] = pack_bf16x2(p0, p1);
               }
-              if (i & 1) lacc1 = add2(lacc1, p2); else lacc0 = add2(lacc0, p2);
-              pk[i] = pack_bf16x2(p0, p1);
+              tmem_st16(tP + cc * 16, pk);
             }
-            tmem_st16(tP + cc * 16, pk);
-          }
-          {
             float a0, a1, b0, b1;
             unpack2(lacc0, a0, a1);
             unpack2(lacc1, b0, b1);
-            l += (a0 + a1) + (b0 + b1);
+            return (a0 + a1) + (b0 + b1);
+          };
+          bool exact = j == 0 || (CAUSAL && w.off < 0 && __any_sync(0xffffffffu, m == -INFINITY));
+          float bm_first = 0.f;
+          if (exact) bm_first = row_max();
+          if (kSepP && pv_cnt > 0) {
+            // S(j) may be ready before O += P(j-1) V(j-1) has finished: wait for that product before
+            // rescaling O or overwriting P
+            ok = mbar_wait(&p_free[slot], (pv_cnt - 1) & 1, abortp, kWaitLimitCycles);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
           }
+          ++pv_cnt;
+          if (exact) raise_max(bm_first);
+          HK_STAMP2(slot, 3);
+          float l_tile = exps_and_store();
+          if (!exact && __any_sync(0xffffffffu, !(l_tile < 1e30f))) {
+            // a score far above m: the P just stored is not published yet, S is still in registers - do the tile
+            // again the exact way
+            raise_max(row_max());
+            l_tile = exps_and_store();
+          }
+          l += l_tile;
 #undef HK_S
         } else {
           // ---- D = 128. Any reference value m within ~100 powers of two of a row's true maximum gives the same O

@@ -296,11 +296,12 @@ def test_adversarial_numerics(dev):
     o_ref, l_ref = attn_fwd_oracle(qb, k, v, False)
     assert float((o.float() - o_ref.float()).abs().max()) <= TOL_O
     assert float(((l - l_ref).abs() / l_ref.abs().clamp_min(1)).max()) <= 1e-5
-    # (f) logits that jump by hundreds of powers of two after the first tiles: with D = 128 the kernel takes its
-    # exponentials against the maximum it already has and must notice the overflow and redo the tile exactly; the
-    # jump sits in a full tile, in the partial last tile, and (causal) in a diagonal tile
-    for n, causal, jump_at in ((512, False, 300), (450, False, 400), (640, True, 520)):
-        qf, kf, vf = make_prefill_inputs(2, n, 4, 2, 128, seed=17 + n)
+    # (f) logits that jump by hundreds of powers of two after the first tiles: the kernel takes its exponentials
+    # against the maximum it already has and must notice the overflow and redo the tile exactly; the jump sits in a
+    # full tile, in the partial last tile, and (causal) in a diagonal tile, for both head dimensions
+    for n, causal, jump_at, hd in ((512, False, 300, 128), (450, False, 400, 128), (640, True, 520, 128),
+                                   (512, False, 300, 64), (450, False, 400, 64), (640, True, 520, 64)):
+        qf, kf, vf = make_prefill_inputs(2, n, 4, 2, hd, seed=17 + n)
         kj = kf.clone()
         kj[:, jump_at:] = (kf[:, jump_at:].float() * 60).to(torch.bfloat16)
         qj = (qf.float() * 4).to(torch.bfloat16)
@@ -308,7 +309,12 @@ def test_adversarial_numerics(dev):
         o_ref, l_ref = attn_fwd_oracle(qj, kj, vf, causal)
         assert torch.isfinite(o.float()).all() and torch.isfinite(l).all()
         assert float((o.float() - o_ref.float()).abs().max()) <= TOL_O
-        assert float(((l - l_ref).abs() / l_ref.abs().clamp_min(1)).max()) <= 1e-5
+        if hd == 128:
+            assert float(((l - l_ref).abs() / l_ref.abs().clamp_min(1)).max()) <= 1e-5
+        else:
+            # a quarter of the D = 64 exponentials come from a polynomial with a relative error of 1e-4, which is the
+            # absolute error of L when one such term dominates a row
+            assert float((l - l_ref).abs().max()) <= 2.5e-4
     # (g) logits that FALL by hundreds of powers of two after the first tile: later tiles underflow to zero, as they
     # should (their true weight is below fp32 resolution)
     kd = kf.clone()
@@ -316,7 +322,7 @@ def test_adversarial_numerics(dev):
     o, l = run_fwd(qj, kd, vf, False, dev)
     o_ref, l_ref = attn_fwd_oracle(qj, kd, vf, False)
     assert float((o.float() - o_ref.float()).abs().max()) <= TOL_O
-    assert float(((l - l_ref).abs() / l_ref.abs().clamp_min(1)).max()) <= 1e-5
+    assert float((l - l_ref).abs().max()) <= 2.5e-4  # D = 64 here (the last shape of the loop above)
 
 
 def test_bitwise_deterministic_and_gqa_equals_mha(dev):
