@@ -69,7 +69,7 @@ NCU_TRAFFIC_BYTES = {
     "gqa_fwd_b16_n2048_h64_kv8_d128": 4 * 264.7e6,
     # 2 x the B=2 / B=8 captures (profiles/attn_fwd_kernel_causal_d128_and_mha_d64.md)
     "gqa_causal_fwd_b4_n8192_h64_kv8_d128": 2 * (337.2e6 + 237.8e6),
-    "mha_fwd_b16_n4096_h16_d64": 2 * (201.4e6 + 51.2e6),
+    "mha_fwd_b16_n4096_h16_d64": 2 * (201.4e6 + 50.0e6),
     # backward, 4 x the B=4 capture of the two main kernels (profiles/attn_bwd_kernels_gqa_bwd_d128.md) + the prep kernel
     "gqa_bwd_b16_n2048_h64_kv8_d128": 4 * (363.0e6 + 416.4e6) + 1.082e9,
     # rate x duration of the section capture (profiles/rotary_kernel_and_paged_kv_append_kernel.md)
