@@ -57,6 +57,7 @@ WORKLOADS = {
     "profile_mha_fwd_b8_n4096_h16_d64": ("fwd", 8, 4096, 16, 16, 64, False),
     "profile_paged_decode_s14_ctx512_8192_h64_kv8_d128": ("decode", 14, 0, 64, 8, 128, False),
     "profile_gqa_bwd_b4_n2048_h64_kv8_d128": ("bwd", 4, 2048, 64, 8, 128, False),
+    "profile_gqa_causal_bwd_b1_n8192_h64_kv8_d128": ("bwd", 1, 8192, 64, 8, 128, True),
 }
 DECODE_POOL_PAGES = {"paged_decode_s64_ctx512_8192_h64_kv8_d128": 40000,
                      "profile_paged_decode_s14_ctx512_8192_h64_kv8_d128": 8000}
