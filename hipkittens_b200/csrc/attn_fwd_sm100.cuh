@@ -48,9 +48,11 @@ constexpr int kFwdRegsAtLaunch = 168;   // 65536 / 384, rounded down to a multip
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThresholdLog2 = 8.0f;
 // Of every kEmuMod column pairs of a score row, this many take their exponentials from a cubic polynomial on the
-// FMA pipe (ptx::ex2_poly2) instead of the MUFU. Per head dimension: with D = 64 there is one exponential per 64
-// multiply-adds instead of 128 and the MUFU is the busiest unit; with D = 128 every added instruction lengthens the
-// chain S -> softmax -> P V that bounds the kernel, and the polynomial measured slower at every share.
+// FMA pipe (ptx::ex2_poly2, relative error 1e-4) instead of the MUFU: an exponential costs its warp's scheduler 8
+// clocks at the MUFU, a polynomial pair about 13 against the 16 of two MUFU ones. A quarter of the pairs is the best
+// share for both head dimensions (D = 64: +3 %, half of them -10 %; D = 128: +1 %, a third of them -3 %). It is taken
+// at D = 64 only: it raises the error of L from 1e-5 to 1e-4 (of the 1e-3 allowed), which one per cent does not buy
+// at D = 128.
 #ifndef HK_EMU_MOD
 #define HK_EMU_MOD 4
 #endif
