@@ -56,6 +56,11 @@ constexpr float kRescaleThresholdLog2 = 8.0f;
 #ifndef HK_EMU_MOD
 #define HK_EMU_MOD 4
 #endif
+// 1: non-causal D = 64 sends O through shared memory and TMA as well (two staging tiles per slot, the store issued
+// by one of the slot's own threads); 0: 32-byte stores from registers, as causal D = 64 always does.
+#ifndef HK_D64_STAGE_OUT
+#define HK_D64_STAGE_OUT 1
+#endif
 #ifndef HK_EMU_CNT_D64
 #define HK_EMU_CNT_D64 1
 #endif
@@ -129,13 +134,16 @@ struct FwdParams {
 #endif
 };
 
-template <int D>
+template <int D, bool CAUSAL>
 struct FwdSmem {
   static constexpr int kTileBytes = kBlockM * D * 2;            // one 128 x D bf16 tile
   static constexpr int kSubTileBytes = kBlockM * 128;           // 128 rows x 64 bf16 (128 B swizzled rows)
   static constexpr int kStages = (D == 128) ? 4 : 8;            // a fifth stage at D = 128 measured no faster
-  // D = 128: one [128 x 128] staging tile (two 64-column halves) from which O leaves through TMA
-  static constexpr int kOutStageBytes = (D == 128) ? kTileBytes : 0;
+  // Staging from which O leaves through TMA. D = 128: one [128 x 128] tile (two 64-column halves) that the slots use
+  // in turn. D = 64 non-causal: two [128 x 64] tiles per slot, used alternately. D = 64 causal: none (it stores from
+  // registers, and shared memory it does not need is L1 cache it does).
+  static constexpr int kOutStageBytes =
+      (D == 128) ? kTileBytes : ((HK_D64_STAGE_OUT && !CAUSAL) ? 4 * kSubTileBytes : 0);
   static constexpr int kDynBytes = (2 + kStages) * kTileBytes + kOutStageBytes + 1024;  // + alignment slack
 };
 
@@ -263,7 +271,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
                 const FwdParams p) {
   using namespace ptx;
-  using SM = FwdSmem<D>;
+  using SM = FwdSmem<D, CAUSAL>;
   constexpr int kStages = SM::kStages;
   constexpr int kTile = SM::kTileBytes;
   constexpr int kSub = SM::kSubTileBytes;
@@ -279,10 +287,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint8_t* sQ = smem;                 // 2 tiles
   uint8_t* sKV = smem + 2 * kTile;    // kStages tiles, K and V alternate through the ring
   // D = 128: O leaves through TMA from one [128 x 128] staging tile (two 64-column halves) that the two slots use
-  // in turn. D = 64 stores from registers: its softmax warps are short of issue slots, and the staging instructions
-  // cost them more than the scattered 32-byte stores do.
+  // in turn, sent by the store thread. D = 64: see kStage64 below.
   uint8_t* sOut = sKV + kStages * kTile;
   constexpr bool kTmaOut = (D == 128);
+  // D = 64 non-causal: O leaves through two staging tiles per slot and TMA stores issued by one of the slot's own
+  // threads (+0.7 to +3 %, the more the shorter the sequence). Causal D = 64 keeps the 32-byte stores from
+  // registers: the staged form measured 3-4 % slower there.
+  constexpr bool kStage64 = (D == 64) && !CAUSAL && (HK_D64_STAGE_OUT != 0);
   // D = 64, non-causal: the Q tiles are loaded by a thread of their own (warp 11, which has no stores to send
   // there). Measured +1.7 % there, but -7 % at D = 64 causal and -2 % at D = 128 with short items, where the
   // producer thread goes on loading Q itself.
@@ -633,7 +644,44 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // (conflict-free 16-byte stores) and the store warp sends the tile to global memory as TMA boxes, which write
       // whole 128-byte lines and clip the rows beyond N. (Storing from registers, each thread its own row, touched
       // 32 separate lines per instruction and cost almost two tile periods per work item.)
-      if constexpr (!kTmaOut) {
+      if constexpr (kStage64) {
+        // D = 64: the slot's rows go into one of its two staging tiles, swizzled, and one of its threads sends the
+        // tile off with a TMA store. Tile k & 1 of the slot was last used by its store k - 2; the issuing thread
+        // waits for its previous store (k - 1) to have been read before it arrives on so_full, and every warp waits
+        // on so_full, so that when epilogue k + 1 starts the tile it writes is known to be free. (32-byte stores
+        // from registers, each thread its own row, kept the store unit busy for ~1 500 clocks per item and slot.)
+        const bool issuer_thread = (warp & 3) == 0 && lane == 0;
+        uint8_t* const so_tile = sOut + (slot * 2 + ((o_cnt - 1) & 1)) * kSub;
+        uint8_t* const so_row = so_tile + row * 128;
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t o[32];
+          tmem_ld32(tO + cc * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 val;
+            val.x = pack_bf16x2(__uint_as_float(o[u * 8 + 0]) * inv_l, __uint_as_float(o[u * 8 + 1]) * inv_l);
+            val.y = pack_bf16x2(__uint_as_float(o[u * 8 + 2]) * inv_l, __uint_as_float(o[u * 8 + 3]) * inv_l);
+            val.z = pack_bf16x2(__uint_as_float(o[u * 8 + 4]) * inv_l, __uint_as_float(o[u * 8 + 5]) * inv_l);
+            val.w = pack_bf16x2(__uint_as_float(o[u * 8 + 6]) * inv_l, __uint_as_float(o[u * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(so_row + (((cc * 4 + u) ^ (row & 7)) << 4)) = val;
+          }
+        }
+        fence_proxy_async();  // this thread's stores, visible to the TMA engine
+        __syncwarp();
+        if (lane == 0) {
+          if (issuer_thread) bulk_wait_group_read0();  // the slot's previous store has left its tile
+          mbar_arrive(&so_full[slot]);
+        }
+        ok = mbar_wait(&so_full[slot], (o_cnt - 1) & 1, abortp, kWaitLimitCycles);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (issuer_thread) {
+          tma_store_4d(&tmap_o, so_tile, 0, head, w.qb[slot] * kBlockM, w.b);
+          bulk_commit_group();
+        }
+      } else if constexpr (!kTmaOut) {
         // straight from registers, 32 bytes per store where the tensor allows it
         __nv_bfloat16* orow = p.o + ((static_cast<size_t>(w.b) * p.N + qrow) * p.H + head) * D;
         const bool wide = (reinterpret_cast<uintptr_t>(p.o) & 31) == 0;  // rows are multiples of 128 bytes apart
@@ -692,6 +740,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // order this slot's TMEM reads before the next item's PV (published through p_full)
       tc_fence_before();
     }
+    if (kStage64 && (warp & 3) == 0 && lane == 0) bulk_wait_group0();  // the last tiles have left
   } else {
     // ------------------------------------------------------------------ producer warpgroup
     asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");

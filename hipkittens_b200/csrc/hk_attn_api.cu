@@ -67,7 +67,7 @@ DeviceState g_dev[kMaxDevices];
 template <int D, bool CAUSAL>
 int prepare_fwd_kernel() {
   auto* fn = hk::attn_fwd_kernel<D, CAUSAL>;
-  HK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, hk::FwdSmem<D>::kDynBytes));
+  HK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, hk::FwdSmem<D, CAUSAL>::kDynBytes));
   cudaFuncAttributes attr;
   HK_CUDA(cudaFuncGetAttributes(&attr, fn));
   // The kernel re-balances registers between warpgroups (208 per softmax thread, 88 per producer thread);
@@ -272,7 +272,7 @@ __global__ void bounded_wait_selftest_kernel(int* status, unsigned long long lim
 template <int D, bool CAUSAL>
 int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
                const hk::FwdParams& p, int grid, cudaStream_t stream) {
-  hk::attn_fwd_kernel<D, CAUSAL><<<grid, hk::kFwdThreads, hk::FwdSmem<D>::kDynBytes, stream>>>(tq, tk, tv, to, p);
+  hk::attn_fwd_kernel<D, CAUSAL><<<grid, hk::kFwdThreads, hk::FwdSmem<D, CAUSAL>::kDynBytes, stream>>>(tq, tk, tv, to, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   HK_CUDA(cudaGetLastError());
   return HK_OK;
