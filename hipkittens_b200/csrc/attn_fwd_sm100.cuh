@@ -280,6 +280,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   // (columns [384,448) and [448,512)). S(j+1) = Q K(j+1)^T can then be issued as soon as the softmax has
   // read S(j), instead of after O += P(j) V(j), and a slot's softmax never waits for the tensor pipe.
   constexpr bool kSepP = (D == 64);
+  // Registers after the re-balancing: 8 softmax warps and 4 others share the 168 x 384 the CTA was launched with.
+  // 208 / 88 everywhere except the non-causal D = 64 kernel, which compiles to a 4 % faster schedule with 216 / 72
+  // (200 / 104 and 224 / 56 are both slower there, and 216 / 72 is 2.5 % slower for causal D = 64: the effect is the
+  // compiler's instruction schedule, not spills).
+  constexpr int kSoftmaxRegs = (D == 64 && !CAUSAL) ? 216 : 208;
+  constexpr int kOtherRegs = (D == 64 && !CAUSAL) ? 72 : 88;
+  static_assert(8 * kSoftmaxRegs + 4 * kOtherRegs == 12 * kFwdRegsAtLaunch, "registers taken = registers released");
   constexpr int kEmuCnt = (D == 64) ? HK_EMU_CNT_D64 : HK_EMU_CNT_D128;
 
   extern __shared__ uint8_t smem_raw[];
@@ -343,7 +350,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
   if (warp < 8) {
     // ------------------------------------------------------------------ softmax warpgroups
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
     const int slot = warp >> 2;
     const int row = (warp & 3) * 32 + lane;                      // row inside the tile == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -743,7 +750,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     if (kStage64 && (warp & 3) == 0 && lane == 0) bulk_wait_group0();  // the last tiles have left
   } else {
     // ------------------------------------------------------------------ producer warpgroup
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
     if (warp == 8) {
       // ---------------- TMA producer. Contiguous K/V: one thread (lane 0) walks the work list. Paged K/V: the whole
       // warp does, lane 0 doing the waits and lanes 0-7 each fetching one page of a K/V tile (one thread issuing the
