@@ -52,7 +52,9 @@ constexpr float kRescaleThresholdLog2 = 8.0f;
 // clocks at the MUFU, a polynomial pair about 13 against the 16 of two MUFU ones. A quarter of the pairs is the best
 // share for both head dimensions (D = 64: +3 %, half of them -10 %; D = 128: +1 %, a third of them -3 %). It is taken
 // at D = 64 only: it raises the error of L from 1e-5 to 1e-4 (of the 1e-3 allowed), which one per cent does not buy
-// at D = 128.
+// at D = 128. Which pairs matters as much as how many, through the instruction schedule the compiler arrives at: the
+// non-causal D = 64 kernel is fastest with the first two of every eight pairs (+1.4 % over one of every four; the
+// same quarter at other offsets or in runs of four is 0.5 to 3 % slower), the causal one with one of every four.
 #ifndef HK_EMU_MOD
 #define HK_EMU_MOD 4
 #endif
@@ -67,7 +69,12 @@ constexpr float kRescaleThresholdLog2 = 8.0f;
 #ifndef HK_EMU_CNT_D128
 #define HK_EMU_CNT_D128 0
 #endif
-constexpr int kEmuMod = HK_EMU_MOD;
+#ifndef HK_EMU_MOD_D64_NONCAUSAL
+#define HK_EMU_MOD_D64_NONCAUSAL 8
+#endif
+#ifndef HK_EMU_CNT_D64_NONCAUSAL
+#define HK_EMU_CNT_D64_NONCAUSAL 2
+#endif
 constexpr uint64_t kWaitLimitCycles = 8000ull * 1000 * 1000;  // SM cycles, > 4 s: far beyond any legitimate wait
 
 // Device status codes written to FwdParams::status (0 = OK).
@@ -287,7 +294,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   constexpr int kSoftmaxRegs = (D == 64 && !CAUSAL) ? 216 : 208;
   constexpr int kOtherRegs = (D == 64 && !CAUSAL) ? 72 : 88;
   static_assert(8 * kSoftmaxRegs + 4 * kOtherRegs == 12 * kFwdRegsAtLaunch, "registers taken = registers released");
-  constexpr int kEmuCnt = (D == 64) ? HK_EMU_CNT_D64 : HK_EMU_CNT_D128;
+  constexpr int kEmuMod = (D == 64 && !CAUSAL) ? HK_EMU_MOD_D64_NONCAUSAL : HK_EMU_MOD;
+  constexpr int kEmuCnt = (D == 64) ? (CAUSAL ? HK_EMU_CNT_D64 : HK_EMU_CNT_D64_NONCAUSAL) : HK_EMU_CNT_D128;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
